@@ -1,0 +1,76 @@
+// SwiGLU's elementwise middle: out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(g) = g / (1 + exp(-g))
+// in 32-bit (src/ops/silu_and_mul.cu:44-46,76-79).  The gate and up projections are one fused
+// matrix product, so both halves of a row sit side by side.
+// Also the plain residual add h += delta in 32-bit (src/ops/add.cu:16-27).
+#include "common.cuh"
+#include <algorithm>
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+
+template <typename T>
+__global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                                    long long total) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    if ((inter & 7) == 0) {
+        const long long groups = total / 8;
+        const int per_row = inter / 8;
+        for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups; g += stride) {
+            const long long t = g / per_row;
+            const int i = static_cast<int>(g - t * per_row) * 8;
+            float a[8], b[8], r[8];
+            load8(gu + t * 2 * inter + i, a);
+            load8(gu + t * 2 * inter + inter + i, b);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r[k] = silu(a[k]) * b[k];
+            store8(out + t * inter + i, r);
+        }
+    } else {
+        for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total; e += stride) {
+            const long long t = e / inter;
+            const int i = static_cast<int>(e - t * inter);
+            out[e] = from_f32<T>(silu(to_f32(gu[t * 2 * inter + i])) * to_f32(gu[t * 2 * inter + inter + i]));
+        }
+    }
+}
+
+extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_tokens, int inter,
+                                uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (inter <= 0) return LLM_REFUSED_SIZE;
+    if ((inter & 7) == 0 && (!aligned16(gu) || !aligned16(out))) return LLM_REFUSED_ALIGN;
+    const long long total = static_cast<long long>(num_tokens) * inter;
+    const int threads = 256;
+    const long long work = (inter & 7) == 0 ? total / 8 : total;
+    const int blocks = static_cast<int>(std::min<long long>((work + threads - 1) / threads, 148LL * 16));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == LLM_DT_F32)
+        silu_and_mul_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(gu),
+                                                              static_cast<float*>(out), inter, total);
+    else if (dtype == LLM_DT_BF16)
+        silu_and_mul_kernel<bf16><<<blocks, threads, 0, s>>>(static_cast<const bf16*>(gu),
+                                                             static_cast<bf16*>(out), inter, total);
+    else
+        return LLM_REFUSED_DTYPE;
+    return launch_status();
+}
+
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
+        h[i] += to_f32(delta[i]);
+}
+
+extern "C" int llm_residual_add(float* h, const void* delta, int delta_dtype, long long n, uintptr_t stream) {
+    if (n <= 0) return LLM_OK;
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<long long>((n + threads - 1) / threads, 148LL * 16));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (delta_dtype == LLM_DT_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, s>>>(h, static_cast<const float*>(delta), n);
+    else if (delta_dtype == LLM_DT_BF16)
+        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>(h, static_cast<const bf16*>(delta), n);
+    else
+        return LLM_REFUSED_DTYPE;
+    return launch_status();
+}

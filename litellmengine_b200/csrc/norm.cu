@@ -1,0 +1,81 @@
+// RMSNorm over the last dimension, fused with the residual add that precedes it.
+//
+//   v   = x[row] (+ delta[row])                      32-bit sum: the residual stream is float32
+//   out = v * rsqrt(mean(v^2) + eps) * w             sum of squares, rsqrt and products in 32-bit
+//
+// One block per output row.  `rows` (optional) picks which rows of x/delta are read, so the
+// final norm can run only at the positions whose logits are wanted.  With `write_sum` the sum
+// v is written back into x (the layer's residual update), which needs rows == nullptr.
+// Formula and product order (x*inv)*w: src/layers/rms_norm.cu:77-93; the reference runs the
+// add as its own kernel (src/ops/add.cu:16-27).
+#include "common.cuh"
+
+template <typename TX, typename TD, typename TO>
+__global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
+                               const float* __restrict__ w, TO* __restrict__ out,
+                               const int32_t* __restrict__ rows, int hidden, float eps,
+                               int write_sum) {
+    extern __shared__ float smem[];            // hidden floats + 33 for the reduction
+    float* v = smem;
+    float* scratch = smem + hidden;
+    const size_t src = rows ? static_cast<size_t>(rows[blockIdx.x]) : blockIdx.x;
+    TX* xr = x + src * hidden;
+    const TD* dr = delta ? delta + src * hidden : nullptr;
+    TO* orow = out + static_cast<size_t>(blockIdx.x) * hidden;
+    float ss = 0.0f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float a = to_f32(xr[h]);
+        if (dr) a += to_f32(dr[h]);
+        v[h] = a;
+        ss += a * a;
+        if (write_sum) xr[h] = from_f32<TX>(a);
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) orow[h] = from_f32<TO>(v[h] * inv * w[h]);
+}
+
+template <typename TX, typename TD, typename TO>
+static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out, const int32_t* rows,
+                          int num_rows, int hidden, float eps, int write_sum, cudaStream_t s) {
+    const size_t smem = (static_cast<size_t>(hidden) + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
+    auto kern = rmsnorm_kernel<TX, TD, TO>;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+    kern<<<num_rows, threads, smem, s>>>(static_cast<TX*>(x), static_cast<const TD*>(delta), w,
+                                         static_cast<TO*>(out), rows, hidden, eps, write_sum);
+    return launch_status();
+}
+
+// x: [*, hidden] (x_dtype), delta: same shape or null (delta_dtype), w: float32 [hidden],
+// out: [num_rows, hidden] (out_dtype), rows: int32 [num_rows] or null.
+extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dtype, const float* w,
+                           void* out, int out_dtype, const int32_t* rows, int num_rows, int hidden,
+                           float eps, int write_sum, uintptr_t stream) {
+    if (num_rows <= 0) return LLM_OK;
+    if (hidden <= 0) return LLM_REFUSED_SIZE;
+    if (write_sum && rows) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!delta) delta_dtype = x_dtype;
+    const int key = x_dtype * 4 + delta_dtype * 2 + out_dtype;
+#define CASE(k, TX, TD, TO)                                                                     \
+    case k:                                                                                       \
+        return launch_rmsnorm<TX, TD, TO>(x, delta, w, out, rows, num_rows, hidden, eps, write_sum, s);
+    switch (key) {
+        CASE(0, float, float, float)
+        CASE(1, float, float, bf16)
+        CASE(2, float, bf16, float)
+        CASE(3, float, bf16, bf16)
+        CASE(4, bf16, float, float)
+        CASE(5, bf16, float, bf16)
+        CASE(6, bf16, bf16, float)
+        CASE(7, bf16, bf16, bf16)
+    }
+#undef CASE
+    return LLM_REFUSED_DTYPE;
+}

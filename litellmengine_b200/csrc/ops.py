@@ -1,0 +1,286 @@
+"""Python faces of the CUDA kernels: argument checks, then one ctypes call per launch.
+
+Every function takes CUDA tensors, launches on torch's current stream, allocates only its
+result (or writes into `out`), and raises if the kernel refuses the sizes.  There is no CPU
+or library fallback here: a tensor that is not on a CUDA device is an error, and a missing
+compiler or library surfaces as `BuildError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int32, c_longlong, c_uint32, c_uint64, c_void_p
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+_REFUSALS = {
+    -1: "a size this kernel does not take",
+    -2: "a dtype combination this kernel is not built for",
+    -3: "a pointer or stride that is not 16-byte aligned",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib(family: str) -> ctypes.CDLL:
+    l = _libs.get(family)
+    if l is None:
+        l = ctypes.CDLL(build.ensure_built(family))
+        _libs[family] = l
+    return l
+
+
+def loaded_libraries():
+    return {k: v._name for k, v in _libs.items()}
+
+
+def _fn(family: str, name: str, argtypes, restype=c_int):
+    f = getattr(lib(family), name)
+    if f.argtypes is None:
+        f.argtypes = argtypes
+        f.restype = restype
+    return f
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused, {_REFUSALS.get(code, f'code {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not float32 or bfloat16")
+
+
+def _dev(*tensors) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("tensor is not on a CUDA device; the engine has no CPU path")
+        if not t.is_contiguous():
+            raise KernelError("tensor is not contiguous")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _i32(t: Optional[torch.Tensor], what: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+
+
+# ------------------------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [T, H] = table[ids]."""
+    _dev(ids, table, status, out)
+    _i32(ids, "ids")
+    T, (V, H) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    f = _fn("embedding", "llm_embedding_gather",
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(status), _stream()), "embedding")
+    return out
+
+
+def scatter_int32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor, count: torch.Tensor,
+                  max_count: int, status: torch.Tensor) -> None:
+    """dst.flat[index[i]] = value[i] for i < count[0] (count is a device scalar)."""
+    _dev(dst, index, value, count, status)
+    for t, n in ((dst, "dst"), (index, "index"), (value, "value"), (count, "count")):
+        _i32(t, n)
+    f = _fn("embedding", "llm_scatter_int32",
+            [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(dst), dst.numel(), _ptr(index), _ptr(value), _ptr(count), max_count, _ptr(status), _stream()),
+           "scatter_int32")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            write_sum: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = rmsnorm(x (+ delta)) * weight over the last dim; with `write_sum`, x += delta in place.
+    `rows` (int32) selects which rows are normalised (out has len(rows) rows)."""
+    _dev(x, weight, delta, rows, out)
+    _i32(rows, "rows")
+    H = x.shape[-1]
+    if weight.dtype != torch.float32 or weight.numel() != H:
+        raise KernelError("norm weight must be float32 of the row length")
+    if delta is not None and delta.shape != x.shape:
+        raise KernelError("delta must have x's shape")
+    n = rows.numel() if rows is not None else x.numel() // H
+    if out is None:
+        out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+    f = _fn("norm", "llm_rmsnorm",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
+             c_int, c_void_p])
+    _check(f(_ptr(x), _dt(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight), _ptr(out),
+             _dt(out), _ptr(rows), n, H, float(eps), 1 if write_sum else 0, _stream()), "rmsnorm")
+    return out
+
+
+def silu_and_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, 2I] -> [T, I]: silu(first half) * second half."""
+    _dev(gate_up, out)
+    T, two_i = gate_up.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("activation", "llm_silu_and_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _dt(gate_up), T, inter, _stream()), "silu_and_mul")
+    return out
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """h (float32) += delta, in place."""
+    _dev(h, delta)
+    if h.dtype != torch.float32 or h.shape != delta.shape:
+        raise KernelError("residual_add wants a float32 residual and a delta of its shape")
+    f = _fn("activation", "llm_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(h), _ptr(delta), _dt(delta), h.numel(), _stream()), "residual_add")
+    return h
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], positions, token_entry, entry_slot,
+                          block_table: Optional[torch.Tensor], q_norm_w, k_norm_w, eps: float, inv_freq,
+                          rotary_dim: int, nq: int, nkv: int, d: int, page_size: int, has_kv: bool,
+                          status: torch.Tensor, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Normalise and rotate q and k, write k and v into the cache pages, return q [T, nq*d].
+    cache: [num_pages, 2, nkv, page_size, d] of one stage (None with has_kv False)."""
+    _dev(qkv, cache, positions, token_entry, entry_slot, block_table, q_norm_w, k_norm_w, inv_freq, status, q_out)
+    for t, n in ((positions, "positions"), (token_entry, "token_entry"), (entry_slot, "entry_slot"),
+                 (block_table, "block_table")):
+        _i32(t, n)
+    T = qkv.shape[0]
+    heads_total = nq + (2 * nkv if has_kv else 0)
+    if qkv.shape[1] != heads_total * d:
+        raise KernelError(f"qkv row is {qkv.shape[1]}, expected {heads_total * d}")
+    if has_kv:
+        if cache is None or block_table is None or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+            raise KernelError("cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    for w in (q_norm_w, k_norm_w):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != d):
+            raise KernelError("q/k norm weight must be float32 [head_dim]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim):
+        raise KernelError("inv_freq must be float32 [rotary_dim/2]")
+    if q_out is None:
+        q_out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("rope_cache", "llm_qk_norm_rope_kv_write",
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p])
+    _check(f(_ptr(qkv), _ptr(q_out), _dt(qkv), _ptr(cache), _dt(cache) if cache is not None else _dt(qkv),
+             _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table),
+             block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
+             _ptr(inv_freq), rotary_dim if inv_freq is not None else 0, T, nq, nkv, d, page_size,
+             1 if has_kv else 0, cache.shape[0] if cache is not None else 0, _ptr(status), _stream()),
+           "qk_norm_rope_kv_write")
+    return q_out
+
+
+def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, positions, token_entry, entry_slot,
+                            block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                            window: Optional[int], scale: float, status: torch.Tensor,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every token in q [T, nq*d] over its request's pages."""
+    _dev(q, cache, positions, token_entry, entry_slot, block_table, status, out)
+    for t, n in ((positions, "positions"), (token_entry, "token_entry"), (entry_slot, "entry_slot"),
+                 (block_table, "block_table")):
+        _i32(t, n)
+    T = q.shape[0]
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    if out is None:
+        out = torch.empty_like(q)
+    f = _fn("attention_generic", "llm_paged_attention_generic",
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(cache), _dt(cache), _ptr(positions), _ptr(token_entry),
+             _ptr(entry_slot), _ptr(block_table), block_table.shape[1], T, nq, nkv, d, page_size,
+             int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _stream()),
+           "paged_attention_generic")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _dev(logits, out)
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise KernelError("logits must be float32 [rows, vocab]")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "llm_argmax_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(logits), R, V, _ptr(out), _stream()), "argmax_rows")
+    return out
+
+
+def sample_rows(logits: torch.Tensor, row_slot: torch.Tensor, sampler_state: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row by the row's slot state {seed_lo, seed_hi, counter, temperature bits};
+    temperature <= 0 takes the argmax.  Advances the counters of sampled rows."""
+    _dev(logits, row_slot, sampler_state, out)
+    _i32(row_slot, "row_slot")
+    _i32(sampler_state, "sampler_state")
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise KernelError("logits must be float32 [rows, vocab]")
+    if sampler_state.dim() != 2 or sampler_state.shape[1] != 4:
+        raise KernelError("sampler_state must be int32 [slots, 4]")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "llm_sample_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), R, V, _ptr(row_slot), _ptr(sampler_state), _ptr(out), _stream()), "sample_rows")
+    return out
+
+
+def sampler_uniform(seed: int, counter: int) -> float:
+    """The u in [0,1) that the sampling kernel draws for (seed, counter); runs on the host."""
+    f = _fn("sampling", "llm_sampler_uniform", [c_uint64, c_uint32], restype=c_float)
+    return float(f(seed & 0xFFFFFFFFFFFFFFFF, counter & 0xFFFFFFFF))
+
+
+# ------------------------------------------------------------------------------------------
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [T, K] @ weight[N, K]^T through the library matrix product (the reference uses cuBLAS for
+    its products too, src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a
+    float32 weight keeps its product in true float32 (no TF32), whatever x is."""
+    _dev(x, weight)
+    if weight.dtype == torch.float32:
+        y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
+        want = out_dtype or x.dtype
+        return y if want == torch.float32 else y.to(want)
+    if x.dtype != weight.dtype:
+        x = x.to(weight.dtype)
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return torch.mm(x, weight.t())
+
+
+def configure_library_products() -> None:
+    """No reduced-precision modes in the library products: float32 stays IEEE float32 and
+    bfloat16 products reduce in float32."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    try:
+        torch.set_float32_matmul_precision("highest")
+    except Exception:
+        pass

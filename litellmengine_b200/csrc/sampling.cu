@@ -1,0 +1,148 @@
+// Picking the next token on the device: greedy argmax and temperature sampling.
+//
+// argmax: largest logit, ties to the lowest index (src/ops/argmax.cu:41-62,98-114).
+// sampling (the reference parses --temperature but only ever takes the argmax,
+// src/main.cpp:175-178): p = softmax(logits / T) in 32-bit, u uniform in [0,1) from the
+// request's own random stream, token = first index whose cumulative probability exceeds u.
+//
+// Each request's stream lives in its fixed-size state slot: {seed_lo, seed_hi, counter,
+// temperature as float bits}.  u is a pure function of (seed, counter), so a request draws the
+// same numbers whatever else is in the batch; the kernel advances the counter.
+#include "common.cuh"
+#include <math_constants.h>
+
+#define SAMPLE_THREADS 1024
+
+__host__ __device__ inline uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    uint64_t z = x;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// 24 random bits -> [0, 1)
+__host__ __device__ inline float uniform_from(uint64_t seed, uint32_t counter) {
+    const uint64_t r = splitmix64(splitmix64(seed) + counter);
+    return static_cast<float>(r >> 40) * (1.0f / 16777216.0f);
+}
+
+struct MaxIdx {
+    float v;
+    int i;
+};
+__device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+__device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* sh) {
+    MaxIdx best = {-CUDART_INF_F, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best.v || (v == best.v && i < best.i)) best = {v, i};    // NaN never wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxIdx other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sh[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        MaxIdx b = (lane < (blockDim.x >> 5)) ? sh[lane] : MaxIdx{-CUDART_INF_F, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            MaxIdx other = {__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+            b = better(b, other);
+        }
+        if (lane == 0) sh[32] = b;
+    }
+    __syncthreads();
+    MaxIdx r = sh[32];
+    if (r.i == 0x7fffffff) r.i = 0;            // a row of NaN or -inf: token 0, like a scan from index 0
+    return r;
+}
+
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, int32_t* __restrict__ out) {
+    __shared__ MaxIdx sh[33];
+    const MaxIdx r = block_argmax(logits + static_cast<size_t>(blockIdx.x) * vocab, vocab, sh);
+    if (threadIdx.x == 0) out[blockIdx.x] = r.i;
+}
+
+extern "C" int llm_argmax_rows(const float* logits, int num_rows, int vocab, int32_t* out, uintptr_t stream) {
+    if (num_rows <= 0) return LLM_OK;
+    if (vocab <= 0) return LLM_REFUSED_SIZE;
+    argmax_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, vocab, out);
+    return launch_status();
+}
+
+__global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
+                                   const int32_t* __restrict__ row_slot, int32_t* __restrict__ sampler_state,
+                                   int32_t* __restrict__ out) {
+    __shared__ MaxIdx sh[33];
+    __shared__ float fs[33];
+    __shared__ float warp_tot[32];
+    __shared__ int result;
+    const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
+    int32_t* st = sampler_state + static_cast<size_t>(row_slot[blockIdx.x]) * 4;
+    const float temperature = __int_as_float(st[3]);
+    const MaxIdx top = block_argmax(row, vocab, sh);
+    if (!(temperature > 0.0f)) {
+        if (threadIdx.x == 0) out[blockIdx.x] = top.i;
+        return;
+    }
+    const uint64_t seed = (static_cast<uint64_t>(static_cast<uint32_t>(st[1])) << 32) | static_cast<uint32_t>(st[0]);
+    const uint32_t counter = static_cast<uint32_t>(st[2]);
+    const float u = uniform_from(seed, counter);
+    const float inv_t = 1.0f / temperature;
+
+    // Each thread owns a contiguous run of the vocabulary, so cumulative order is index order.
+    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
+    const int c0 = min(static_cast<int>(threadIdx.x) * chunk, vocab), c1 = min(c0 + chunk, vocab);
+    float mine = 0.0f;
+    for (int i = c0; i < c1; ++i) mine += expf((row[i] - top.v) * inv_t);
+    const float total = block_sum(mine, fs);
+
+    // exclusive prefix of `mine` over threads: inclusive scan inside the warp, then warp totals
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    if (threadIdx.x == 0) result = top.i;     // rounding may leave u*total past the last run
+    __syncthreads();
+    float before = 0.0f;
+    for (int wi = 0; wi < warp; ++wi) before += warp_tot[wi];
+    const float excl = before + incl - mine;
+    const float target = u * total;
+    if (c1 > c0 && target >= excl && target < excl + mine) {
+        float run = excl;
+        int pick = c1 - 1;
+        for (int i = c0; i < c1; ++i) {
+            run += expf((row[i] - top.v) * inv_t);
+            if (target < run) { pick = i; break; }
+        }
+        result = pick;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        out[blockIdx.x] = result;
+        st[2] = static_cast<int32_t>(counter + 1u);
+    }
+}
+
+extern "C" int llm_sample_rows(const float* logits, int num_rows, int vocab, const int32_t* row_slot,
+                               int32_t* sampler_state, int32_t* out, uintptr_t stream) {
+    if (num_rows <= 0) return LLM_OK;
+    if (vocab <= 0) return LLM_REFUSED_SIZE;
+    sample_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        logits, vocab, row_slot, sampler_state, out);
+    return launch_status();
+}
+
+// Host copy of the stream function, so that tests and the scheduler can predict u.
+extern "C" float llm_sampler_uniform(uint64_t seed, uint32_t counter) { return uniform_from(seed, counter); }

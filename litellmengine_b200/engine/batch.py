@@ -1,0 +1,139 @@
+"""One step's batch: what the host knows, packed once into a pinned buffer and copied to
+fixed device arrays that every kernel of the step reads.
+
+The reference builds fresh host vectors and device tensors for every call and only knows
+two shapes of batch: one prompt from position 0, or B single tokens
+(src/engine/paged_generate_engine.cpp:221-278,444-473).  Here a batch is any list of
+(request, its next tokens): prompt portions at any past length beside single decoded tokens.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its slot, the tokens to run now (they follow what the
+    cache already holds for it), and the places among them whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+    past: int = 0                     # filled in by the step function: tokens already cached
+
+
+class StepBuffers:
+    """Pinned staging and device arrays sized once for the largest step."""
+
+    def __init__(self, max_tokens: int, max_entries: int, num_groups: int, device):
+        self.max_tokens, self.max_entries, self.num_groups = max_tokens, max_entries, num_groups
+        self.max_updates = max_tokens + 2 * max_entries + 8      # new pages a step can append, with slack
+        T, B, U = max_tokens, max_entries, self.max_updates
+        off = 0
+        self.off = {}
+        for name, n in (("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
+                        ("entry_q_start", B), ("entry_q_len", B), ("entry_kv_len", B), ("want_rows", T),
+                        ("want_slot", T), ("counts", 8 + num_groups)):
+            self.off[name] = (off, n)
+            off += n
+        for g in range(num_groups):
+            self.off[f"upd_index{g}"] = (off, U)
+            off += U
+            self.off[f"upd_value{g}"] = (off, U)
+            off += U
+        self.size = off
+        self.device = torch.device(device)
+        self.pinned = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self.host = self.pinned.numpy()
+        self.dev = torch.zeros(off, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.copied = torch.cuda.Event()
+        self._in_flight = False
+
+    def host_view(self, name: str) -> np.ndarray:
+        o, n = self.off[name]
+        return self.host[o:o + n]
+
+    def dev_view(self, name: str, count: Optional[int] = None) -> torch.Tensor:
+        o, n = self.off[name]
+        return self.dev[o:o + (n if count is None else count)]
+
+    def wait_reusable(self) -> None:
+        if self._in_flight:
+            self.copied.synchronize()
+            self._in_flight = False
+
+    def upload(self) -> None:
+        self.dev.copy_(self.pinned, non_blocking=True)
+        self.copied.record()
+        self._in_flight = True
+
+
+@dataclass
+class StepBatch:
+    """Device views of one step (exact lengths) plus the host-side facts kernels are chosen by."""
+    token_ids: torch.Tensor          # int32 [T]
+    positions: torch.Tensor          # int32 [T] absolute position of each token in its request
+    token_entry: torch.Tensor        # int32 [T] index of the token's entry
+    entry_slot: torch.Tensor         # int32 [B]
+    entry_q_start: torch.Tensor      # int32 [B] first row of the entry in the batch
+    entry_q_len: torch.Tensor        # int32 [B]
+    entry_kv_len: torch.Tensor       # int32 [B] cached length after this step
+    want_rows: torch.Tensor          # int32 [W] rows whose logits are wanted
+    want_slot: torch.Tensor          # int32 [W] slot of each wanted row
+    status: torch.Tensor             # int32 [2]
+    num_tokens: int
+    num_entries: int
+    num_want: int
+    max_q_len: int
+    max_kv_len: int
+    entries: List[StepEntry] = field(default_factory=list)
+
+
+def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBatch:
+    """Fill the pinned buffer from `entries` (whose `past` is set) and the cache manager's
+    pending table `updates`, start the copy, and return the device views."""
+    T = sum(len(e.tokens) for e in entries)
+    B = len(entries)
+    if T > buffers.max_tokens or B > buffers.max_entries:
+        raise ValueError(f"a step of {T} tokens in {B} entries exceeds the limits "
+                         f"({buffers.max_tokens} tokens, {buffers.max_entries} entries)")
+    buffers.wait_reusable()
+    hv = buffers.host_view
+    tok, pos, ent = hv("token_ids"), hv("positions"), hv("token_entry")
+    slot, qs, ql, kl = hv("entry_slot"), hv("entry_q_start"), hv("entry_q_len"), hv("entry_kv_len")
+    wr, ws = hv("want_rows"), hv("want_slot")
+    row = w = 0
+    max_q = max_kv = 0
+    for i, e in enumerate(entries):
+        n = len(e.tokens)
+        tok[row:row + n] = np.asarray(e.tokens, dtype=np.int32)
+        pos[row:row + n] = np.arange(e.past, e.past + n, dtype=np.int32)
+        ent[row:row + n] = i
+        slot[i], qs[i], ql[i], kl[i] = e.slot, row, n, e.past + n
+        for j in e.want:
+            if not 0 <= j < n:
+                raise ValueError(f"want={j} is outside the entry's {n} tokens")
+            wr[w], ws[w] = row + j, e.slot
+            w += 1
+        max_q, max_kv = max(max_q, n), max(max_kv, e.past + n)
+        row += n
+    counts = hv("counts")
+    counts[0], counts[1], counts[2] = T, B, w
+    for g, (idx, val) in enumerate(updates):
+        if len(idx) > buffers.max_updates:
+            raise ValueError("more block-table changes than the step buffer holds")
+        hv(f"upd_index{g}")[:len(idx)] = idx
+        hv(f"upd_value{g}")[:len(val)] = val
+        counts[8 + g] = len(idx)
+    buffers.upload()
+    dv = buffers.dev_view
+    return StepBatch(
+        token_ids=dv("token_ids", T), positions=dv("positions", T), token_entry=dv("token_entry", T),
+        entry_slot=dv("entry_slot", B), entry_q_start=dv("entry_q_start", B), entry_q_len=dv("entry_q_len", B),
+        entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
+        status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
+        entries=entries)

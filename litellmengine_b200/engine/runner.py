@@ -1,0 +1,132 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and return the
+logits at the wanted places.  Everything above it (scheduler, generation, trace replay)
+calls this one function; everything below it (model, cache, kernels) is called from here.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, OutOfPages, StateNeed
+from ..config import load_config
+from ..csrc import ops
+from ..parts.model import Model
+from ..weights import RandomSource, SafetensorsSource, WeightSource
+from .batch import StepBatch, StepBuffers, StepEntry, pack_step
+
+STATUS_TEXT = {1: "a token id outside the vocabulary reached the embedding kernel",
+               2: "a block-table update pointed outside the table",
+               3: "the cache write met a page number outside the pool",
+               4: "attention met a page number outside the pool"}
+
+
+class ModelRunner:
+    """A model on one GPU with its cache manager and the step function.
+
+    The reference's engine owns the same things (src/engine/paged_generate_engine.cpp:17-97)
+    but has three entry points — prefill, decode_one_step, decode_batch (:99-341) — where this
+    has `step`.
+    """
+
+    def __init__(self, model: Model, page_size: int = 16, max_total_tokens: int = 4096,
+                 max_requests: int = 64, max_tokens_per_step: int = 8192,
+                 max_request_tokens: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: the engine has no CPU path")
+        ops.configure_library_products()
+        self.model = model
+        self.plan = model.plan
+        self.device = model.device
+        limit = min(max_request_tokens or self.plan.max_position, self.plan.max_position)
+        self.cache = CacheManager(
+            model.stage_needs(), page_size, max_total_tokens, max_requests, max_request_tokens=limit,
+            dtype=model.dtype, device=self.device,
+            extra_state={"sampler": StateNeed((4,), "int32")})
+        self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device)
+        self.steps_run = 0
+
+    # ---- construction ----------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda", **kw) -> "ModelRunner":
+        config = load_config(model_dir)
+        model = Model(config.plan(), dtype=dtype, device=device)
+        model.load_weights(SafetensorsSource(model_dir), where=model_dir)
+        r = cls(model, **kw)
+        r.config = config
+        return r
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, dtype="bfloat16", device="cuda",
+                    source: Optional[WeightSource] = None, **kw) -> "ModelRunner":
+        """Random weights drawn on the device (for benchmarks); `source` overrides them."""
+        model = Model(config.plan(), dtype=dtype, device=device)
+        if source is None:
+            store = torch.bfloat16 if model.dtype == torch.bfloat16 else torch.float32
+            source = RandomSource(model.parameters(), seed, store, device=device)
+        model.load_weights(source)
+        r = cls(model, **kw)
+        r.config = config
+        return r
+
+    # ---- requests --------------------------------------------------------------------------
+    def admit(self) -> int:
+        return self.cache.admit()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    # ---- the step --------------------------------------------------------------------------
+    def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """Host half of a step: checks, pages, metadata upload, block-table updates."""
+        entries = list(entries)
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        V, seen = self.plan.vocab_size, set()
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise ValueError("an entry needs at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise ValueError(f"token id {t} is outside the vocabulary [0, {V})")
+            e.past = self.cache.length(e.slot)
+            if e.past + len(e.tokens) > self.plan.max_position:
+                raise ValueError(f"position {e.past + len(e.tokens) - 1} exceeds max_position_embeddings "
+                                 f"{self.plan.max_position}")
+        if not self.cache.can_hold([(e.slot, e.past + len(e.tokens)) for e in entries]):
+            raise OutOfPages("the step's tokens do not fit the free pages")
+        for e in entries:
+            self.cache.ensure(e.slot, e.past + len(e.tokens))
+        batch = pack_step(self.buffers, entries, self.cache.drain_updates())
+        counts = self.buffers.dev_view("counts")
+        for g, group in enumerate(self.cache.groups):
+            n = int(self.buffers.host_view("counts")[8 + g])
+            if n:
+                ops.scatter_int32(group.table_dev, self.buffers.dev_view(f"upd_index{g}", n),
+                                  self.buffers.dev_view(f"upd_value{g}", n), counts[8 + g:9 + g], n,
+                                  self.buffers.status)
+        return batch
+
+    def finish(self, batch: StepBatch) -> None:
+        for e in batch.entries:
+            self.cache.commit(e.slot, e.past + len(e.tokens))
+        self.steps_run += 1
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch; returns float32 [wanted, vocab] in the order of
+        the entries and of each entry's `want`."""
+        batch = self.prepare(entries)
+        logits = self.model.forward(batch, self.cache)
+        self.finish(batch)
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel recorded a refused index (reads two ints back; synchronises)."""
+        code, where = self.buffers.status.tolist()
+        if code:
+            self.buffers.status.zero_()
+            raise RuntimeError(f"device status {code}: {STATUS_TEXT.get(code, 'unknown')} (at index {where})")

@@ -1,0 +1,101 @@
+"""The attention mixer: grouped-query causal attention over the paged cache."""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..cache import PagedNeed
+from ..config.specs import MixerSpec
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .context import StageContext
+from .registry import lookup, register_mixer
+
+
+@register_mixer("attention")
+class AttentionMixer:
+    """q/k/v projections without bias fused into one product, per-head RMSNorm of q and k,
+    rotation, cache write, attention over the pages, output projection
+    (src/model/qwen3.cpp:357-449,464-481,550-567).  kv head of query head h is h // (heads /
+    kv_heads); scores are scaled by 1/sqrt(head_dim) unless the spec gives a scale
+    (src/ops/attention.cu:204-207)."""
+
+    def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
+            raise ValueError("attention heads must be a positive multiple of kv heads")
+        if spec.head_dim <= 0 or spec.head_dim % 16 or spec.head_dim > 256:
+            raise ValueError(f"head_dim {spec.head_dim}: the attention kernels take multiples of 16 up to 256")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("an attention window must be positive")
+        self.spec = spec
+        self.hidden = hidden_size
+        self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.d))
+        self.dtype = compute_dtype
+        self.position = lookup("position", spec.position.kind)(spec.position, self.d, device)
+        self.q_norm = self.k_norm = None
+        if spec.qk_norm is not None:
+            cls = lookup("norm", spec.qk_norm.kind)
+            self.q_norm = cls(spec.qk_norm, self.d)
+            self.k_norm = cls(spec.qk_norm, self.d) if spec.has_kv else None
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        p = {"q_proj.weight": ParamSpec((self.nq * self.d, self.hidden)),
+             "o_proj.weight": ParamSpec((self.hidden, self.nq * self.d))}
+        if self.spec.has_kv:
+            p["k_proj.weight"] = ParamSpec((self.nkv * self.d, self.hidden))
+            p["v_proj.weight"] = ParamSpec((self.nkv * self.d, self.hidden))
+        if self.q_norm is not None:
+            p["q_norm.weight"] = self.q_norm.parameters()["weight"]
+        if self.k_norm is not None:
+            p["k_norm.weight"] = self.k_norm.parameters()["weight"]
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        parts = [t["q_proj.weight"]]
+        if self.spec.has_kv:
+            parts += [t["k_proj.weight"], t["v_proj.weight"]]
+        # Row concatenation, so one product yields [q | k | v] per token.  A float32 member
+        # keeps the fused matrix in float32.
+        dt = torch.float32 if any(x.dtype == torch.float32 for x in parts) else parts[0].dtype
+        self.w_qkv = torch.cat([x.to(dt) for x in parts], dim=0).contiguous()
+        self.w_o = t["o_proj.weight"].contiguous()
+        if self.q_norm is not None:
+            self.q_norm.load({"weight": t["q_norm.weight"]})
+        if self.k_norm is not None:
+            self.k_norm.load({"weight": t["k_norm.weight"]})
+
+    def cache_need(self):
+        if not self.spec.has_kv:
+            return None
+        return PagedNeed(self.nkv, self.d, self.spec.window)
+
+    def forward(self, x: torch.Tensor, ctx: StageContext) -> torch.Tensor:
+        b = ctx.batch
+        qkv = ops.linear(x, self.w_qkv, out_dtype=self.dtype)
+        has_kv = self.spec.has_kv and ctx.writes_cache
+        if self.spec.has_kv and not ctx.writes_cache:
+            raise RuntimeError("a mixer with its own keys and values was given a borrowed cache")
+        eps = self.spec.qk_norm.eps if self.spec.qk_norm is not None else 0.0
+        q = ops.qk_norm_rope_kv_write(
+            qkv, ctx.cache if has_kv else None, b.positions, b.token_entry, b.entry_slot,
+            ctx.block_table if has_kv else None,
+            self.q_norm.weight if self.q_norm is not None else None,
+            self.k_norm.weight if self.k_norm is not None else None, eps,
+            self.position.inv_freq, self.position.rotary_dim, self.nq, self.nkv, self.d,
+            ctx.page_size, has_kv, ctx.status)
+        a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
+        return ops.linear(a, self.w_o, out_dtype=self.dtype)
+
+
+def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,
+                         window: Optional[int], scale: float) -> torch.Tensor:
+    """Pick the attention kernel for this batch.  Every choice reads the same pages and gives
+    the same result up to rounding."""
+    b = ctx.batch
+    return ops.paged_attention_generic(q, ctx.cache, b.positions, b.token_entry, b.entry_slot,
+                                       ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

@@ -1,0 +1,39 @@
+"""Feed-forward parts."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..config.specs import FeedForwardSpec
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .registry import register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU:
+    """down(silu(gate(x)) * up(x)), no biases (src/model/qwen3.cpp:143-152,
+    src/ops/silu_and_mul.cu:44-46).  Gate and up are one fused product [g | u]."""
+
+    def __init__(self, spec: FeedForwardSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        if spec.intermediate_size <= 0:
+            raise ValueError("intermediate_size must be positive")
+        self.hidden, self.inter, self.dtype = hidden_size, spec.intermediate_size, compute_dtype
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        g, u = t["gate_proj.weight"], t["up_proj.weight"]
+        dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.w_down = t["down_proj.weight"].contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype)
+        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=self.dtype)

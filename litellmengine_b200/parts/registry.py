@@ -1,0 +1,68 @@
+"""Registries of the kinds of parts a layer can be assembled from.
+
+A part is a class built from its spec and the model's hidden size; it declares the tensors
+it wants (`parameters`), receives them (`load`), and runs (`forward`).  No part knows which
+model it is in.  Adding a kind is one `register_*` call; nothing else in the package
+changes.  The interfaces:
+
+  norm           __init__(spec: NormSpec, size: int)
+                 parameters() -> {local name: ParamSpec}
+                 load(tensors: {local name: tensor})
+                 forward(x, out_dtype, delta=None, rows=None, write_sum=False) -> tensor
+                     norm of x (+ delta); with write_sum the sum is stored back into x;
+                     rows picks the rows to normalise.
+  position       __init__(spec: PositionSpec, head_dim: int, device)
+                 tables needed by the mixer's kernels (for 'rope': `inv_freq`, `rotary_dim`)
+  mixer          __init__(spec: MixerSpec, hidden_size: int, compute_dtype, device)
+                 parameters(), load(tensors)
+                 cache_need() -> PagedNeed | StateNeed | None
+                 forward(x [T, hidden] compute dtype, ctx: StageContext) -> [T, hidden]
+  feed_forward   __init__(spec: FeedForwardSpec, hidden_size: int, compute_dtype, device)
+                 parameters(), load(tensors)
+                 forward(x [T, hidden]) -> [T, hidden]
+  arrangement    a function (block, h, delta, ctx) -> (h, delta) wiring a layer's parts
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict
+
+_KINDS: Dict[str, Dict[str, object]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {},
+                                        "arrangement": {}}
+
+
+def _register(family: str, kind: str):
+    def deco(obj):
+        _KINDS[family][kind] = obj
+        return obj
+    return deco
+
+
+def register_norm(kind: str):
+    return _register("norm", kind)
+
+
+def register_position(kind: str):
+    return _register("position", kind)
+
+
+def register_mixer(kind: str):
+    return _register("mixer", kind)
+
+
+def register_feed_forward(kind: str):
+    return _register("feed_forward", kind)
+
+
+def register_arrangement(kind: str):
+    return _register("arrangement", kind)
+
+
+def unregister(family: str, kind: str) -> None:
+    _KINDS[family].pop(kind, None)
+
+
+def lookup(family: str, kind: str):
+    try:
+        return _KINDS[family][kind]
+    except KeyError:
+        raise KeyError(f"no {family} of kind {kind!r}; registered: {sorted(_KINDS[family])}") from None
