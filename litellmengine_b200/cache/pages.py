@@ -170,7 +170,11 @@ class CacheManager:
         self.page_size = page_size
         self.max_slots = max_slots
         self.num_pages = (max_total_tokens + page_size - 1) // page_size
-        self.max_request_tokens = min(max_request_tokens or max_total_tokens, self.num_pages * page_size)
+        # A request can be longer than the pool only if every group forgets old positions.
+        keeps_all = any(isinstance(n, PagedNeed) and n.window is None for n in stage_needs)
+        self.max_request_tokens = max_request_tokens or max_total_tokens
+        if keeps_all:
+            self.max_request_tokens = min(self.max_request_tokens, self.num_pages * page_size)
         max_pages_per_request = (self.max_request_tokens + page_size - 1) // page_size
         self.device = device
         self.dtype = dtype

@@ -1,0 +1,122 @@
+"""The Python entry point: `PagedGenerateEngine`, named and shaped after the reference's
+class of that name (include/engine/paged_generate_engine.hpp:14-87): `add_request`,
+`generate_until_finished`, `finished`, `request`, `release_request`.  Where the reference
+has `prefill`, `decode_one_step` and `decode_batch`, this has one `step()` that runs
+whatever the scheduler picked — prompt portions and decode tokens in the same batch — and
+`run()` that steps until every request is finished.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..sampling import Sampler
+from .batch import StepEntry
+from .request import GenerationRequest, RequestStatus
+from .runner import ModelRunner
+from .scheduler import ScheduledPortion, Scheduler
+
+
+class PagedGenerateEngine:
+    def __init__(self, model, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
+                 max_total_tokens: int = 8192, max_requests: int = 64, max_tokens_per_step: int = 8192,
+                 chunk: Optional[int] = None, verbose: bool = False, seed: int = 0):
+        """`model`: a model folder (config.json + *.safetensors), a typed configuration (random
+        weights from `seed`, drawn on the device), or a ready `ModelRunner`."""
+        if isinstance(model, ModelRunner):
+            self.runner = model
+        else:
+            kw = dict(dtype=dtype, device=device, page_size=page_size, max_total_tokens=max_total_tokens,
+                      max_requests=max_requests, max_tokens_per_step=max_tokens_per_step)
+            if isinstance(model, str):
+                self.runner = ModelRunner.from_folder(model, **kw)
+            else:
+                self.runner = ModelRunner.from_config(model, seed=seed, **kw)
+        self.scheduler = Scheduler(self.runner.cache, self.runner.buffers.max_tokens, chunk)
+        self.sampler = Sampler(self.runner.cache.state["sampler"])
+        self.verbose = verbose
+        self._tokens_pinned = torch.empty(self.runner.buffers.max_entries, dtype=torch.int32, pin_memory=True)
+
+    # ---- the reference's surface -------------------------------------------------------------
+    def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int, eos_token_id: int = -1,
+                    temperature: float = 0.0, seed: int = 0) -> int:
+        return self.scheduler.add(prompt_ids, max_new_tokens, eos_token_id, temperature, seed).request_id
+
+    def request(self, request_id: int) -> GenerationRequest:
+        try:
+            return self.scheduler.requests[request_id]
+        except KeyError:
+            raise KeyError(f"request id not found: {request_id}") from None
+
+    def finished(self, request_id: int) -> bool:
+        return self.request(request_id).finished
+
+    def generate_until_finished(self, request_id: int) -> List[int]:
+        """Step until this request is finished (others in the queue advance too); returns prompt
+        plus generated ids, like the reference (src/engine/paged_generate_engine.cpp:343-365)."""
+        req = self.request(request_id)
+        while not req.finished:
+            self.step()
+        return list(req.input_ids)
+
+    def release_request(self, request_id: int) -> None:
+        """Forget a request.  A finished request holds no pages (they went back when it
+        finished); an unfinished one is taken out of the queues and its pages freed."""
+        req = self.request(request_id)
+        if not req.finished:
+            if req in self.scheduler.running:
+                self.scheduler.running.remove(req)
+                self.runner.cache.release(req.slot)
+            elif req in self.scheduler.waiting:
+                self.scheduler.waiting.remove(req)
+            req.status, req.finish_reason = RequestStatus.FINISHED, "released"
+        del self.scheduler.requests[request_id]
+
+    # ---- stepping --------------------------------------------------------------------------
+    def step(self) -> List[tuple]:
+        """Run one scheduled batch.  Returns [(request id, sampled token)] of this step."""
+        plan = self.scheduler.schedule()
+        if not plan:
+            return []
+        entries, samplers = [], []
+        for p in plan:
+            req = p.request
+            if req.cached_len == 0:           # first portion since admission: bind its random stream
+                self.sampler.admit(req.slot, req.seed, len(req.generated_ids), req.temperature)
+            toks = req.input_ids[req.cached_len:req.cached_len + p.num_tokens]
+            entries.append(StepEntry(req.slot, toks, [p.num_tokens - 1] if p.samples else []))
+            if p.samples:
+                samplers.append(req)
+        batch = self.runner.prepare(entries)
+        logits = self.runner.model.forward(batch, self.runner.cache)
+        self.runner.finish(batch)
+        tokens: List[int] = []
+        if samplers:
+            dev = self.sampler.sample(logits, batch.want_slot, any(r.temperature > 0 for r in samplers))
+            host = self._tokens_pinned[:len(samplers)]
+            host.copy_(dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            tokens = host.tolist()
+        out = [(r.request_id, t) for r, t in zip(samplers, tokens)]
+        self.scheduler.update(plan, tokens)
+        if self.verbose:
+            print(f"[step {self.runner.steps_run}] tokens={batch.num_tokens} entries={batch.num_entries} "
+                  f"sampled={out}")
+        return out
+
+    def run(self) -> None:
+        while self.scheduler.has_work():
+            self.step()
+        self.runner.check_status()
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, eos_token_id: int = -1,
+                 temperature: float = 0.0, seed: int = 0) -> List[List[int]]:
+        """Token ids in, new token ids out, for a list of prompts run together."""
+        ids = [self.add_request(p, max_new_tokens, eos_token_id, temperature, seed + i)
+               for i, p in enumerate(prompts)]
+        self.run()
+        out = [list(self.request(i).generated_ids) for i in ids]
+        for i in ids:
+            self.release_request(i)
+        return out

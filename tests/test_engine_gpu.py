@@ -1,0 +1,126 @@
+"""The engine against the plain implementation, in float32 and in bfloat16, for every way of
+cutting the work: whole, a tail decoded token by token, portions of changing size, and mixed
+batches of up to four live requests over so few pages that they are used again."""
+import numpy as np
+import pytest
+import torch
+
+import replay_helpers as rh
+import tiny_models as tm
+
+pytestmark = pytest.mark.gpu
+
+MODELS = {
+    "A": (tm.TINY_A, tm.TINY_A_SEED, tm.TINY_A_PAGE),
+    "B": (tm.TINY_B, tm.TINY_B_SEED, tm.TINY_B_PAGE),
+    "C": (tm.TINY_C, tm.TINY_C_SEED, tm.TINY_C_PAGE),
+}
+LENGTHS = {"A": [5, 9, 13, 40, 77], "B": [1, 7, 16, 33, 70, 121], "C": [64, 97, 150, 333]}
+
+
+def setup(name, dtype, sharp=True):
+    cfg, seed, page = MODELS[name]
+    bf = dtype == "bfloat16"
+    w = tm.make_weights(cfg, seed, bf16_exact=bf)
+    if sharp:
+        w = rh.sharpen(w, 4.0, bf16_exact=bf)
+    reqs = rh.requests_for(cfg, LENGTHS[name], seed)
+    return cfg, page, w, reqs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
+    cfg, page, w, reqs = setup(name, dtype)
+    ref = rh.plain_rows(cfg, w, reqs)
+    longest = max(len(t) for t in reqs.values())
+    traces = {
+        "whole": rh.trace_whole(reqs),
+        "tail": rh.trace_tail_decode(reqs, 32),
+        "portions": rh.trace_portions(reqs, seed=3),
+        "mixed": rh.trace_mixed(reqs, seed=5, max_live=4),
+        "mixed2": rh.trace_mixed(reqs, seed=6, max_live=3, prompt_frac=0.3),
+    }
+    results = {}
+    for what, steps in traces.items():
+        pool = rh.peak_tokens(steps, round_to=page)               # exactly enough: pages must be reused
+        runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=pool, max_requests=4,
+                                max_tokens_per_step=max(longest, 64))
+        got = rh.run_trace(runner, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        rh.assert_rows_match(got, ref, rh.tol_for(dtype), f"{name} {dtype} {what}")
+        results[what] = got
+    cut_tol = rh.FP32_CUT_TOL if dtype == "float32" else rh.BF16_CUT_TOL
+    whole = {r: np.stack([results["whole"][(r, p)] for p in range(len(t))]) for r, t in reqs.items()}
+    for what in ("tail", "portions", "mixed", "mixed2"):
+        rh.assert_rows_match(results[what], whole, cut_tol, f"{name} {dtype} {what} against whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page", [4, 8, 16, 64])
+def test_other_page_sizes(page, dtype):
+    cfg, _, w, reqs = setup("B", dtype)
+    ref = rh.plain_rows(cfg, w, reqs)
+    steps = rh.trace_mixed(reqs, seed=11, max_live=4)
+    runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=rh.peak_tokens(steps, page), max_tokens_per_step=256)
+    rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), f"page {page}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype):
+    """Three tokens of prompt, then 400 tokens one by one: every page edge is crossed by a
+    single-token step, and the first tokens of the sequence are decoded too."""
+    cfg, page, w, _ = setup("C", dtype)
+    toks = tm.random_tokens(cfg, 403, 77)
+    ref = rh.plain_rows(cfg, w, {"x": toks})
+    steps = rh.trace_tail_decode({"x": toks}, tail=400)
+    runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=rh.peak_tokens(steps, page))
+    rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), "long decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype):
+    """Lengths 1, 2, 3 and a request fed entirely one token at a time from position 0."""
+    cfg, page, w, _ = setup("A", dtype)
+    reqs = {f"s{n}": tm.random_tokens(cfg, n, 900 + n) for n in (1, 2, 3, 6)}
+    ref = rh.plain_rows(cfg, w, reqs)
+    for steps in (rh.trace_whole(reqs), rh.trace_tail_decode(reqs, tail=64)):
+        runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=64)
+        rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), "first tokens")
+
+
+def test_logits_only_where_wanted_and_a_step_may_want_nothing():
+    cfg, page, w, _ = setup("B", "float32")
+    toks = tm.random_tokens(cfg, 30, 5)
+    ref = rh.plain_rows(cfg, w, {"x": toks})["x"]
+    runner = rh.make_runner(cfg, w, "float32", page, max_total_tokens=64)
+    from litellmengine_b200.engine import StepEntry
+    s = runner.admit()
+    out = runner.step([StepEntry(s, toks[:20], [])])
+    assert out.shape == (0, cfg["vocab_size"])
+    out = runner.step([StepEntry(s, toks[20:], [9, 0, 3])]).cpu().numpy()
+    assert out.shape == (3, cfg["vocab_size"])
+    for row, pos in zip(out, (29, 20, 23)):
+        assert np.abs(row - ref[pos]).max() <= rh.FP32_TOL
+    runner.release(s)
+
+
+def test_step_refuses_bad_input_without_launching():
+    from litellmengine_b200.cache import OutOfPages
+    from litellmengine_b200.engine import StepEntry
+    cfg, page, w, _ = setup("A", "float32")
+    runner = rh.make_runner(cfg, w, "float32", page, max_total_tokens=16, max_requests=2)
+    s = runner.admit()
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        runner.step([StepEntry(s, [1, cfg["vocab_size"]], [])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry(s, list(range(17)), [])])
+    with pytest.raises(ValueError, match="twice"):
+        runner.step([StepEntry(s, [1], []), StepEntry(s, [2], [])])
+    assert runner.cache.length(s) == 0
+    runner.step([StepEntry(s, list(range(16)), [15])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry(s, [3], [0])])
+    runner.release(s)
+    runner.check_status()
+    runner.cache.check_invariants()
