@@ -90,7 +90,7 @@ def trace_mixed(reqs: Dict[str, List[int]], seed: int, max_live: int = 4, prompt
     while waiting or live:
         while waiting and len(live) < max_live:
             r, t = waiting.pop(0)
-            live.append((r, t, 0, max(2, int(len(t) * prompt_frac))))
+            live.append((r, t, 0, min(len(t), max(2, int(len(t) * prompt_frac)))))
         entries, ended, nxt = [], [], []
         for r, t, at, plen in live:
             if rng.random() < 0.15 and len(live) > 1:          # a request may sit a step out
@@ -100,6 +100,7 @@ def trace_mixed(reqs: Dict[str, List[int]], seed: int, max_live: int = 4, prompt
                 n = min(rng.choice((2, 3, 6, 11, 16, 23)), plen - at)
                 if plen - at - n == 1:
                     n += 1
+                assert n >= 1
             else:
                 n = 1
             entries.append({"id": r, "tokens": t[at:at + n], "want": list(range(n))})
