@@ -162,8 +162,10 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
 def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], positions, token_entry, entry_slot,
                           block_table: Optional[torch.Tensor], q_norm_w, k_norm_w, eps: float, inv_freq,
                           rotary_dim: int, nq: int, nkv: int, d: int, page_size: int, has_kv: bool,
-                          status: torch.Tensor, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Normalise and rotate q and k, write k and v into the cache pages, return q [T, nq*d].
+                          status: torch.Tensor, q_out: Optional[torch.Tensor] = None,
+                          q_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Normalise and rotate q and k, write k and v into the cache pages, return q [T, nq*d]
+    in `q_dtype` (default: qkv's).
     cache: [num_pages, 2, nkv, page_size, d] of one stage (None with has_kv False)."""
     _dev(qkv, cache, positions, token_entry, entry_slot, block_table, q_norm_w, k_norm_w, inv_freq, status, q_out)
     for t, n in ((positions, "positions"), (token_entry, "token_entry"), (entry_slot, "entry_slot"),
@@ -182,12 +184,13 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
     if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim):
         raise KernelError("inv_freq must be float32 [rotary_dim/2]")
     if q_out is None:
-        q_out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+        q_out = torch.empty((T, nq * d), dtype=q_dtype or qkv.dtype, device=qkv.device)
     f = _fn("rope_cache", "llm_qk_norm_rope_kv_write",
-            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
              c_void_p, c_void_p])
-    _check(f(_ptr(qkv), _ptr(q_out), _dt(qkv), _ptr(cache), _dt(cache) if cache is not None else _dt(qkv),
+    _check(f(_ptr(qkv), _dt(qkv), _ptr(q_out), _dt(q_out), _ptr(cache),
+             _dt(cache) if cache is not None else _dt(q_out),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
              _ptr(inv_freq), rotary_dim if inv_freq is not None else 0, T, nq, nkv, d, page_size,

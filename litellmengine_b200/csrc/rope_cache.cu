@@ -20,9 +20,9 @@
 
 #define RC_WARPS 4
 
-template <typename T, typename TC>
+template <typename TI, typename T, typename TC>
 __global__ void qk_norm_rope_kv_write_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, TC* __restrict__ cache,
+    const TI* __restrict__ qkv, T* __restrict__ q_out, TC* __restrict__ cache,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
@@ -36,7 +36,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int t = static_cast<int>(item / heads_total);
     const int head = static_cast<int>(item - static_cast<long long>(t) * heads_total);
     float* x = smem + warp * d;
-    const T* src = qkv + static_cast<size_t>(t) * heads_total * d + static_cast<size_t>(head) * d;
+    const TI* src = qkv + static_cast<size_t>(t) * heads_total * d + static_cast<size_t>(head) * d;
 
     float ss = 0.0f;
     for (int i = lane; i < d; i += 32) {
@@ -84,8 +84,10 @@ __global__ void qk_norm_rope_kv_write_kernel(
     for (int i = lane; i < d; i += 32) dst[i] = from_f32<TC>(x[i]);
 }
 
+// qkv: [T, heads_total * d] (qkv_dtype); q_out: [T, nq * d] (q_dtype); cache (cache_dtype).
 extern "C" int llm_qk_norm_rope_kv_write(
-    const void* qkv, void* q_out, int dtype, void* cache, int cache_dtype, const int32_t* positions,
+    const void* qkv, int qkv_dtype, void* q_out, int q_dtype, void* cache, int cache_dtype,
+    const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rotary_dim,
     int num_tokens, int nq, int nkv, int d, int page_size, int has_kv, int num_pages, int32_t* status,
@@ -100,15 +102,16 @@ extern "C" int llm_qk_norm_rope_kv_write(
     const long long items = static_cast<long long>(num_tokens) * heads_total;
     const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-#define LAUNCH(T, TC)                                                                               \
-    qk_norm_rope_kv_write_kernel<T, TC><<<blocks, RC_WARPS * 32, smem, s>>>(                        \
-        static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions,     \
+#define LAUNCH(TI, T, TC)                                                                           \
+    qk_norm_rope_kv_write_kernel<TI, T, TC><<<blocks, RC_WARPS * 32, smem, s>>>(                    \
+        static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions,    \
         token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq,      \
         rotary_dim, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status)
-    if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
-    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
-    else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
-    else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_F32) LAUNCH(bf16, float);
+    const int key = qkv_dtype * 4 + q_dtype * 2 + cache_dtype;
+    if (key == 0) LAUNCH(float, float, float);
+    else if (key == 3) LAUNCH(float, bf16, bf16);
+    else if (key == 7) LAUNCH(bf16, bf16, bf16);
+    else if (key == 1) LAUNCH(float, float, bf16);
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
     return launch_status();

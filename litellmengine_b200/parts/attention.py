@@ -76,7 +76,7 @@ class AttentionMixer:
 
     def forward(self, x: torch.Tensor, ctx: StageContext) -> torch.Tensor:
         b = ctx.batch
-        qkv = ops.linear(x, self.w_qkv, out_dtype=self.dtype)
+        qkv = ops.linear(x, self.w_qkv, out_dtype=torch.float32)    # normalised and rotated in 32-bit
         has_kv = self.spec.has_kv and ctx.writes_cache
         if self.spec.has_kv and not ctx.writes_cache:
             raise RuntimeError("a mixer with its own keys and values was given a borrowed cache")
@@ -87,9 +87,9 @@ class AttentionMixer:
             self.q_norm.weight if self.q_norm is not None else None,
             self.k_norm.weight if self.k_norm is not None else None, eps,
             self.position.inv_freq, self.position.rotary_dim, self.nq, self.nkv, self.d,
-            ctx.page_size, has_kv, ctx.status)
+            ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype)
         a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
-        return ops.linear(a, self.w_o, out_dtype=self.dtype)
+        return ops.linear(a, self.w_o, out_dtype=torch.float32)        # joins the float32 residual
 
 
 def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,

@@ -36,4 +36,4 @@ class SwiGLU:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype)
-        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=self.dtype)
+        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=torch.float32)   # joins the residual

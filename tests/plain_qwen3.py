@@ -7,7 +7,11 @@ reference file and lines it restates.  `tests/golden/` compares it once against
 the reference's own C++ code compiled for the CPU.
 
 A "model" here is a dict of hyper-parameters (`cfg`) plus a dict of float32
-tensors keyed by checkpoint tensor names (`w`).  `window` (None for Qwen3) and a
+tensors keyed by checkpoint tensor names (`w`).  `act` (default: identity) is applied
+wherever a bfloat16 engine stores an activation as an operand of a matrix product or
+in the cache: passing `to_bf16` makes this code round at those places too, which turns
+the comparison with a bfloat16 run from "within bfloat16's error" into "the same
+numbers up to summation order".  Everything else stays float32 either way.  `window` (None for Qwen3) and a
 per-layer hook exist so that tests of the engine's generality can reuse the same
 part functions with other wirings.
 """
@@ -18,6 +22,14 @@ from typing import Dict, List, Optional
 
 import numpy as np
 import torch
+
+
+def identity(t: torch.Tensor) -> torch.Tensor:
+    return t
+
+
+def to_bf16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(torch.float32)
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -83,7 +95,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
 
 def attention_block(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
-                    prefix: str, cfg: dict, window: Optional[int] = None) -> torch.Tensor:
+                    prefix: str, cfg: dict, window: Optional[int] = None, act=identity) -> torch.Tensor:
     """q/k/v projections without bias, per-head RMSNorm of q and k with one [d]
     weight each (same eps), rotation, attention, output projection.
     src/model/qwen3.cpp:357-449,550-567"""
@@ -94,9 +106,9 @@ def attention_block(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch
     v = (x @ w[f"{prefix}.v_proj.weight"].T).view(T, nkv, d)
     q = rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["rms_norm_eps"])
     k = rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["rms_norm_eps"])
-    q = rope(q, positions, cfg["rope_theta"])
-    k = rope(k, positions, cfg["rope_theta"])
-    a = causal_attention(q, k, v, window=window)
+    q = act(rope(q, positions, cfg["rope_theta"]))
+    k = act(rope(k, positions, cfg["rope_theta"]))
+    a = act(causal_attention(q, k, act(v), window=window))
     return a.reshape(T, nq * d) @ w[f"{prefix}.o_proj.weight"].T
 
 
@@ -105,26 +117,26 @@ def silu_and_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate / (1.0 + torch.exp(-gate)) * up
 
 
-def swiglu(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, act=identity) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)), no biases.  src/model/qwen3.cpp:143-152"""
-    g = x @ w[f"{prefix}.gate_proj.weight"].T
-    u = x @ w[f"{prefix}.up_proj.weight"].T
-    return silu_and_mul(g, u) @ w[f"{prefix}.down_proj.weight"].T
+    g = act(x @ w[f"{prefix}.gate_proj.weight"].T)
+    u = act(x @ w[f"{prefix}.up_proj.weight"].T)
+    return act(silu_and_mul(g, u)) @ w[f"{prefix}.down_proj.weight"].T
 
 
 def decoder_layer(h: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
-                  layer: int, cfg: dict, window: Optional[int] = None) -> torch.Tensor:
+                  layer: int, cfg: dict, window: Optional[int] = None, act=identity) -> torch.Tensor:
     """h += attn(norm_in(h)); h += mlp(norm_post(h)).  src/model/qwen3.cpp:948-968"""
     p = f"model.layers.{layer}"
-    a = attention_block(rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"]),
-                        positions, w, f"{p}.self_attn", cfg, window)
+    a = attention_block(act(rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])),
+                        positions, w, f"{p}.self_attn", cfg, window, act)
     h = h + a
-    f = swiglu(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, f"{p}.mlp")
+    f = swiglu(act(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])), w, f"{p}.mlp", act)
     return h + f
 
 
 def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
-                   layer_order: Optional[List[int]] = None) -> torch.Tensor:
+                   layer_order: Optional[List[int]] = None, act=identity) -> torch.Tensor:
     """Logits [T, V] for a whole sequence starting at position 0: embedding, the
     layers in order, final RMSNorm, output head (the embedding table when tied and
     `lm_head.weight` is absent).  src/model/qwen3.cpp:1242-1278,1501"""
@@ -134,8 +146,8 @@ def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
     h = embedding(ids, w["model.embed_tokens.weight"])
     order = layer_order if layer_order is not None else list(range(cfg["num_hidden_layers"]))
     for layer in order:
-        h = decoder_layer(h, positions, w, layer, cfg)
-    hn = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+        h = decoder_layer(h, positions, w, layer, cfg, act=act)
+    hn = act(rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w.get("lm_head.weight")
     if head is None:
         if not cfg.get("tie_word_embeddings", False):

@@ -11,8 +11,14 @@ import torch
 import plain_qwen3 as pq
 import tiny_models as tm
 
-FP32_TOL = 1e-5       # of max(1, max |reference logit|): float32 against the plain float32 code
-BF16_TOL = 3e-2       # bfloat16 run against the plain float32 code on bfloat16-exact weights
+# Tolerances are fractions of max(1, max |reference logit|).
+FP32_TOL = 1e-5       # float32 run against the plain float32 code
+# A bfloat16 run is compared twice.  Against the plain code rounding to bfloat16 where the
+# engine does (same weights, sharpened attention): what is left is summation order and the
+# rounding of values that straddle a bfloat16 boundary.  Against the plain float32 code on
+# unsharpened weights: bfloat16's own error.
+BF16_TOL = 1e-2
+BF16_VS_FP32_TOL = 1.5e-2
 # One way of cutting against another: both are roundings of the same exact value (the library
 # matrix product picks its summation order by the number of rows), so the bound is the same.
 FP32_CUT_TOL = FP32_TOL
@@ -156,8 +162,10 @@ def run_trace(runner, steps: List[dict]) -> Dict[Tuple[str, int], np.ndarray]:
     return collect(steps, got)
 
 
-def plain_rows(cfg: dict, weights, reqs: Dict[str, List[int]]) -> Dict[str, np.ndarray]:
-    return {r: pq.forward_logits(t, weights, cfg).numpy() for r, t in reqs.items()}
+def plain_rows(cfg: dict, weights, reqs: Dict[str, List[int]], dtype: str = "float32") -> Dict[str, np.ndarray]:
+    """Whole-sequence logits from the plain code; for a bfloat16 run it rounds where the engine does."""
+    act = pq.to_bf16 if dtype == "bfloat16" else pq.identity
+    return {r: pq.forward_logits(t, weights, cfg, act=act).numpy() for r, t in reqs.items()}
 
 
 def assert_rows_match(got: Dict[Tuple[str, int], np.ndarray], ref: Dict[str, np.ndarray], tol: float, what: str):

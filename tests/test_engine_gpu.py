@@ -32,7 +32,7 @@ def setup(name, dtype, sharp=True):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
     cfg, page, w, reqs = setup(name, dtype)
-    ref = rh.plain_rows(cfg, w, reqs)
+    ref = rh.plain_rows(cfg, w, reqs, dtype)
     longest = max(len(t) for t in reqs.values())
     traces = {
         "whole": rh.trace_whole(reqs),
@@ -56,11 +56,22 @@ def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
         rh.assert_rows_match(results[what], whole, cut_tol, f"{name} {dtype} {what} against whole")
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_bfloat16_against_the_plain_float32_code(name):
+    """Unsharpened N(0, 0.02) weights, bfloat16 run, plain code in float32 without any rounding."""
+    cfg, page, w, reqs = setup(name, "bfloat16", sharp=False)
+    ref = rh.plain_rows(cfg, w, reqs, "float32")
+    for steps in (rh.trace_whole(reqs), rh.trace_mixed(reqs, seed=8, max_live=4)):
+        runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=rh.peak_tokens(steps, page),
+                                max_tokens_per_step=512)
+        rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.BF16_VS_FP32_TOL, f"{name} bf16 vs fp32 plain")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("page", [4, 8, 16, 64])
 def test_other_page_sizes(page, dtype):
     cfg, _, w, reqs = setup("B", dtype)
-    ref = rh.plain_rows(cfg, w, reqs)
+    ref = rh.plain_rows(cfg, w, reqs, dtype)
     steps = rh.trace_mixed(reqs, seed=11, max_live=4)
     runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=rh.peak_tokens(steps, page), max_tokens_per_step=256)
     rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), f"page {page}")
@@ -72,7 +83,7 @@ def test_long_decoding(dtype):
     single-token step, and the first tokens of the sequence are decoded too."""
     cfg, page, w, _ = setup("C", dtype)
     toks = tm.random_tokens(cfg, 403, 77)
-    ref = rh.plain_rows(cfg, w, {"x": toks})
+    ref = rh.plain_rows(cfg, w, {"x": toks}, dtype)
     steps = rh.trace_tail_decode({"x": toks}, tail=400)
     runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=rh.peak_tokens(steps, page))
     rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), "long decode")
@@ -83,7 +94,7 @@ def test_first_tokens_of_a_sequence(dtype):
     """Lengths 1, 2, 3 and a request fed entirely one token at a time from position 0."""
     cfg, page, w, _ = setup("A", dtype)
     reqs = {f"s{n}": tm.random_tokens(cfg, n, 900 + n) for n in (1, 2, 3, 6)}
-    ref = rh.plain_rows(cfg, w, reqs)
+    ref = rh.plain_rows(cfg, w, reqs, dtype)
     for steps in (rh.trace_whole(reqs), rh.trace_tail_decode(reqs, tail=64)):
         runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=64)
         rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.tol_for(dtype), "first tokens")
