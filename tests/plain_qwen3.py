@@ -11,7 +11,10 @@ tensors keyed by checkpoint tensor names (`w`).  `act` (default: identity) is ap
 wherever a bfloat16 engine stores an activation as an operand of a matrix product or
 in the cache: passing `to_bf16` makes this code round at those places too, which turns
 the comparison with a bfloat16 run from "within bfloat16's error" into "the same
-numbers up to summation order".  Everything else stays float32 either way.  `window` (None for Qwen3) and a
+numbers up to summation order".  Everything else stays float32 either way.
+`forward_logits(..., wd=torch.float64)` runs the same formulas in double precision
+(the rotation angle stays the float32 product the reference defines), which makes it
+an oracle whose own rounding is negligible beside a float32 engine's.  `window` (None for Qwen3) and a
 per-layer hook exist so that tests of the engine's generality can reuse the same
 part functions with other wirings.
 """
@@ -42,10 +45,11 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """out = x * (1/sqrt(mean(x^2) + eps)) * w over the last dim, in float32.
     src/layers/rms_norm.cu:64-93 (mean = sum/size; product order (x*inv)*w)."""
-    x = x.to(torch.float32)
+    if not x.dtype.is_floating_point or x.dtype in (torch.bfloat16, torch.float16):
+        x = x.to(torch.float32)
     mean_sq = (x * x).sum(dim=-1, keepdim=True) / float(x.shape[-1])
-    inv = 1.0 / torch.sqrt(mean_sq + torch.tensor(eps, dtype=torch.float32))
-    return x * inv * weight.to(torch.float32)
+    inv = 1.0 / torch.sqrt(mean_sq + torch.tensor(eps, dtype=torch.float32).to(x.dtype))
+    return x * inv * weight.to(x.dtype)
 
 
 def rope_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
@@ -63,6 +67,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
     T, H, d = x.shape
     half = d // 2
     ang = positions.to(torch.float32)[:, None] * rope_inv_freq(d, theta)[None, :]   # float32 product
+    ang = ang.to(x.dtype)
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x1, x2 = x[..., :half], x[..., half:]
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
@@ -136,14 +141,14 @@ def decoder_layer(h: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.T
 
 
 def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
-                   layer_order: Optional[List[int]] = None, act=identity) -> torch.Tensor:
+                   layer_order: Optional[List[int]] = None, act=identity, wd=torch.float32) -> torch.Tensor:
     """Logits [T, V] for a whole sequence starting at position 0: embedding, the
     layers in order, final RMSNorm, output head (the embedding table when tied and
     `lm_head.weight` is absent).  src/model/qwen3.cpp:1242-1278,1501"""
     ids = torch.as_tensor(ids, dtype=torch.int64)
-    w = {k: t.to(torch.float32) for k, t in w.items()}
+    w = {k: t.to(wd) for k, t in w.items()}
     positions = torch.arange(ids.shape[0], dtype=torch.int32)
-    h = embedding(ids, w["model.embed_tokens.weight"])
+    h = embedding(ids, w["model.embed_tokens.weight"]).to(wd)
     order = layer_order if layer_order is not None else list(range(cfg["num_hidden_layers"]))
     for layer in order:
         h = decoder_layer(h, positions, w, layer, cfg, act=act)
@@ -153,7 +158,7 @@ def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
         if not cfg.get("tie_word_embeddings", False):
             raise KeyError("lm_head.weight")
         head = w["model.embed_tokens.weight"]
-    return hn @ head.T
+    return (hn @ head.T).to(torch.float32)
 
 
 def argmax_token(logits_row: torch.Tensor) -> int:

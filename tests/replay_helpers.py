@@ -12,7 +12,7 @@ import plain_qwen3 as pq
 import tiny_models as tm
 
 # Tolerances are fractions of max(1, max |reference logit|).
-FP32_TOL = 1e-5       # float32 run against the plain float32 code
+FP32_TOL = 1e-5       # float32 run against the plain code in double precision
 # A bfloat16 run is compared twice.  Against the plain code rounding to bfloat16 where the
 # engine does (same weights, sharpened attention): what is left is summation order and the
 # rounding of values that straddle a bfloat16 boundary.  Against the plain float32 code on
@@ -163,9 +163,12 @@ def run_trace(runner, steps: List[dict]) -> Dict[Tuple[str, int], np.ndarray]:
 
 
 def plain_rows(cfg: dict, weights, reqs: Dict[str, List[int]], dtype: str = "float32") -> Dict[str, np.ndarray]:
-    """Whole-sequence logits from the plain code; for a bfloat16 run it rounds where the engine does."""
-    act = pq.to_bf16 if dtype == "bfloat16" else pq.identity
-    return {r: pq.forward_logits(t, weights, cfg, act=act).numpy() for r, t in reqs.items()}
+    """Whole-sequence logits from the plain code.  For a float32 run the oracle works in double
+    precision, so that the error measured is the engine's own; for a bfloat16 run it works in
+    float32 and rounds to bfloat16 where the engine does."""
+    if dtype == "bfloat16":
+        return {r: pq.forward_logits(t, weights, cfg, act=pq.to_bf16).numpy() for r, t in reqs.items()}
+    return {r: pq.forward_logits(t, weights, cfg, wd=torch.float64).numpy() for r, t in reqs.items()}
 
 
 def assert_rows_match(got: Dict[Tuple[str, int], np.ndarray], ref: Dict[str, np.ndarray], tol: float, what: str):
