@@ -17,9 +17,12 @@ class NoPosition:
 
 @register_position("rope")
 class RotaryPosition:
-    """Half-split rotation: inv_freq[i] = theta ** (-(2 i) / rotary_dim), computed once in
-    float32 with theta held as float32, as the reference does per call
-    (src/layers/rotary.cu:81-83).  The angle float(pos) * inv_freq[i] and its sine and cosine
+    """Half-split rotation: inv_freq[i] = powf(theta, -(2 i) / rotary_dim) with theta and the
+    exponent held as float32, as the reference computes per call (src/layers/rotary.cu:81-83).
+    The table is made once, as the correctly rounded float32 power (the power taken in double
+    precision of the float32 operands, then rounded): an inv_freq that is one unit in the last
+    place off turns into an angle error of position * 6e-8, which is what separates one powf
+    from another at long contexts.  The angle float(pos) * inv_freq[i] and its sine and cosine
     are computed in 32-bit inside the kernel (src/layers/rotary.cu:101-105)."""
 
     def __init__(self, spec: PositionSpec, head_dim: int, device):
@@ -30,5 +33,7 @@ class RotaryPosition:
             raise ValueError("rope theta must be positive")
         self.rotary_dim = rd
         i = torch.arange(rd // 2, dtype=torch.float32)
-        expo = -(2.0 * i) / torch.tensor(float(rd), dtype=torch.float32)
-        self.inv_freq = torch.pow(torch.tensor(spec.theta, dtype=torch.float32), expo).to(device).contiguous()
+        expo = -(2.0 * i) / torch.tensor(float(rd), dtype=torch.float32)            # float32 quotient
+        theta32 = torch.tensor(spec.theta, dtype=torch.float32)
+        inv = torch.pow(theta32.double(), expo.double()).to(torch.float32)
+        self.inv_freq = inv.to(device).contiguous()

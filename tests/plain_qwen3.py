@@ -53,11 +53,15 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def rope_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
-    """inv_freq_i = theta ** (-(2i)/head_dim) in float32 with theta held as float32.
-    src/layers/rotary.cu:81-83"""
+    """inv_freq_i = powf(theta, -(2i)/head_dim): theta and the exponent are float32, the
+    exponent is the float32 quotient.  src/layers/rotary.cu:81-83.  The C library's powf is
+    correctly rounded in all but rare cases, so it is restated as the double-precision power
+    of the float32 operands, rounded to float32 (numpy's float32 power is sometimes one unit
+    in the last place off, which shows as an angle error of position * 6e-8)."""
     i = np.arange(head_dim // 2, dtype=np.float32)
-    expo = -(2.0 * i).astype(np.float32) / np.float32(head_dim)
-    return torch.from_numpy(np.power(np.float32(theta), expo).astype(np.float32))
+    expo = (-(2.0 * i).astype(np.float32) / np.float32(head_dim)).astype(np.float32)
+    inv = np.power(np.float64(np.float32(theta)), expo.astype(np.float64)).astype(np.float32)
+    return torch.from_numpy(inv)
 
 
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
