@@ -48,8 +48,13 @@ def _fn(family: str, name: str, argtypes, restype=c_int):
     return f
 
 
+launch_count = 0          # launches of the engine's own kernels since import (library products are not counted)
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
     if code == 0:
+        launch_count += 1
         return
     if code < 0:
         raise KernelError(f"{what}: refused, {_REFUSALS.get(code, f'code {code}')}")
