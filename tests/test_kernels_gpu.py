@@ -1,0 +1,314 @@
+"""Each CUDA kernel alone against a plain float32 statement of the same operation, at sizes the
+tiny models do not have (rows that are no multiple of 8, head sizes 16 to 256, groups of 1, 3
+and 8, vocabularies that are no power of two), in float32 and bfloat16."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as pq
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def ops():
+    from litellmengine_b200.csrc import ops as o
+    return o
+
+
+def status():
+    return torch.zeros(2, dtype=torch.int32, device=DEV)
+
+
+def close(a, b, tol):
+    a, b = a.double().cpu(), b.double().cpu()
+    scale = max(1.0, float(b.abs().max()))
+    err = float((a - b).abs().max())
+    assert err <= tol * scale, f"max error {err:.3e} > {tol * scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [100, 64, 4104])
+def test_embedding(dtype, hidden):
+    torch.manual_seed(0)
+    table = torch.randn(331, hidden).to(DT[dtype])
+    ids = torch.tensor([0, 330, 7, 7, 123], dtype=torch.int32)
+    st = status()
+    out = ops().embedding(ids.to(DEV), table.to(DEV), st)
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table.float()[ids.long()])
+    assert st.tolist() == [0, 0]
+    bad = torch.tensor([3, 331, 5, -1], dtype=torch.int32)
+    out = ops().embedding(bad.to(DEV), table.to(DEV), st).cpu()
+    code, where = st.tolist()
+    assert code == 1 and where in (1, 3)                 # recorded, not trapped
+    assert out[1].abs().sum() == 0 and out[3].abs().sum() == 0 and torch.equal(out[0], table.float()[3])
+
+
+@pytest.mark.parametrize("xd,dd,od", [("float32", None, "float32"), ("float32", "bfloat16", "bfloat16"),
+                                      ("float32", "float32", "bfloat16"), ("bfloat16", "bfloat16", "float32")])
+@pytest.mark.parametrize("hidden", [100, 48, 5120])
+def test_rmsnorm_with_residual_add_and_row_pick(xd, dd, od, hidden):
+    torch.manual_seed(1)
+    x = torch.randn(37, hidden).to(DT[xd])
+    delta = (torch.randn(37, hidden) * 0.5).to(DT[dd]) if dd else None
+    w = 1 + 0.1 * torch.randn(hidden)
+    eps = 3e-5
+    v = x.float() + (delta.float() if delta is not None else 0)
+    ref = pq.rms_norm(v, w, eps)
+    tol = 1e-6 if od == "float32" else 4e-3
+    xg = x.to(DEV)
+    out = ops().rmsnorm(xg, w.to(DEV), eps, DT[od], delta=delta.to(DEV) if delta is not None else None,
+                        write_sum=delta is not None)
+    close(out, ref, tol)
+    if delta is not None:                                 # the sum went back into x
+        close(xg, v, 1e-6 if xd == "float32" else 4e-3)
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32)
+    out = ops().rmsnorm(x.to(DEV), w.to(DEV), eps, DT[od], delta=delta.to(DEV) if delta is not None else None,
+                        rows=rows.to(DEV))
+    close(out, ref[rows.long()], tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inter", [100, 24, 3000])
+def test_silu_and_mul(dtype, inter):
+    torch.manual_seed(2)
+    gu = (torch.randn(19, 2 * inter) * 3).to(DT[dtype])
+    ref = pq.silu_and_mul(gu.float()[:, :inter], gu.float()[:, inter:])
+    close(ops().silu_and_mul(gu.to(DEV)), ref, 1e-6 if dtype == "float32" else 8e-3)
+
+
+def test_residual_add_and_scatter():
+    h = torch.randn(7, 33)
+    d = torch.randn(7, 33).to(torch.bfloat16)
+    hg = h.to(DEV)
+    ops().residual_add(hg, d.to(DEV))
+    assert torch.equal(hg.cpu(), h + d.float())
+    dst = torch.zeros(4, 5, dtype=torch.int32, device=DEV)
+    st = status()
+    idx = torch.tensor([0, 19, 7, 99, 3], dtype=torch.int32, device=DEV)
+    val = torch.tensor([11, 12, 13, 14, 15], dtype=torch.int32, device=DEV)
+    ops().scatter_int32(dst, idx, val, torch.tensor([4], dtype=torch.int32, device=DEV), 5, st)
+    flat = dst.flatten().tolist()
+    assert flat[0] == 11 and flat[19] == 12 and flat[7] == 13 and flat[3] == 0      # count 4: the fifth is not applied
+    assert st.tolist()[0] == 2                            # index 99 is outside: recorded and skipped
+
+
+def build_cache(k, v, page, table, num_pages, dtype):
+    """k, v [T, nkv, d] of ONE request laid into pages by `table` (logical -> physical)."""
+    T, nkv, d = k.shape
+    cache = torch.zeros(num_pages, 2, nkv, page, d)
+    cache += 77.0                                          # stale data everywhere: reads must be bounded
+    for t in range(T):
+        cache[table[t // page], 0, :, t % page] = k[t]
+        cache[table[t // page], 1, :, t % page] = v[t]
+    return cache.to(DT[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 4, 16, 4, 16), (6, 2, 48, 16, 48), (8, 1, 128, 8, 64),
+                                               (3, 3, 256, 32, 256), (2, 1, 80, 16, 40)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, rot):
+    torch.manual_seed(3)
+    T, theta, eps = 29, 50000.0, 1e-5
+    heads = nq + 2 * nkv
+    qkv = torch.randn(T, heads * d)
+    qw, kw = 1 + 0.2 * torch.randn(d), 1 + 0.2 * torch.randn(d)
+    # two requests: slot 2 holds positions 5.., slot 0 holds positions 40..
+    lens = [17, 12]
+    pos = torch.cat([torch.arange(5, 5 + 17), torch.arange(40, 40 + 12)]).to(torch.int32)
+    entry = torch.cat([torch.zeros(17), torch.ones(12)]).to(torch.int32)
+    slots = torch.tensor([2, 0], dtype=torch.int32)
+    num_pages, width = 40, 8
+    table = torch.full((3, width), -1, dtype=torch.int32)
+    perm = torch.randperm(num_pages)[:2 * width].to(torch.int32)
+    table[2], table[0] = perm[:width], perm[width:]
+    cache = torch.zeros(num_pages, 2, nkv, page, d, dtype=DT[dtype], device=DEV)
+    i = torch.arange(rot // 2, dtype=torch.float32)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float32).double(), (-(2.0 * i) / float(rot)).double()).float()
+    st = status()
+    q = ops().qk_norm_rope_kv_write(qkv.to(DEV), cache, pos.to(DEV), entry.to(DEV), slots.to(DEV), table.to(DEV),
+                                    qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot, nq, nkv, d, page, True, st,
+                                    q_dtype=DT[dtype])
+    assert st.tolist() == [0, 0]
+    x = qkv.view(T, heads, d)
+
+    def rope_part(t):                                      # rotate the first `rot` dims, pass the rest
+        r = pq.rope(t[..., :rot].contiguous(), pos, theta) if rot == d else \
+            torch.cat([_rope_custom(t[..., :rot], pos, inv), t[..., rot:]], dim=-1)
+        return r
+    qr = rope_part(pq.rms_norm(x[:, :nq], qw, eps))
+    kr = rope_part(pq.rms_norm(x[:, nq:nq + nkv], kw, eps))
+    vr = x[:, nq + nkv:]
+    tol = 2e-6 if dtype == "float32" else 8e-3
+    close(q.view(T, nq, d), qr, tol)
+    c = cache.float().cpu()
+    for t in range(T):
+        p, s = int(pos[t]), int(slots[entry[t]])
+        pg = int(table[s, p // page])
+        close(c[pg, 0, :, p % page], kr[t], tol)
+        close(c[pg, 1, :, p % page], vr[t], tol)
+    touched = {(int(table[int(slots[entry[t]]), int(pos[t]) // page]), int(pos[t]) % page) for t in range(T)}
+    for pg in range(num_pages):
+        for r in range(page):
+            if (pg, r) not in touched:
+                assert c[pg, :, :, r].abs().sum() == 0, "a row nobody owns was written"
+
+
+def _rope_custom(x, pos, inv):
+    half = x.shape[-1] // 2
+    ang = pos.float()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+
+
+def test_qk_write_refuses_a_bad_page_without_trapping():
+    nq = nkv = 1
+    d, page = 16, 4
+    cache = torch.zeros(2, 2, nkv, page, d, device=DEV)
+    table = torch.tensor([[0, 9]], dtype=torch.int32, device=DEV)      # page 9 does not exist
+    st = status()
+    z = lambda *a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    ops().qk_norm_rope_kv_write(torch.randn(2, 3 * d, device=DEV), cache, z(3, 4), z(0, 0), z(0), table, None, None,
+                                0.0, None, 0, nq, nkv, d, page, True, st)
+    assert st.tolist() == [3, 1] and cache[1].abs().sum() == 0
+
+
+def attention_case(dtype, nq, nkv, d, page, lens, window=None, spike=None, q_rows=None, seed=0):
+    """Requests of the given lengths in shuffled pages; queries at `q_rows` (default: all
+    positions).  `spike` = (request, key position): that key is made to dominate its row, so a
+    wrong page or row shows as a different value vector, not as a small shift of a mean."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    width = max((n + page - 1) // page for n in lens)
+    num_pages = B * width + 3
+    perm = torch.randperm(num_pages, generator=g).to(torch.int32)
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    caches, qs, refs, pos_l, ent_l = [], [], [], [], []
+    cache = torch.zeros(num_pages, 2, nkv, page, d) + 55.0
+    for b, n in enumerate(lens):
+        table[b, :width] = perm[b * width:(b + 1) * width]
+        q = torch.randn(n, nq, d, generator=g)
+        k = torch.randn(n, nkv, d, generator=g)
+        v = torch.randn(n, nkv, d, generator=g)
+        if spike is not None and spike[0] == b:
+            j = spike[1]
+            k[j] = 0.0
+            k[j, :, 0] = 6.0
+            q[:, :, 0] = 6.0 * math.sqrt(d) / 6.0 * 3.0          # score of key j: 18, far above the rest
+            v[j] = torch.arange(d, dtype=torch.float32)[None, :] + 100.0
+        rows = list(range(n)) if q_rows is None else [r for r in q_rows[b]]
+        for t in range(n):
+            cache[table[b, t // page], 0, :, t % page] = k[t]
+            cache[table[b, t // page], 1, :, t % page] = v[t]
+        kk, vv = (k.to(DT[dtype]).float(), v.to(DT[dtype]).float())
+        qq = q.to(DT[dtype]).float()
+        full = pq.causal_attention(qq.double(), kk.double(), vv.double(), window=window)
+        qs.append(qq[rows])
+        refs.append(full[rows])
+        pos_l += rows
+        ent_l += [b] * len(rows)
+    q_all = torch.cat(qs).reshape(-1, nq * d).to(DT[dtype])
+    out = ops().paged_attention_generic(
+        q_all.to(DEV), cache.to(DT[dtype]).to(DEV), torch.tensor(pos_l, dtype=torch.int32, device=DEV),
+        torch.tensor(ent_l, dtype=torch.int32, device=DEV), torch.arange(B, dtype=torch.int32, device=DEV),
+        table.to(DEV), nq, nkv, d, page, window, 1.0 / math.sqrt(d), status())
+    return out.view(-1, nq, d), torch.cat(refs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 4, 16, 4), (6, 2, 48, 16), (8, 1, 128, 16), (3, 3, 256, 8),
+                                           (5, 5, 80, 64), (16, 2, 64, 1)])
+def test_paged_attention_sizes(dtype, nq, nkv, d, page):
+    out, ref = attention_case(dtype, nq, nkv, d, page, lens=[1, 37, 130])
+    close(out, ref, 3e-6 if dtype == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", [0, 15, 16, 17, 31, 32, 255, 256, 300, 479])
+def test_a_far_key_among_hundreds_is_found(dtype, key):
+    """One key dominates; its value vector is unmistakable.  Keys at page edges (page 16),
+    at tile edges (32), the first and the last."""
+    n = 480
+    out, ref = attention_case(dtype, 6, 2, 32, 16, lens=[40, n], spike=(1, key),
+                              q_rows=[[39], [n - 1, max(key, 1)]], seed=key)
+    close(out, ref, 3e-6 if dtype == "float32" else 1e-2)
+    assert float(out[1].float().mean()) > 90.0           # the spiked value really carried the row
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 33, 200])
+def test_window_edges(dtype, window):
+    """The key just inside the window counts, the one just outside does not: spike each."""
+    n = 230
+    for inside in (True, False):
+        qpos = n - 1
+        key = qpos - window + 1 if inside else qpos - window
+        if key < 0:
+            continue
+        out, ref = attention_case(dtype, 4, 2, 32, 16, lens=[n], window=window, spike=(0, key),
+                                  q_rows=[[qpos, window // 2]], seed=window)
+        close(out, ref, 3e-6 if dtype == "float32" else 1e-2)
+        assert (float(out[0].float().mean()) > 90.0) == inside
+
+
+def test_attention_refuses_sizes_it_was_not_written_for():
+    from litellmengine_b200.csrc.ops import KernelError
+    z = lambda *a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    for nq, nkv, d in ((4, 3, 32), (2, 1, 24), (2, 1, 272)):
+        with pytest.raises(KernelError, match="refused"):
+            ops().paged_attention_generic(torch.zeros(1, nq * d, device=DEV), torch.zeros(1, 2, nkv, 4, d, device=DEV),
+                                          z(0), z(0), z(0), z(0).view(1, 1), nq, nkv, d, 4, None, 1.0, status())
+    with pytest.raises(KernelError, match="CUDA device"):
+        ops().silu_and_mul(torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("vocab", [331, 1000, 151936])
+def test_argmax_rows_ties_go_low(vocab):
+    torch.manual_seed(5)
+    lg = torch.randn(6, vocab)
+    lg[1, 17] = lg[1, vocab - 1] = 9.0                    # tie: lowest index wins
+    lg[2, :] = 0.5
+    lg[3, vocab - 1] = 12.0
+    got = ops().argmax_rows(lg.to(DEV)).tolist()
+    assert got == [pq.argmax_token(r) for r in lg] and got[1] == 17 and got[2] == 0 and got[3] == vocab - 1
+
+
+@pytest.mark.parametrize("vocab", [331, 50021])
+def test_sample_rows_follow_their_own_streams(vocab):
+    from litellmengine_b200.sampling import slot_state_row
+    torch.manual_seed(6)
+    lg = torch.randn(5, vocab) * 2
+    temps = [0.8, 0.0, 1.5, 0.8, 0.3]
+    seeds = [11, 12, 13, 11, 2**40 + 5]
+    state = torch.tensor([slot_state_row(s, 0, t) for s, t in zip(seeds, temps)] + [[0, 0, 0, 0]] * 3, dtype=torch.int32)
+    row_slot = torch.tensor([0, 1, 2, 3, 4], dtype=torch.int32)
+    sd = state.to(DEV)
+    draws = []
+    for step in range(6):
+        tok = ops().sample_rows(lg.to(DEV), row_slot.to(DEV), sd).tolist()
+        draws.append(tok)
+        for r, t in enumerate(tok):
+            if temps[r] == 0.0:
+                assert t == pq.argmax_token(lg[r])
+                continue
+            u = ops().sampler_uniform(seeds[r], step)
+            p = pq.temperature_probs(lg[r], temps[r]).double()
+            cdf = torch.cumsum(p, 0)
+            lo = float(cdf[t - 1]) if t > 0 else 0.0
+            assert lo - 1e-5 <= u <= float(cdf[t]) + 1e-5, f"row {r} step {step}: u={u} not in token {t}'s interval"
+    assert sd[:, 2].tolist()[:5] == [6, 0, 6, 6, 6]       # sampled rows advanced their counters
+    assert len({tuple(d) for d in draws}) > 1             # the stream moves
+    # same logits and same seed give the same draws: rows 0 and 3
+    lg2 = lg.clone()
+    lg2[3] = lg2[0]
+    sd = state.to(DEV)
+    for _ in range(4):
+        tok = ops().sample_rows(lg2.to(DEV), row_slot.to(DEV), sd).tolist()
+        assert tok[0] == tok[3]
+    us = [ops().sampler_uniform(7, c) for c in range(2000)]
+    assert 0.0 <= min(us) and max(us) < 1.0 and abs(np.mean(us) - 0.5) < 0.03
