@@ -58,7 +58,8 @@ __global__ void paged_attention_generic_kernel(
         long long koff = -1;
         float s = -CUDART_INF_F;
         if (valid) {
-            const int page = table[j / page_size];
+            const int logical = j / page_size;
+            const int page = logical < table_stride ? table[logical] : -1;
             if (page < 0 || page >= num_pages) {
                 if (atomicCAS(status, 0, 4) == 0) status[1] = t;
             } else {

@@ -74,7 +74,9 @@ __global__ void qk_norm_rope_kv_write_kernel(
     }
     const int kv_head = is_k ? head - nq : head - nq - nkv;
     const int slot = entry_slot[token_entry[t]];
-    const int page = block_table[static_cast<size_t>(slot) * table_stride + pos / page_size];
+    const int logical = pos / page_size;
+    const int page = (pos >= 0 && logical < table_stride)
+                         ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
     if (page < 0 || page >= num_pages) {
         if (lane == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
         return;

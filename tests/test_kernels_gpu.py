@@ -122,7 +122,8 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, rot):
     pos = torch.cat([torch.arange(5, 5 + 17), torch.arange(40, 40 + 12)]).to(torch.int32)
     entry = torch.cat([torch.zeros(17), torch.ones(12)]).to(torch.int32)
     slots = torch.tensor([2, 0], dtype=torch.int32)
-    num_pages, width = 40, 8
+    width = (52 + page - 1) // page + 1
+    num_pages = 2 * width + 5
     table = torch.full((3, width), -1, dtype=torch.int32)
     perm = torch.randperm(num_pages)[:2 * width].to(torch.int32)
     table[2], table[0] = perm[:width], perm[width:]
