@@ -103,22 +103,32 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return out
 
 
-def attention_block(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
-                    prefix: str, cfg: dict, window: Optional[int] = None, act=identity) -> torch.Tensor:
-    """q/k/v projections without bias, per-head RMSNorm of q and k with one [d]
-    weight each (same eps), rotation, attention, output projection.
-    src/model/qwen3.cpp:357-449,550-567"""
+def attention_qkv(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict,
+                  act=identity, with_kv: bool = True):
+    """q/k/v projections without bias, per-head RMSNorm of q and k with one [d] weight each
+    (same eps), rotation of q and k; v stays as projected.  src/model/qwen3.cpp:357-449"""
     T = x.shape[0]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     q = (x @ w[f"{prefix}.q_proj.weight"].T).view(T, nq, d)
+    q = act(rope(rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["rms_norm_eps"]), positions, cfg["rope_theta"]))
+    if not with_kv:
+        return q, None, None
     k = (x @ w[f"{prefix}.k_proj.weight"].T).view(T, nkv, d)
     v = (x @ w[f"{prefix}.v_proj.weight"].T).view(T, nkv, d)
-    q = rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["rms_norm_eps"])
-    k = rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["rms_norm_eps"])
-    q = act(rope(q, positions, cfg["rope_theta"]))
-    k = act(rope(k, positions, cfg["rope_theta"]))
-    a = act(causal_attention(q, k, act(v), window=window))
-    return a.reshape(T, nq * d) @ w[f"{prefix}.o_proj.weight"].T
+    k = act(rope(rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["rms_norm_eps"]), positions, cfg["rope_theta"]))
+    return q, k, act(v)
+
+
+def attention_block(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
+                    prefix: str, cfg: dict, window: Optional[int] = None, act=identity, kv=None) -> torch.Tensor:
+    """Attention over this layer's own keys and values, or over `kv` = (k, v) of another layer
+    when given; then the output projection.  src/model/qwen3.cpp:550-567"""
+    T = x.shape[0]
+    q, k, v = attention_qkv(x, positions, w, prefix, cfg, act, with_kv=kv is None)
+    if kv is not None:
+        k, v = kv
+    a = act(causal_attention(q, k, v, window=window))
+    return a.reshape(T, -1) @ w[f"{prefix}.o_proj.weight"].T
 
 
 def silu_and_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
