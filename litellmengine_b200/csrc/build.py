@@ -30,6 +30,8 @@ FAMILIES: Dict[str, List[str]] = {
     "activation": ["activation.cu"],
     "rope_cache": ["rope_cache.cu"],
     "attention_generic": ["attention_generic.cu"],
+    "attention_decode": ["attention_decode.cu"],
+    "attention_prefill": ["attention_prefill.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh"]

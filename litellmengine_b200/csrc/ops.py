@@ -228,6 +228,77 @@ def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, positions, tok
     return out
 
 
+def fast_attention_supported(d: int, group: int) -> bool:
+    """Whether the tuned bfloat16 kernels (tensor-core prefill, split-key decode) take this shape."""
+    a = _fn("attention_decode", "llm_paged_decode_supported", [c_int, c_int])
+    b = _fn("attention_prefill", "llm_paged_prefill_supported", [c_int])
+    return bool(a(d, group)) and bool(b(d))
+
+
+PREFILL_TILE_ROWS = 64
+_scratch: Dict[str, torch.Tensor] = {}
+
+
+def decode_scratch(device, floats: int) -> Optional[torch.Tensor]:
+    """The float32 scratch the split-key decode kernel merges through; grown on demand and kept."""
+    if floats <= 0:
+        return None
+    key = str(device)
+    t = _scratch.get(key)
+    if t is None or t.numel() < floats:
+        t = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[key] = t
+    return t
+
+
+def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, rows: Optional[torch.Tensor],
+                           n_rows: int, positions, token_entry, entry_slot, block_table: torch.Tensor, nq: int,
+                           nkv: int, d: int, page_size: int, window: Optional[int], scale: float, num_splits: int,
+                           status: torch.Tensor) -> torch.Tensor:
+    """Attention for single decoded tokens (rows of q named by `rows`, or rows 0..n_rows-1), written
+    into the same rows of `out`.  bfloat16 only."""
+    _dev(q, out, cache, rows, positions, token_entry, entry_slot, block_table, status)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the decode attention kernel is bfloat16 only")
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    need = _fn("attention_decode", "llm_paged_decode_scratch_floats", [c_int, c_int, c_int, c_int],
+               restype=c_longlong)(n_rows, nq, d, num_splits)
+    scratch = decode_scratch(q.device, int(need))
+    f = _fn("attention_decode", "llm_paged_attention_decode",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(rows), n_rows, _ptr(positions), _ptr(token_entry),
+             _ptr(entry_slot), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
+             int(window) if window else 0, float(scale), cache.shape[0], num_splits, _ptr(scratch), _ptr(status),
+             _stream()), "paged_attention_decode")
+    if num_splits > 1:
+        global launch_count
+        launch_count += 1                         # the merge kernel
+    return out
+
+
+def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor,
+                            n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                            block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                            window: Optional[int], scale: float, status: torch.Tensor) -> torch.Tensor:
+    """Attention for prompt portions: `tiles` int32 [n_tiles, 2] = (entry, first row of a 64-row
+    tile inside the entry).  bfloat16 only."""
+    _dev(q, out, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the prefill attention kernel is bfloat16 only")
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    f = _fn("attention_prefill", "llm_paged_attention_prefill",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
+             _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d,
+             page_size, int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _stream()),
+           "paged_attention_prefill")
+    return out
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(logits, out)
     if logits.dtype != torch.float32 or logits.dim() != 2:

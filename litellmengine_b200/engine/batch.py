@@ -15,6 +15,9 @@ import numpy as np
 import torch
 
 
+PREFILL_TILE_ROWS = 64          # query rows per tile of the tensor-core prefill attention kernel
+
+
 @dataclass
 class StepEntry:
     """One request's share of a step: its slot, the tokens to run now (they follow what the
@@ -36,7 +39,8 @@ class StepBuffers:
         self.off = {}
         for name, n in (("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
                         ("entry_q_start", B), ("entry_q_len", B), ("entry_kv_len", B), ("want_rows", T),
-                        ("want_slot", T), ("counts", 8 + num_groups)):
+                        ("want_slot", T), ("decode_rows", T), ("prefill_tiles", 2 * (T // PREFILL_TILE_ROWS + B + 1)),
+                        ("counts", 8 + num_groups)):
             self.off[name] = (off, n)
             off += n
         for g in range(num_groups):
@@ -84,12 +88,16 @@ class StepBatch:
     entry_kv_len: torch.Tensor       # int32 [B] cached length after this step
     want_rows: torch.Tensor          # int32 [W] rows whose logits are wanted
     want_slot: torch.Tensor          # int32 [W] slot of each wanted row
+    decode_rows: torch.Tensor        # int32 [n_decode] rows of entries that bring a single token
+    prefill_tiles: torch.Tensor      # int32 [n_tiles, 2] (entry, first row inside it) of entries that bring more
     status: torch.Tensor             # int32 [2]
     num_tokens: int
     num_entries: int
     num_want: int
     max_q_len: int
     max_kv_len: int
+    num_decode: int = 0
+    num_prefill_tiles: int = 0
     entries: List[StepEntry] = field(default_factory=list)
 
 
@@ -106,6 +114,8 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
     tok, pos, ent = hv("token_ids"), hv("positions"), hv("token_entry")
     slot, qs, ql, kl = hv("entry_slot"), hv("entry_q_start"), hv("entry_q_len"), hv("entry_kv_len")
     wr, ws = hv("want_rows"), hv("want_slot")
+    dec, tiles = hv("decode_rows"), hv("prefill_tiles")
+    n_dec = n_tiles = 0
     row = w = 0
     max_q = max_kv = 0
     for i, e in enumerate(entries):
@@ -119,10 +129,17 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
                 raise ValueError(f"want={j} is outside the entry's {n} tokens")
             wr[w], ws[w] = row + j, e.slot
             w += 1
+        if n == 1:
+            dec[n_dec] = row
+            n_dec += 1
+        else:
+            for q0 in range(0, n, PREFILL_TILE_ROWS):
+                tiles[2 * n_tiles], tiles[2 * n_tiles + 1] = i, q0
+                n_tiles += 1
         max_q, max_kv = max(max_q, n), max(max_kv, e.past + n)
         row += n
     counts = hv("counts")
-    counts[0], counts[1], counts[2] = T, B, w
+    counts[0], counts[1], counts[2], counts[3], counts[4] = T, B, w, n_dec, n_tiles
     for g, (idx, val) in enumerate(updates):
         if len(idx) > buffers.max_updates:
             raise ValueError("more block-table changes than the step buffer holds")
@@ -135,5 +152,6 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
         token_ids=dv("token_ids", T), positions=dv("positions", T), token_entry=dv("token_entry", T),
         entry_slot=dv("entry_slot", B), entry_q_start=dv("entry_q_start", B), entry_q_len=dv("entry_q_len", B),
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
-        status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
+        decode_rows=dv("decode_rows", n_dec), prefill_tiles=dv("prefill_tiles", 2 * n_tiles).view(n_tiles, 2),
+        num_decode=n_dec, num_prefill_tiles=n_tiles, status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
         entries=entries)

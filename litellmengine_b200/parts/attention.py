@@ -94,8 +94,25 @@ class AttentionMixer:
 
 def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,
                          window: Optional[int], scale: float) -> torch.Tensor:
-    """Pick the attention kernel for this batch.  Every choice reads the same pages and gives
-    the same result up to rounding."""
+    """Pick the attention kernels for this batch.  Every choice reads the same pages and gives
+    the same result up to rounding.  bfloat16 with a head size and group the tuned kernels
+    take: single tokens go to the split-key decode kernel, longer portions to the tensor-core
+    prefill kernel (a mixed batch launches both, each over its own rows).  Everything else,
+    float32 included, goes through the generic kernel."""
     b = ctx.batch
-    return ops.paged_attention_generic(q, ctx.cache, b.positions, b.token_entry, b.entry_slot,
+    cache = ctx.cache
+    if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and ops.fast_attention_supported(d, nq // nkv)):
+        out = torch.empty_like(q)
+        if b.num_decode:
+            work = b.num_decode * nkv
+            splits = max(1, min(16, -(-444 // work), -(-b.max_kv_len // 256)))
+            ops.paged_attention_decode(q, out, cache, None if b.num_decode == b.num_tokens else b.decode_rows,
+                                       b.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
+                                       nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
+        if b.num_prefill_tiles:
+            ops.paged_attention_prefill(q, out, cache, b.prefill_tiles, b.num_prefill_tiles, b.entry_slot,
+                                        b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv,
+                                        d, ctx.page_size, window, scale, ctx.status)
+        return out
+    return ops.paged_attention_generic(q, cache, b.positions, b.token_entry, b.entry_slot,
                                        ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

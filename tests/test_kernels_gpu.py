@@ -313,3 +313,128 @@ def test_sample_rows_follow_their_own_streams(vocab):
         assert tok[0] == tok[3]
     us = [ops().sampler_uniform(7, c) for c in range(2000)]
     assert 0.0 <= min(us) and max(us) < 1.0 and abs(np.mean(us) - 0.5) < 0.03
+
+
+# ---- the tuned bfloat16 attention kernels ------------------------------------------------------
+def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1, seed=0):
+    """reqs: [(keys in the cache after the step, queries at the end)].  Runs `kernel` ('decode' or
+    'prefill') over all queries and returns (out, reference) for the query rows."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(reqs)
+    width = max((n + page - 1) // page for n, _ in reqs) + 1
+    num_pages = B * width + 2
+    perm = torch.randperm(num_pages, generator=g).to(torch.int32)
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    cache = torch.zeros(num_pages, 2, nkv, page, d) + 33.0
+    qs, refs, pos_l, ent_l, q_start, q_len, kv_len, tiles, dec_rows = [], [], [], [], [], [], [], [], []
+    row = 0
+    for b, (n, nqr) in enumerate(reqs):
+        table[b] = perm[b * width:(b + 1) * width]
+        q = torch.randn(n, nq, d, generator=g)
+        k = torch.randn(n, nkv, d, generator=g)
+        v = torch.randn(n, nkv, d, generator=g)
+        if spike is not None and spike[0] == b:
+            j = spike[1]
+            k[j] = 0.0
+            k[j, :, 0] = 6.0
+            q[:, :, 0] = 3.0 * math.sqrt(d)
+            v[j] = torch.arange(d, dtype=torch.float32)[None, :] + 100.0
+        q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
+        for t in range(n):
+            cache[table[b, t // page], 0, :, t % page] = k[t]
+            cache[table[b, t // page], 1, :, t % page] = v[t]
+        full = pq.causal_attention(q.double(), k.double(), v.double(), window=window)
+        qs.append(q[n - nqr:])
+        refs.append(full[n - nqr:])
+        pos_l += list(range(n - nqr, n))
+        ent_l += [b] * nqr
+        q_start.append(row)
+        q_len.append(nqr)
+        kv_len.append(n)
+        if nqr == 1:
+            dec_rows.append(row)
+        for q0 in range(0, nqr, 64):
+            tiles += [b, q0]
+        row += nqr
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    q_all = torch.cat(qs).reshape(-1, nq * d).to(torch.bfloat16).to(DEV)
+    out = torch.zeros_like(q_all)
+    st = status()
+    cache = cache.to(torch.bfloat16).to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    if kernel == "decode":
+        rows = None if len(dec_rows) == row else i32(dec_rows)
+        ops().paged_attention_decode(q_all, out, cache, rows, len(dec_rows), i32(pos_l), i32(ent_l),
+                                     i32(list(range(B))), table.to(DEV), nq, nkv, d, page, window, scale, splits, st)
+    else:
+        ops().paged_attention_prefill(q_all, out, cache, i32(tiles).view(-1, 2), len(tiles) // 2, i32(list(range(B))),
+                                      i32(q_start), i32(q_len), i32(kv_len), table.to(DEV), nq, nkv, d, page, window,
+                                      scale, st)
+    assert st.tolist() == [0, 0]
+    return out.view(-1, nq, d), torch.cat(refs)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 16), (7, 1, 64, 8), (16, 2, 128, 64),
+                                           (6, 2, 128, 4), (5, 1, 64, 16)])
+def test_decode_attention_kernel(nq, nkv, d, page, splits):
+    out, ref = fast_case("decode", nq, nkv, d, page, [(1, 1), (37, 1), (300, 1), (513, 1), (64, 1)], splits=splits)
+    close(out, ref, 1e-2)
+
+
+@pytest.mark.parametrize("key", [0, 15, 16, 31, 32, 127, 128, 255, 256, 511, 600, 639])
+def test_decode_kernel_finds_a_far_key(key):
+    out, ref = fast_case("decode", 8, 2, 128, 16, [(50, 1), (640, 1)], spike=(1, key), splits=5, seed=key)
+    close(out, ref, 1e-2)
+    assert float(out[1].float().mean()) > 90.0
+
+
+@pytest.mark.parametrize("window", [1, 16, 33, 200])
+def test_decode_kernel_window_edges(window):
+    n = 300
+    for inside in (True, False):
+        key = n - 1 - window + 1 if inside else n - 1 - window
+        out, ref = fast_case("decode", 4, 2, 64, 16, [(n, 1)], window=window, spike=(0, key), splits=3, seed=window)
+        close(out, ref, 1e-2)
+        assert (float(out[0].float().mean()) > 90.0) == inside
+
+
+def test_decode_kernel_on_a_subset_of_rows():
+    """A mixed batch: only the single-token entries go to the decode kernel; other rows of the
+    output are left alone."""
+    out, ref = fast_case("decode", 8, 2, 128, 16, [(40, 7), (99, 1), (64, 3), (130, 1)], splits=2)
+    rows = [7, 11]
+    close(out[rows], ref[rows], 1e-2)
+    rest = [i for i in range(12) if i not in rows]
+    assert out[rest].abs().sum() == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (6, 6, 64, 16), (3, 1, 64, 8), (4, 2, 128, 64), (6, 2, 128, 4)])
+def test_prefill_attention_kernel(nq, nkv, d, page):
+    reqs = [(2, 2), (64, 64), (65, 65), (130, 130), (200, 7), (333, 129), (128, 64), (70, 2)]
+    out, ref = fast_case("prefill", nq, nkv, d, page, reqs)
+    close(out, ref, 1e-2)
+
+
+@pytest.mark.parametrize("key", [0, 15, 16, 63, 64, 65, 127, 128, 300, 383, 384, 400, 449])
+def test_prefill_kernel_finds_a_far_key(key):
+    """The portion is the last 66 positions of 450; the spiked key lies before it, at its first
+    position, inside it, at tile and page edges.  Queries before the key must not see it."""
+    n, nqr = 450, 66
+    out, ref = fast_case("prefill", 4, 2, 128, 16, [(30, 30), (n, nqr)], spike=(1, key), seed=key)
+    close(out, ref, 1e-2)
+    first_q = n - nqr
+    means = out[30:].float().mean(dim=(1, 2))
+    for i in range(nqr):
+        assert (float(means[i]) > 90.0) == (first_q + i >= key)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 100])
+def test_prefill_kernel_window_edges(window):
+    n, nqr = 300, 150
+    for inside in (True, False):
+        qpos = n - 1
+        key = qpos - window + 1 if inside else qpos - window
+        out, ref = fast_case("prefill", 4, 2, 64, 16, [(n, nqr)], window=window, spike=(0, key), seed=window)
+        close(out, ref, 1e-2)
+        assert (float(out[-1].float().mean()) > 90.0) == inside
