@@ -14,8 +14,10 @@ MODELS = {
     "A": (tm.TINY_A, tm.TINY_A_SEED, tm.TINY_A_PAGE),
     "B": (tm.TINY_B, tm.TINY_B_SEED, tm.TINY_B_PAGE),
     "C": (tm.TINY_C, tm.TINY_C_SEED, tm.TINY_C_PAGE),
+    "D": (tm.TINY_D, tm.TINY_D_SEED, tm.TINY_D_PAGE),
 }
-LENGTHS = {"A": [5, 9, 13, 40, 77], "B": [1, 7, 16, 33, 70, 121], "C": [64, 97, 150, 333]}
+LENGTHS = {"A": [5, 9, 13, 40, 77], "B": [1, 7, 16, 33, 70, 121], "C": [64, 97, 150, 333],
+           "D": [2, 63, 64, 65, 129, 200, 333, 700]}
 
 
 def setup(name, dtype, sharp=True):
@@ -29,7 +31,7 @@ def setup(name, dtype, sharp=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
     cfg, page, w, reqs = setup(name, dtype)
     ref = rh.plain_rows(cfg, w, reqs, dtype)
@@ -56,7 +58,7 @@ def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
         rh.assert_rows_match(results[what], whole, cut_tol, f"{name} {dtype} {what} against whole")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_bfloat16_against_the_plain_float32_code(name):
     """Unsharpened N(0, 0.02) weights, bfloat16 run, plain code in float32 without any rounding."""
     cfg, page, w, reqs = setup(name, "bfloat16", sharp=False)
@@ -81,7 +83,7 @@ def test_other_page_sizes(page, dtype):
 def test_long_decoding(dtype):
     """Three tokens of prompt, then 400 tokens one by one: every page edge is crossed by a
     single-token step, and the first tokens of the sequence are decoded too."""
-    cfg, page, w, _ = setup("C", dtype)
+    cfg, page, w, _ = setup("D" if dtype == "bfloat16" else "C", dtype)
     toks = tm.random_tokens(cfg, 403, 77)
     ref = rh.plain_rows(cfg, w, {"x": toks}, dtype)
     steps = rh.trace_tail_decode({"x": toks}, tail=400)

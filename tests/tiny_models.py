@@ -42,6 +42,17 @@ TINY_C = dict(
 TINY_C_PAGE, TINY_C_SEED = 16, 7
 
 
+# Head size 64, which the tuned bfloat16 attention kernels take (the others run the generic one).
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=96, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=64, intermediate_size=160, vocab_size=211, rope_theta=1000000.0,
+    rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=True,
+    torch_dtype="bfloat16",
+)
+TINY_D_PAGE, TINY_D_SEED = 16, 11
+
+
 def tensor_shapes(cfg: dict) -> dict:
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
