@@ -237,16 +237,20 @@ def fast_attention_supported(d: int, group: int) -> bool:
 
 PREFILL_TILE_ROWS = 64
 _scratch: Dict[str, torch.Tensor] = {}
+_scratch_retired = []          # outgrown buffers stay alive: a captured graph may still point at them
 
 
 def decode_scratch(device, floats: int) -> Optional[torch.Tensor]:
-    """The float32 scratch the split-key decode kernel merges through; grown on demand and kept."""
+    """The float32 scratch the split-key decode kernel merges through; grown on demand, never
+    freed (launches on one stream are ordered, so one buffer per device serves them all)."""
     if floats <= 0:
         return None
     key = str(device)
     t = _scratch.get(key)
     if t is None or t.numel() < floats:
-        t = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        if t is not None:
+            _scratch_retired.append(t)
+        t = torch.empty(max(2 * floats, 1 << 22), dtype=torch.float32, device=device)
         _scratch[key] = t
     return t
 

@@ -89,7 +89,7 @@ class PagedGenerateEngine:
             if p.samples:
                 samplers.append(req)
         batch = self.runner.prepare(entries)
-        logits = self.runner.model.forward(batch, self.runner.cache)
+        logits = self.runner.forward(batch)
         self.runner.finish(batch)
         tokens: List[int] = []
         if samplers:

@@ -32,7 +32,7 @@ class ModelRunner:
 
     def __init__(self, model: Model, page_size: int = 16, max_total_tokens: int = 4096,
                  max_requests: int = 64, max_tokens_per_step: int = 8192,
-                 max_request_tokens: Optional[int] = None):
+                 max_request_tokens: Optional[int] = None, use_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: the engine has no CPU path")
         ops.configure_library_products()
@@ -46,6 +46,16 @@ class ModelRunner:
             extra_state={"sampler": StateNeed((4,), "int32")})
         self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device)
         self.steps_run = 0
+        # CUDA graphs for steps made only of single decoded tokens: one graph per batch size,
+        # captured the second time that size is seen.  Only for models whose parts all say
+        # they launch nothing but kernels on the current stream (no host reads, no host loops).
+        self.use_graphs = use_graphs and all(
+            getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
+            for b in model.blocks)
+        self._graphs = {}
+        self._graph_seen = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ---- construction ----------------------------------------------------------------------
     @classmethod
@@ -116,11 +126,50 @@ class ModelRunner:
             self.cache.commit(e.slot, e.past + len(e.tokens))
         self.steps_run += 1
 
+    def forward(self, batch: StepBatch) -> torch.Tensor:
+        """The device half of a step.  A step of B single decoded tokens that wants all B logits
+        replays a captured CUDA graph of the same kernels; everything else launches them one by
+        one.  A graph's logits tensor is reused by the next replay of that batch size: read it
+        (sample, copy) before stepping again."""
+        B = batch.num_tokens
+        if self.use_graphs and batch.num_decode == B and batch.num_want == B:
+            g = self._graphs.get(B)
+            if g is None:
+                seen = self._graph_seen.get(B, 0)
+                self._graph_seen[B] = seen + 1
+                if seen >= 1:
+                    g = self._capture(batch)
+            if g is not None:
+                g[0].replay()
+                self.graph_replays += 1
+                return g[1]
+        return self.model.forward(batch, self.cache)
+
+    def _capture(self, batch: StepBatch):
+        B = batch.num_tokens
+        real_max_kv = batch.max_kv_len
+        batch.max_kv_len = 1 << 30              # kernel choices inside a graph must not depend on lengths
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):           # warm every kernel and library handle outside capture
+            self.model.forward(batch, self.cache)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch, self.cache)
+        batch.max_kv_len = real_max_kv
+        self._graphs[B] = (graph, logits)
+        return self._graphs[B]
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; returns float32 [wanted, vocab] in the order of
         the entries and of each entry's `want`."""
         batch = self.prepare(entries)
-        logits = self.model.forward(batch, self.cache)
+        logits = self.forward(batch)
         self.finish(batch)
         return logits
 

@@ -22,6 +22,8 @@ class AttentionMixer:
     kv_heads); scores are scaled by 1/sqrt(head_dim) unless the spec gives a scale
     (src/ops/attention.cu:204-207)."""
 
+    graph_safe = True          # forward only launches kernels on the current stream
+
     def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
             raise ValueError("attention heads must be a positive multiple of kv heads")

@@ -16,6 +16,8 @@ class SwiGLU:
     """down(silu(gate(x)) * up(x)), no biases (src/model/qwen3.cpp:143-152,
     src/ops/silu_and_mul.cu:44-46).  Gate and up are one fused product [g | u]."""
 
+    graph_safe = True          # forward only launches kernels on the current stream
+
     def __init__(self, spec: FeedForwardSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.intermediate_size <= 0:
             raise ValueError("intermediate_size must be positive")

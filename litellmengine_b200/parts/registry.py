@@ -21,6 +21,10 @@ changes.  The interfaces:
                  parameters(), load(tensors)
                  forward(x [T, hidden]) -> [T, hidden]
   arrangement    a function (block, h, delta, ctx) -> (h, delta) wiring a layer's parts
+
+A mixer or feed-forward whose forward only launches kernels on the current stream (no host
+reads, no loops over host data) may set the class attribute `graph_safe = True`; decode steps
+of a model whose parts all do are replayed as CUDA graphs.
 """
 from __future__ import annotations
 

@@ -65,7 +65,7 @@ def test_bfloat16_against_the_plain_float32_code(name):
     ref = rh.plain_rows(cfg, w, reqs, "float32")
     for steps in (rh.trace_whole(reqs), rh.trace_mixed(reqs, seed=8, max_live=4)):
         runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=rh.peak_tokens(steps, page),
-                                max_tokens_per_step=512)
+                                max_tokens_per_step=1024)
         rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.BF16_VS_FP32_TOL, f"{name} bf16 vs fp32 plain")
 
 
@@ -137,3 +137,29 @@ def test_step_refuses_bad_input_without_launching():
     runner.release(s)
     runner.check_status()
     runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_replayed_as_graphs_match_kernel_by_kernel_launches(dtype):
+    """Steps made only of single decoded tokens are replayed as CUDA graphs from the third step of
+    a batch size on.  Same trace with graphs off: same logits up to rounding (a graph fixes the
+    number of key splits once, the plain launches choose it per step)."""
+    cfg, page, w, _ = setup("D", dtype)
+    reqs = rh.requests_for(cfg, [90, 41, 140], 5)
+    ref = rh.plain_rows(cfg, w, reqs, dtype)
+    steps = rh.trace_mixed(reqs, seed=4, max_live=3, prompt_frac=0.2)
+    got = {}
+    for graphs in (True, False):
+        from litellmengine_b200.config import config_from_dict
+        from litellmengine_b200.engine import ModelRunner
+        from litellmengine_b200.weights import DictSource
+        store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        runner = ModelRunner.from_config(
+            config_from_dict(cfg), dtype=dtype, device="cuda:0", page_size=page, max_total_tokens=512,
+            max_requests=4, max_tokens_per_step=256, use_graphs=graphs,
+            source=DictSource({k: (v.to(store) if v.dim() == 2 else v) for k, v in w.items()}))
+        got[graphs] = rh.run_trace(runner, steps)
+        rh.assert_rows_match(got[graphs], ref, rh.tol_for(dtype), f"graphs={graphs}")
+        assert (runner.graph_replays > 20) == graphs
+    worst = max(float(np.abs(got[True][k] - got[False][k]).max()) for k in got[True])
+    assert worst <= rh.tol_for(dtype)
