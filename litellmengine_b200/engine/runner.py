@@ -142,6 +142,7 @@ class ModelRunner:
             if g is not None:
                 g[0].replay()
                 self.graph_replays += 1
+                ops.launch_count += g[2]          # the kernels the graph holds ran again
                 return g[1]
         return self.model.forward(batch, self.cache)
 
@@ -159,10 +160,13 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self.model.forward(batch, self.cache)
+        kernels = ops.launch_count - before     # counted while capturing, not run
+        ops.launch_count = before
         batch.max_kv_len = real_max_kv
-        self._graphs[B] = (graph, logits)
+        self._graphs[B] = (graph, logits, kernels)
         return self._graphs[B]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
