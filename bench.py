@@ -217,11 +217,13 @@ def main() -> int:
 
     # ---- the same through the Python entry point: host token ids in, host token ids out ------------
     engine = PagedGenerateEngine(runner)
-    n_new = args.steps + args.warmup
-    ids = [engine.add_request(tokens(CONTEXT - n_new), n_new + 1) for _ in range(args.batch)]
+    # Prompts are prefilled one per step, so the first request decodes a few tokens before the
+    # last one starts: leave room for that, so that all of them still decode in the timed steps.
+    n_new = args.steps + args.warmup + args.batch
+    ids = [engine.add_request(tokens(CONTEXT - n_new), n_new + 8) for _ in range(args.batch)]
     while any(engine.request(i).cached_len < engine.request(i).prompt_len for i in ids):
-        engine.step()                                    # prompts (and the first sampled token)
-    for _ in range(args.warmup - 1):
+        engine.step()                                    # prompts (and the first sampled tokens)
+    for _ in range(args.warmup):
         engine.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -230,6 +232,7 @@ def main() -> int:
         produced += len(engine.step())
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    assert produced == args.steps * args.batch, "a request left the batch inside the timed steps"
     for i in ids:
         engine.release_request(i)
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s",

@@ -1,172 +1,240 @@
-// Paged attention for single decoded tokens, bfloat16, split over the keys so that a small
-// batch still fills the GPU.  Memory-bound by design: every key and value row of the request's
-// kv head is read once, as 16-byte (keys) and 8-byte (values) loads, and serves all the query
-// heads of the group.
+// Paged attention for single decoded tokens, bfloat16, on the tensor cores, split over the keys
+// so that a small batch still fills the GPU.  Memory-bound by design: every key and value row
+// of the request's kv head is read once (coalesced 16-byte cp.async into shared memory,
+// double-buffered) and serves all the query heads of the group, which sit in the 16 rows of
+// one mma tile (rows past the group size are zero and never stored).
 //
 // For the token in row r (request slot s, position p), kv head c, split i of n:
 //     keys j in [lo + i*len, lo + (i+1)*len) ∩ [lo, p],  lo = 0 or p - window + 1
 //     per query head h of the group: s_j = (q_h . k_j) * scale, running max m, sum l of
-//     exp(s_j - m), acc = sum exp(s_j - m) v_j      -- all in 32-bit
+//     exp(s_j - m), acc = sum exp(s_j - m) v_j      -- softmax state and accumulators in 32-bit
 // (the running-maximum form of src/ops/attention.cu:577-668, which walks the keys one by one
 // with one block per query head).  The partial (m, l, acc) of each split go to scratch memory;
-// `paged_decode_combine` merges them: out = sum_i acc_i e^{m_i - M} / sum_i l_i e^{m_i - M}.
+// `paged_decode_combine` merges them: out = sum_i acc_i 2^{m_i - M} / sum_i l_i 2^{m_i - M}
+// (m is kept in the base-2 domain: scores are multiplied by scale*log2(e) once).
 //
-// One CTA of 4 warps per (split, kv head, token).  A warp takes tiles of 32 keys: each lane
-// scores one key against all G query heads (q sits in shared memory, pre-scaled), the warp
-// reduces max and sum per head, then each lane accumulates its D/32 output dimensions over
-// the tile's 32 value rows.  The 4 warps' states are merged through shared memory.
-// Built for head sizes 64 and 128 and groups of 1 to 8; other sizes use the generic kernel.
+// One CTA of 4 warps per (split, kv head, token).  The CTA loads tiles of 64 keys; warp w owns
+// keys 16w..16w+15 of every tile: S = Q K^T (mma.sync m16n8k16), mask, online softmax, P rounded
+// to bfloat16, O += P V.  The four warps' states are merged through shared memory at the end.
+// Built for head sizes 64 and 128 and groups up to 16; other sizes use the generic kernel.
 #include "common.cuh"
 #include <math_constants.h>
 
-#define AD_WARPS 4
-#define AD_THREADS (AD_WARPS * 32)
+#define AD_BN 64
+#define AD_THREADS 128
 
-template <int D, int G>
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    const int bytes = valid ? 16 : 0;                 // 0: nothing is read, the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+// 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile, XOR-swizzled against bank conflicts.
+template <int D>
+__device__ __forceinline__ bf16* tile_at(bf16* base, int row, int chunk) {
+    return base + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+template <int D>
 __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ cache, const int32_t* __restrict__ rows,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
-    int page_size, int window, float scale, int num_pages, int num_splits, int32_t* __restrict__ status) {
-    constexpr int DPL = D / 32;                     // output dims per lane
-    constexpr int GP = (G <= 4) ? 4 : 8;            // heads padded so that p of one key is 1-2 float4
-    __shared__ __align__(16) float q_s[G * D];
-    __shared__ __align__(16) float p_s[AD_WARPS][32][GP];
-    __shared__ long long voff_s[AD_WARPS][32];
-    __shared__ float m_s[AD_WARPS][G], l_s[AD_WARPS][G];
-    __shared__ __align__(16) float acc_s[AD_WARPS][G][D];
+    int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
+    constexpr int CH = D / 8, KB = D / 16;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][D]
+    bf16* k_s = q_s + 16 * D;                                      // [2][64][D]
+    bf16* v_s = k_s + 2 * AD_BN * D;                               // [2][64][D]
+    __shared__ float m_s[4][16], l_s[4][16];
 
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = nq / nkv, h0 = kvh * G;
     const int t = rows ? rows[r] : r;
     const int pos = positions[t];
-    const int slot = entry_slot[token_entry[t]];
-    const int32_t* table = block_table + static_cast<size_t>(slot) * table_stride;
+    const int32_t* table = block_table + static_cast<size_t>(entry_slot[token_entry[t]]) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int n_keys = pos - lo + 1;
     int per_split = (n_keys + num_splits - 1) / num_splits;
-    per_split = (per_split + 31) & ~31;
+    per_split = (per_split + AD_BN - 1) / AD_BN * AD_BN;
     const int k_begin = lo + split * per_split;
     const int k_end = min(pos + 1, k_begin + per_split);
-    const int h0 = kvh * G;                          // first query head of the group
-
-    for (int i = threadIdx.x; i < G * D; i += AD_THREADS)
-        q_s[i] = to_f32(q[(static_cast<size_t>(t) * nq + h0) * D + i]) * scale;
-    __syncthreads();
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + AD_BN - 1) / AD_BN : 0;
 
     const size_t head_stride = static_cast<size_t>(page_size) * D;
     const size_t page_stride = 2 * static_cast<size_t>(nkv) * head_stride;
-    const long long v_shift = static_cast<long long>(nkv) * head_stride;
+    const size_t v_shift = static_cast<size_t>(nkv) * head_stride;
+    const int ld_row = tid >> 1, ld_half = tid & 1;                // a pair of threads copies one row
 
-    float m[G], l[G], acc[G][DPL];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = -CUDART_INF_F;
-        l[g] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[g][e] = 0.0f;
-    }
-
-    for (int base = k_begin + warp * 32; base < k_end; base += AD_WARPS * 32) {
-        const int j = base + lane;
-        long long koff = -1;
-        if (j < k_end) {
-            const int logical = j / page_size;
+    auto load_kv = [&](int kt, int buf) {
+        const int key = kt + ld_row;
+        bool valid = key < k_end;
+        const bf16* src = cache;
+        if (valid) {
+            const int logical = key / page_size;
             const int page = logical < table_stride ? table[logical] : -1;
             if (page < 0 || page >= num_pages) {
                 if (atomicCAS(status, 0, 4) == 0) status[1] = t;
+                valid = false;
             } else {
-                koff = static_cast<long long>(page) * page_stride + kvh * head_stride +
-                       static_cast<long long>(j - logical * page_size) * D;
+                src = cache + static_cast<size_t>(page) * page_stride + kvh * head_stride +
+                      static_cast<size_t>(key - logical * page_size) * D;
             }
         }
-        float s[G];
+        bf16* kd = k_s + buf * AD_BN * D;
+        bf16* vd = v_s + buf * AD_BN * D;
 #pragma unroll
-        for (int g = 0; g < G; ++g) s[g] = 0.0f;
-        if (koff >= 0) {
-            const bf16* kr = cache + koff;
-#pragma unroll 4
-            for (int c = 0; c < D; c += 8) {
-                float kf[8];
-                load8(kr + c, kf);
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + c);
-                    const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + c + 4);
-                    s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] +
-                            qb.y * kf[5] + qb.z * kf[6] + qb.w * kf[7];
-                }
-            }
+        for (int i = 0; i < CH / 2; ++i) {
+            const int c = 2 * i + ld_half;
+            cp_async16(tile_at<D>(kd, ld_row, c), src + c * 8, valid);
+            cp_async16(tile_at<D>(vd, ld_row, c), src + v_shift + c * 8, valid);
         }
-        voff_s[warp][lane] = koff + v_shift;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float sv = (koff >= 0) ? s[g] : -CUDART_INF_F;
-            const float m_new = fmaxf(m[g], warp_max(sv));
-            const float p = (koff >= 0) ? __expf(sv - m_new) : 0.0f;
-            const float alpha = (m[g] == -CUDART_INF_F) ? 0.0f : __expf(m[g] - m_new);
-            l[g] = l[g] * alpha + warp_sum(p);
-            m[g] = m_new;
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) acc[g][e] *= alpha;
-            p_s[warp][lane][g] = p;
-        }
-        __syncwarp();
-        const int count = min(32, k_end - base);
-#pragma unroll 4
-        for (int jj = 0; jj < count; ++jj) {
-            float pv[GP];
-            *reinterpret_cast<float4*>(pv) = *reinterpret_cast<const float4*>(&p_s[warp][jj][0]);
-            if (GP == 8) *reinterpret_cast<float4*>(pv + 4) = *reinterpret_cast<const float4*>(&p_s[warp][jj][4]);
-            const long long vo = voff_s[warp][jj];
-            if (vo < v_shift) continue;              // the key's page was refused
-            const bf16* vr = cache + vo + lane * DPL;
-            float vf[DPL];
-            if (DPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
-            } else {
-                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
-                vf[0] = a.x; vf[1] = a.y;
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-#pragma unroll
-                for (int e = 0; e < DPL; ++e) acc[g][e] += pv[g] * vf[e];
-        }
-        __syncwarp();
-    }
+    };
 
-    // merge the warps' states
+    if (n_tiles > 0) {
+        if (ld_row < 16) {                                          // the group's query heads, zero rows after them
+            const bool valid = ld_row < G;
+            const bf16* src = q + (static_cast<size_t>(t) * nq + h0 + (valid ? ld_row : 0)) * D;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (lane == 0) {
-            m_s[warp][g] = m[g];
-            l_s[warp][g] = l[g];
+            for (int i = 0; i < CH / 2; ++i) {
+                const int c = 2 * i + ld_half;
+                cp_async16(tile_at<D>(q_s, ld_row, c), src + c * 8, valid);
+            }
+        }
+        load_kv(k_begin, 0);
+    }
+    cp_async_commit();
+
+    unsigned qf[KB][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.0f, l1 = 0.0f;   // rows lane/4 and lane/4 + 8
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = k_begin + it * AD_BN, buf = it & 1;
+        cp_async_wait_all();
+        __syncthreads();
+        if (it + 1 < n_tiles) load_kv(kt + AD_BN, buf ^ 1);
+        cp_async_commit();
+        if (it == 0) {
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                ldmatrix_x4(qf[kb], tile_at<D>(q_s, (lane & 7) + ((lane >> 3) & 1) * 8, kb * 2 + (lane >> 4)));
+        }
+        const int key0 = kt + warp * 16;                            // this warp's 16 keys of the tile
+        if (key0 >= k_end) continue;                                // warp-uniform: nothing of ours in this tile
+        bf16* kd = k_s + buf * AD_BN * D;
+        bf16* vd = v_s + buf * AD_BN * D;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            unsigned b[4];
+            ldmatrix_x4(b, tile_at<D>(kd, warp * 16 + (lane & 7) + (lane >> 4) * 8, kb * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s[0], qf[kb], b[0], b[1]);
+            mma_bf16(s[1], qf[kb], b[2], b[3]);
+        }
+        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const bool vis = key0 + nb * 8 + (lane & 3) * 2 + c < k_end;
+                s[nb][c] = vis ? s[nb][c] * scale_log2e : -CUDART_INF_F;
+                s[nb][2 + c] = vis ? s[nb][2 + c] * scale_log2e : -CUDART_INF_F;
+                mx0 = fmaxf(mx0, s[nb][c]);
+                mx1 = fmaxf(mx1, s[nb][2 + c]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);     // finite: key0 < k_end, so one key is visible
+        const float al0 = (m0 == -CUDART_INF_F) ? 0.0f : exp2f(m0 - mn0);
+        const float al1 = (m1 == -CUDART_INF_F) ? 0.0f : exp2f(m1 - mn1);
+        const float p00 = exp2f(s[0][0] - mn0), p01 = exp2f(s[0][1] - mn0), p02 = exp2f(s[1][0] - mn0),
+                    p03 = exp2f(s[1][1] - mn0);
+        const float p10 = exp2f(s[0][2] - mn1), p11 = exp2f(s[0][3] - mn1), p12 = exp2f(s[1][2] - mn1),
+                    p13 = exp2f(s[1][3] - mn1);
+        float sum0 = p00 + p01 + p02 + p03, sum1 = p10 + p11 + p12 + p13;
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        l0 = l0 * al0 + sum0;
+        l1 = l1 * al1 + sum1;
+        m0 = mn0;
+        m1 = mn1;
+        unsigned pf[4] = {pack_bf16(p00, p01), pack_bf16(p10, p11), pack_bf16(p02, p03), pack_bf16(p12, p13)};
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            o[nb][0] *= al0; o[nb][1] *= al0;
+            o[nb][2] *= al1; o[nb][3] *= al1;
         }
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) acc_s[warp][g][lane * DPL + e] = acc[g][e];
+        for (int np = 0; np < D / 16; ++np) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, tile_at<D>(vd, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)));
+            mma_bf16(o[2 * np], pf, b[0], b[1]);
+            mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();                                                // tiles are done: reuse their memory
+
+    float* acc_s = reinterpret_cast<float*>(k_s);                   // [4 warps][16 rows][D]
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+        float* a0 = acc_s + (warp * 16 + r0) * D + c0;
+        float* a1 = a0 + 8 * D;
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            a0[nb * 8] = o[nb][0]; a0[nb * 8 + 1] = o[nb][1];
+            a1[nb * 8] = o[nb][2]; a1[nb * 8 + 1] = o[nb][3];
+        }
+        if ((lane & 3) == 0) {
+            m_s[warp][r0] = m0; l_s[warp][r0] = l0;
+            m_s[warp][r0 + 8] = m1; l_s[warp][r0 + 8] = l1;
+        }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < G * D; i += AD_THREADS) {
+    for (int i = tid; i < G * D; i += AD_THREADS) {
         const int g = i / D, dim = i - g * D;
-        float M = m_s[0][g];
-#pragma unroll
-        for (int w = 1; w < AD_WARPS; ++w) M = fmaxf(M, m_s[w][g]);
+        float M = fmaxf(fmaxf(m_s[0][g], m_s[1][g]), fmaxf(m_s[2][g], m_s[3][g]));
         float a = 0.0f, L = 0.0f;
 #pragma unroll
-        for (int w = 0; w < AD_WARPS; ++w) {
-            const float f = (m_s[w][g] == -CUDART_INF_F) ? 0.0f : __expf(m_s[w][g] - M);
-            a += acc_s[w][g][dim] * f;
+        for (int w = 0; w < 4; ++w) {
+            const float f = (m_s[w][g] == -CUDART_INF_F) ? 0.0f : exp2f(m_s[w][g] - M);
+            a += acc_s[(w * 16 + g) * D + dim] * f;
             L += l_s[w][g] * f;
         }
-        const size_t hrow = static_cast<size_t>(r) * nq + h0 + g;
         if (num_splits == 1) {
             out[(static_cast<size_t>(t) * nq + h0 + g) * D + dim] = __float2bfloat16_rn(a / L);
         } else {
+            const size_t hrow = static_cast<size_t>(r) * nq + h0 + g;
             part_acc[(hrow * num_splits + split) * D + dim] = a;
             if (dim == 0) {
                 part_ml[(hrow * num_splits + split) * 2] = M;
@@ -176,7 +244,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     }
 }
 
-// One block per (token row, query head): merge the splits.
+// One block per (token row, query head): merge the splits (m in the base-2 domain).
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                             const int32_t* __restrict__ rows, bf16* __restrict__ out, int nq,
@@ -191,8 +259,8 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
         float a = 0.0f, L = 0.0f;
         for (int s = 0; s < num_splits; ++s) {
             const float ls = part_ml[(hrow * num_splits + s) * 2 + 1];
-            if (ls > 0.0f) {                          // an empty split wrote no acc
-                const float f = __expf(part_ml[(hrow * num_splits + s) * 2] - M);
+            if (ls > 0.0f) {                          // an empty split holds nothing to add
+                const float f = exp2f(part_ml[(hrow * num_splits + s) * 2] - M);
                 a += part_acc[(hrow * num_splits + s) * D + dim] * f;
                 L += ls * f;
             }
@@ -201,16 +269,22 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
     }
 }
 
-template <int D, int G>
+template <int D>
 static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, const int32_t* positions,
                          const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
                          int table_stride, float* part_acc, float* part_ml, bf16* out, int n_rows, int nq, int nkv,
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
                          cudaStream_t s) {
+    const size_t smem = static_cast<size_t>(16 + 4 * AD_BN) * D * sizeof(bf16);
+    auto kern = paged_decode_attention_kernel<D>;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
     dim3 grid(num_splits, nkv, n_rows);
-    paged_decode_attention_kernel<D, G><<<grid, AD_THREADS, 0, s>>>(
-        q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride, part_acc, part_ml, out, nq,
-        nkv, page_size, window, scale, num_pages, num_splits, status);
+    kern<<<grid, AD_THREADS, smem, s>>>(q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
+                                        part_acc, part_ml, out, nq, nkv, page_size, window,
+                                        scale * 1.4426950408889634f, num_pages, num_splits, status);
     int rc = launch_status();
     if (rc != LLM_OK || num_splits == 1) return rc;
     dim3 cgrid(n_rows, nq);
@@ -220,7 +294,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
 
 // Whether (head_dim, group) has a tuned kernel; the Python side asks before choosing.
 extern "C" int llm_paged_decode_supported(int d, int group) {
-    return (d == 64 || d == 128) && group >= 1 && group <= 8;
+    return (d == 64 || d == 128) && group >= 1 && group <= 16;
 }
 
 // Floats of scratch the call needs: part_acc then part_ml.
@@ -237,23 +311,22 @@ extern "C" int llm_paged_attention_decode(
     int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
     int32_t* status, uintptr_t stream) {
     if (n_rows <= 0) return LLM_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || num_splits < 1 || num_splits > 65535)
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || num_splits < 1 || num_splits > 65535 ||
+        nkv > 65535 || n_rows > 65535)
         return LLM_REFUSED_SIZE;
-    const int group = nq / nkv;
-    if (!llm_paged_decode_supported(d, group)) return LLM_REFUSED_SIZE;
+    if (!llm_paged_decode_supported(d, nq / nkv)) return LLM_REFUSED_SIZE;
     if (!aligned16(cache) || !aligned16(q) || (num_splits > 1 && (!scratch || !aligned16(scratch))))
         return LLM_REFUSED_ALIGN;
     float* part_acc = scratch;
     float* part_ml = scratch ? scratch + static_cast<size_t>(n_rows) * nq * num_splits * d : nullptr;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-#define CASE(DD, GG)                                                                                        \
-    if (d == DD && group == GG)                                                                             \
-        return launch_decode<DD, GG>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows,    \
-                                     positions, token_entry, entry_slot, block_table, table_stride,         \
-                                     part_acc, part_ml, static_cast<bf16*>(out), n_rows, nq, nkv,           \
-                                     page_size, window, scale, num_pages, num_splits, status, s);
-    CASE(64, 1) CASE(64, 2) CASE(64, 3) CASE(64, 4) CASE(64, 5) CASE(64, 6) CASE(64, 7) CASE(64, 8)
-    CASE(128, 1) CASE(128, 2) CASE(128, 3) CASE(128, 4) CASE(128, 5) CASE(128, 6) CASE(128, 7) CASE(128, 8)
-#undef CASE
-    return LLM_REFUSED_SIZE;
+    if (d == 64)
+        return launch_decode<64>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions,
+                                 token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,
+                                 static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages,
+                                 num_splits, status, s);
+    return launch_decode<128>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions,
+                              token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,
+                              static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages,
+                              num_splits, status, s);
 }

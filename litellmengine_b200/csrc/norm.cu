@@ -14,31 +14,60 @@ template <typename TX, typename TD, typename TO>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
                                const float* __restrict__ w, TO* __restrict__ out,
                                const int32_t* __restrict__ rows, int hidden, float eps,
-                               int write_sum) {
-    extern __shared__ float smem[];            // hidden floats + 33 for the reduction
+                               int write_sum, int vec) {
+    extern __shared__ __align__(16) float smem[];   // hidden floats (padded to 8) + 33 for the reduction
     float* v = smem;
-    float* scratch = smem + hidden;
+    float* scratch = smem + ((hidden + 7) & ~7);
     const size_t src = rows ? static_cast<size_t>(rows[blockIdx.x]) : blockIdx.x;
     TX* xr = x + src * hidden;
     const TD* dr = delta ? delta + src * hidden : nullptr;
     TO* orow = out + static_cast<size_t>(blockIdx.x) * hidden;
     float ss = 0.0f;
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
-        float a = to_f32(xr[h]);
-        if (dr) a += to_f32(dr[h]);
-        v[h] = a;
-        ss += a * a;
-        if (write_sum) xr[h] = from_f32<TX>(a);
+    if (vec) {                                      // 8 elements per thread per trip, 16-byte accesses
+        for (int h = threadIdx.x * 8; h < hidden; h += blockDim.x * 8) {
+            float a[8];
+            load8(xr + h, a);
+            if (dr) {
+                float b[8];
+                load8(dr + h, b);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[i] += b[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += a[i] * a[i];
+            store8(v + h, a);
+            if (write_sum) store8(xr + h, a);
+        }
+    } else {
+        for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+            float a = to_f32(xr[h]);
+            if (dr) a += to_f32(dr[h]);
+            v[h] = a;
+            ss += a * a;
+            if (write_sum) xr[h] = from_f32<TX>(a);
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) orow[h] = from_f32<TO>(v[h] * inv * w[h]);
+    if (vec) {
+        for (int h = threadIdx.x * 8; h < hidden; h += blockDim.x * 8) {
+            float a[8], g[8];
+            load8(v + h, a);
+            load8(w + h, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = a[i] * inv * g[i];
+            store8(orow + h, a);
+        }
+    } else {
+        for (int h = threadIdx.x; h < hidden; h += blockDim.x) orow[h] = from_f32<TO>(v[h] * inv * w[h]);
+    }
 }
 
 template <typename TX, typename TD, typename TO>
 static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out, const int32_t* rows,
                           int num_rows, int hidden, float eps, int write_sum, cudaStream_t s) {
-    const size_t smem = (static_cast<size_t>(hidden) + 33) * sizeof(float);
+    const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33) * sizeof(float);
+    const int vec = (hidden % 8 == 0) && aligned16(x) && aligned16(out) && aligned16(w) && (!delta || aligned16(delta));
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     auto kern = rmsnorm_kernel<TX, TD, TO>;
     if (smem > 48 * 1024) {
@@ -48,7 +77,7 @@ static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out,
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
     kern<<<num_rows, threads, smem, s>>>(static_cast<TX*>(x), static_cast<const TD*>(delta), w,
-                                         static_cast<TO*>(out), rows, hidden, eps, write_sum);
+                                         static_cast<TO*>(out), rows, hidden, eps, write_sum, vec);
     return launch_status();
 }
 

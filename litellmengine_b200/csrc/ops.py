@@ -310,8 +310,9 @@ def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     R, V = logits.shape
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    f = _fn("sampling", "llm_argmax_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(logits), R, V, _ptr(out), _stream()), "argmax_rows")
+    scratch = decode_scratch(logits.device, R * 64 * 2)
+    f = _fn("sampling", "llm_argmax_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), R, V, _ptr(out), _ptr(scratch), _stream()), "argmax_rows")
     return out
 
 

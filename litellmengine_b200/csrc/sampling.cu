@@ -70,10 +70,60 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, 
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
 
-extern "C" int llm_argmax_rows(const float* logits, int num_rows, int vocab, int32_t* out, uintptr_t stream) {
+// Two stages for long rows: every block takes a chunk of one row and leaves its best (value,
+// index); a second launch picks the best chunk per row.  Ties still go to the lowest index,
+// because `better` compares indices and chunks are index ranges.
+__global__ void argmax_chunks_kernel(const float* __restrict__ logits, int vocab, int chunk,
+                                     float* __restrict__ part_val, int32_t* __restrict__ part_idx) {
+    __shared__ MaxIdx sh[33];
+    const int row = blockIdx.y, c0 = blockIdx.x * chunk, n = min(chunk, vocab - c0);
+    MaxIdx r = block_argmax(logits + static_cast<size_t>(row) * vocab + c0, n, sh);
+    if (threadIdx.x == 0) {
+        part_val[row * gridDim.x + blockIdx.x] = r.v;
+        part_idx[row * gridDim.x + blockIdx.x] = r.i + c0;
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
+                                    int chunks, int32_t* __restrict__ out) {
+    MaxIdx best = {-CUDART_INF_F, 0x7fffffff};
+    for (int c = threadIdx.x; c < chunks; c += 32)
+        best = better(best, MaxIdx{part_val[blockIdx.x * chunks + c], part_idx[blockIdx.x * chunks + c]});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxIdx other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+#define ARGMAX_CHUNK 8192
+#define ARGMAX_MAX_CHUNKS 64
+
+// scratch: room for num_rows * chunks floats and as many int32 (chunks = ceil(vocab / 8192), at most
+// 64); may be null when vocab <= 8192.
+extern "C" int llm_argmax_rows(const float* logits, int num_rows, int vocab, int32_t* out, void* scratch,
+                               uintptr_t stream) {
     if (num_rows <= 0) return LLM_OK;
     if (vocab <= 0) return LLM_REFUSED_SIZE;
-    argmax_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, vocab, out);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    int chunk = ARGMAX_CHUNK;
+    int chunks = (vocab + chunk - 1) / chunk;
+    if (chunks > ARGMAX_MAX_CHUNKS) {
+        chunks = ARGMAX_MAX_CHUNKS;
+        chunk = (vocab + chunks - 1) / chunks;
+        chunks = (vocab + chunk - 1) / chunk;
+    }
+    if (chunks <= 1 || scratch == nullptr || num_rows > 65535) {
+        argmax_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, out);
+        return launch_status();
+    }
+    float* part_val = static_cast<float*>(scratch);
+    int32_t* part_idx = reinterpret_cast<int32_t*>(part_val + static_cast<size_t>(num_rows) * chunks);
+    argmax_chunks_kernel<<<dim3(chunks, num_rows), 256, 0, s>>>(logits, vocab, chunk, part_val, part_idx);
+    int rc = launch_status();
+    if (rc != LLM_OK) return rc;
+    argmax_merge_kernel<<<num_rows, 32, 0, s>>>(part_val, part_idx, chunks, out);
     return launch_status();
 }
 

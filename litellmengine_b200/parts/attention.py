@@ -107,7 +107,7 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
         out = torch.empty_like(q)
         if b.num_decode:
             work = b.num_decode * nkv
-            splits = max(1, min(16, -(-444 // work), -(-b.max_kv_len // 256)))
+            splits = max(1, min(32, -(-444 // work), -(-b.max_kv_len // 128)))
             ops.paged_attention_decode(q, out, cache, None if b.num_decode == b.num_tokens else b.decode_rows,
                                        b.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
                                        nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
