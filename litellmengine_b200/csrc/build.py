@@ -33,6 +33,7 @@ FAMILIES: Dict[str, List[str]] = {
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
     "sampling": ["sampling.cu"],
+    "gemm_skinny": ["gemm_skinny.cu"],
 }
 HEADERS = ["common.cuh"]
 

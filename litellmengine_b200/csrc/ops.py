@@ -342,11 +342,36 @@ def sampler_uniform(seed: int, counter: int) -> float:
 
 
 # ------------------------------------------------------------------------------------------
+SKINNY_MAX_ROWS = 16
+
+
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M <= 16, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16
+    operands, float32 accumulation, float32 or bfloat16 result)."""
+    _dev(x, weight, out)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError("the skinny product takes bfloat16 operands")
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError("x and weight disagree on K")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    f = _fn("gemm_skinny", "llm_linear_skinny", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), M, N, K, _stream()), "linear_skinny")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [T, K] @ weight[N, K]^T through the library matrix product (the reference uses cuBLAS for
-    its products too, src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a
-    float32 weight keeps its product in true float32 (no TF32), whatever x is."""
+    """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's own
+    weight-streaming kernel; everything else through the library matrix product (the reference
+    uses cuBLAS for all its products, src/layers/linear.cu:169-215).  bfloat16 operands accumulate
+    in float32; a float32 weight keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
+            and x.shape[1] % 8 == 0):
+        return linear_skinny(x, weight, out_dtype or x.dtype)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
         want = out_dtype or x.dtype

@@ -438,3 +438,20 @@ def test_prefill_kernel_window_edges(window):
         out, ref = fast_case("prefill", 4, 2, 64, 16, [(n, nqr)], window=window, spike=(0, key), seed=window)
         close(out, ref, 1e-2)
         assert (float(out[-1].float().mean()) > 90.0) == inside
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (16, 48, 4096), (9, 1000, 1544),
+                                   (5, 17, 8), (8, 6144, 4096)])
+def test_skinny_product(M, N, K, out_dtype):
+    """The weight-streaming product for decode steps against float64, at sizes that are no multiple
+    of its tiles (N of 16, K of 512, M of 8)."""
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    got = ops().linear_skinny(x.to(DEV), w.to(DEV), DT[out_dtype])
+    assert got.dtype == DT[out_dtype] and got.shape == (M, N)
+    close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    lib = torch.mm(x.to(DEV), w.to(DEV).t(), out_dtype=torch.float32)
+    close(got, lib, 2e-5 if out_dtype == "float32" else 6e-3)      # and against the library product
