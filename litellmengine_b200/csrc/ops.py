@@ -342,7 +342,7 @@ def sampler_uniform(seed: int, counter: int) -> float:
 
 
 # ------------------------------------------------------------------------------------------
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 0      # rows up to which `linear` prefers the engine's own kernel (0: never; see linear_skinny)
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
