@@ -330,3 +330,59 @@ extern "C" int llm_paged_attention_decode(
                               static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages,
                               num_splits, status, s);
 }
+
+// ---- the entry point that allocates nothing (declared and explained in attention_decode_noalloc.h) ----
+#include "attention_decode_noalloc.h"
+
+// The splits' partial results of llm_paged_attention_decode_noalloc live here, in the library image.
+static __device__ __align__(256) float g_decode_noalloc_scratch[LLM_DECODE_NOALLOC_SCRATCH_FLOATS];
+
+#define NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES];      // device address of the array, per device
+
+extern "C" long long llm_paged_attention_decode_noalloc_needed(int n_rows, int nq, int d, int num_splits) {
+    return llm_paged_decode_scratch_floats(n_rows, nq, d, num_splits);
+}
+
+extern "C" const char* llm_noalloc_strerror(int code) {
+    switch (code) {
+        case LLM_OK: return "ok";
+        case LLM_REFUSED_SIZE: return "refused: head size, group or counts the decode attention kernel does not take";
+        case LLM_REFUSED_DTYPE: return "refused: dtype";
+        case LLM_REFUSED_ALIGN: return "refused: q, out or cache is not 16-byte aligned";
+        case LLM_REFUSED_SCRATCH:
+            return "refused: n_rows * nq * num_splits * (d + 2) exceeds the 4194304 floats of the static scratch; "
+                   "use fewer splits or rows, or the allocating entry point";
+        case LLM_SYMBOL_ADDRESS_FAILED: return "cudaGetSymbolAddress failed for the static scratch on this device";
+        default: return code > 0 ? "CUDA error at launch (the value is the cudaError_t)" : "unknown code";
+    }
+}
+
+extern "C" int llm_paged_attention_decode_noalloc(
+    const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
+    const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
+    int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
+    uintptr_t stream) {
+    if (n_rows <= 0) return LLM_OK;
+    if (nq <= 0 || d <= 0 || num_splits < 1) return LLM_REFUSED_SIZE;
+    if (llm_paged_decode_scratch_floats(n_rows, nq, d, num_splits) > LLM_DECODE_NOALLOC_SCRATCH_FLOATS)
+        return LLM_REFUSED_SCRATCH;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NOALLOC_MAX_DEVICES)
+        return LLM_SYMBOL_ADDRESS_FAILED;
+    float* scratch = g_noalloc_scratch_ptr[device];
+    if (scratch == nullptr) {
+        // Set-up, once per device, with that device current: the host-side name of a __device__
+        // array is not a device address; the runtime hands out the real one.
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_decode_noalloc_scratch) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return LLM_SYMBOL_ADDRESS_FAILED;
+        }
+        scratch = static_cast<float*>(p);
+        g_noalloc_scratch_ptr[device] = scratch;
+    }
+    return llm_paged_attention_decode(q, out, cache, rows, n_rows, positions, token_entry, entry_slot, block_table,
+                                      table_stride, nq, nkv, d, page_size, window, scale, num_pages, num_splits,
+                                      scratch, status, stream);
+}
