@@ -1,7 +1,7 @@
 // Paged attention for single decoded tokens, bfloat16, on the tensor cores, split over the keys
 // so that a small batch still fills the GPU.  Memory-bound by design: every key and value row
-// of the request's kv head is read once (coalesced 16-byte cp.async into shared memory,
-// double-buffered) and serves all the query heads of the group, which sit in the 16 rows of
+// of the request's kv head is read once (coalesced 16-byte cp.async into shared memory, three
+// tiles deep) and serves all the query heads of the group, which sit in the 16 rows of
 // one mma tile (rows past the group size are zero and never stored).
 //
 // For the token in row r (request slot s, position p), kv head c, split i of n:
@@ -22,6 +22,7 @@
 
 #define AD_BN 64
 #define AD_THREADS 128
+#define AD_STAGES 3          // key/value tiles in shared memory: one being read, two in flight
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
@@ -30,6 +31,7 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
     const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -65,8 +67,8 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     constexpr int CH = D / 8, KB = D / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][D]
-    bf16* k_s = q_s + 16 * D;                                      // [2][64][D]
-    bf16* v_s = k_s + 2 * AD_BN * D;                               // [2][64][D]
+    bf16* k_s = q_s + 16 * D;                                      // [STAGES][64][D]
+    bf16* v_s = k_s + AD_STAGES * AD_BN * D;                       // [STAGES][64][D]
     __shared__ float m_s[4][16], l_s[4][16];
 
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
@@ -126,6 +128,11 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
         load_kv(k_begin, 0);
     }
     cp_async_commit();
+#pragma unroll
+    for (int st = 1; st < AD_STAGES - 1; ++st) {
+        if (st < n_tiles) load_kv(k_begin + st * AD_BN, st);
+        cp_async_commit();
+    }
 
     unsigned qf[KB][4];
     float o[D / 8][4];
@@ -134,10 +141,10 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.0f, l1 = 0.0f;   // rows lane/4 and lane/4 + 8
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int kt = k_begin + it * AD_BN, buf = it & 1;
-        cp_async_wait_all();
-        __syncthreads();
-        if (it + 1 < n_tiles) load_kv(kt + AD_BN, buf ^ 1);
+        const int kt = k_begin + it * AD_BN, buf = it % AD_STAGES;
+        cp_async_wait<AD_STAGES - 2>();                             // tile `it` has landed; later ones may be in flight
+        __syncthreads();                                            // and every warp is done with tile it-1's buffer
+        if (it + AD_STAGES - 1 < n_tiles) load_kv(kt + (AD_STAGES - 1) * AD_BN, (it + AD_STAGES - 1) % AD_STAGES);
         cp_async_commit();
         if (it == 0) {
 #pragma unroll
@@ -205,15 +212,21 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     cp_async_wait_all();
     __syncthreads();                                                // tiles are done: reuse their memory
 
-    float* acc_s = reinterpret_cast<float*>(k_s);                   // [4 warps][16 rows][D]
+    constexpr int AS = D + 8;                                       // padded row: rows 0..3 hit different banks
+    float* acc_s = reinterpret_cast<float*>(k_s);                   // [4 warps][16 rows][AS]; only rows < G are used
     {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
-        float* a0 = acc_s + (warp * 16 + r0) * D + c0;
-        float* a1 = a0 + 8 * D;
+        float* a0 = acc_s + (warp * 16 + r0) * AS + c0;
+        float* a1 = a0 + 8 * AS;
+        if (r0 < G) {
 #pragma unroll
-        for (int nb = 0; nb < D / 8; ++nb) {
-            a0[nb * 8] = o[nb][0]; a0[nb * 8 + 1] = o[nb][1];
-            a1[nb * 8] = o[nb][2]; a1[nb * 8 + 1] = o[nb][3];
+            for (int nb = 0; nb < D / 8; ++nb)
+                *reinterpret_cast<float2*>(a0 + nb * 8) = make_float2(o[nb][0], o[nb][1]);
+        }
+        if (r0 + 8 < G) {
+#pragma unroll
+            for (int nb = 0; nb < D / 8; ++nb)
+                *reinterpret_cast<float2*>(a1 + nb * 8) = make_float2(o[nb][2], o[nb][3]);
         }
         if ((lane & 3) == 0) {
             m_s[warp][r0] = m0; l_s[warp][r0] = l0;
@@ -228,7 +241,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float f = (m_s[w][g] == -CUDART_INF_F) ? 0.0f : exp2f(m_s[w][g] - M);
-            a += acc_s[(w * 16 + g) * D + dim] * f;
+            a += acc_s[(w * 16 + g) * AS + dim] * f;
             L += l_s[w][g] * f;
         }
         if (num_splits == 1) {
@@ -275,7 +288,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
                          int table_stride, float* part_acc, float* part_ml, bf16* out, int n_rows, int nq, int nkv,
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
                          cudaStream_t s) {
-    const size_t smem = static_cast<size_t>(16 + 4 * AD_BN) * D * sizeof(bf16);
+    const size_t smem = static_cast<size_t>(16 + 2 * AD_STAGES * AD_BN) * D * sizeof(bf16);
     auto kern = paged_decode_attention_kernel<D>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
