@@ -88,42 +88,41 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const size_t head_stride = static_cast<size_t>(page_size) * D;
     const size_t page_stride = 2 * static_cast<size_t>(nkv) * head_stride;
     const size_t v_shift = static_cast<size_t>(nkv) * head_stride;
-    // Copies: consecutive threads take consecutive 16-byte chunks of a row, so one warp instruction
-    // covers whole rows (512 contiguous bytes) in global memory and 8 distinct bank groups per
-    // quarter-warp in shared memory.  A thread meets 64*CH/128 rows per tile, one page lookup each.
-    constexpr int RPI = AD_THREADS / CH;                            // rows covered per pass of the CTA
-    const int ld_chunk = tid % CH, ld_row0 = tid / CH;
+    const int ld_row = tid >> 1, ld_half = tid & 1;                // a pair of threads copies one row
 
     auto load_kv = [&](int kt, int buf) {
+        const int key = kt + ld_row;
+        bool valid = key < k_end;
+        const bf16* src = cache;
+        if (valid) {
+            const int logical = key / page_size;
+            const int page = logical < table_stride ? table[logical] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (atomicCAS(status, 0, 4) == 0) status[1] = t;
+                valid = false;
+            } else {
+                src = cache + static_cast<size_t>(page) * page_stride + kvh * head_stride +
+                      static_cast<size_t>(key - logical * page_size) * D;
+            }
+        }
         bf16* kd = k_s + buf * AD_BN * D;
         bf16* vd = v_s + buf * AD_BN * D;
 #pragma unroll
-        for (int i = 0; i < AD_BN / RPI; ++i) {
-            const int row = ld_row0 + i * RPI, key = kt + row;
-            bool valid = key < k_end;
-            const bf16* src = cache;
-            if (valid) {
-                const int logical = key / page_size;
-                const int page = logical < table_stride ? table[logical] : -1;
-                if (page < 0 || page >= num_pages) {
-                    if (atomicCAS(status, 0, 4) == 0) status[1] = t;
-                    valid = false;
-                } else {
-                    src = cache + static_cast<size_t>(page) * page_stride + kvh * head_stride +
-                          static_cast<size_t>(key - logical * page_size) * D + ld_chunk * 8;
-                }
-            }
-            cp_async16(tile_at<D>(kd, row, ld_chunk), src, valid);
-            cp_async16(tile_at<D>(vd, row, ld_chunk), src + v_shift, valid);
+        for (int i = 0; i < CH / 2; ++i) {
+            const int c = 2 * i + ld_half;
+            cp_async16(tile_at<D>(kd, ld_row, c), src + c * 8, valid);
+            cp_async16(tile_at<D>(vd, ld_row, c), src + v_shift + c * 8, valid);
         }
     };
 
     if (n_tiles > 0) {
-        {                                                           // the group's query heads, zero rows after them
-            for (int row = ld_row0; row < 16; row += RPI) {
-                const bool valid = row < G;
-                const bf16* src = q + (static_cast<size_t>(t) * nq + h0 + (valid ? row : 0)) * D + ld_chunk * 8;
-                cp_async16(tile_at<D>(q_s, row, ld_chunk), src, valid);
+        if (ld_row < 16) {                                          // the group's query heads, zero rows after them
+            const bool valid = ld_row < G;
+            const bf16* src = q + (static_cast<size_t>(t) * nq + h0 + (valid ? ld_row : 0)) * D;
+#pragma unroll
+            for (int i = 0; i < CH / 2; ++i) {
+                const int c = 2 * i + ld_half;
+                cp_async16(tile_at<D>(q_s, ld_row, c), src + c * 8, valid);
             }
         }
         load_kv(k_begin, 0);
