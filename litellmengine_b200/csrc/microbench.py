@@ -100,6 +100,8 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--out-dtype", default="bfloat16")
+    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own"],
+                    help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -159,7 +161,13 @@ def main():
         x = torch.randn(args.tokens, args.k, device=dev, dtype=torch.bfloat16)
         w = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02
         od = torch.float32 if args.out_dtype == "float32" else torch.bfloat16
-        fn = lambda: ops.linear(x, w, out_dtype=od)
+        if args.impl == "library":
+            fn = lambda: torch.mm(x, w.t(), out_dtype=od) if od != x.dtype else torch.mm(x, w.t())
+        elif args.impl == "own":
+            fn = lambda: ops.linear_skinny(x, w, od)
+        else:
+            fn = lambda: ops.linear(x, w, out_dtype=od)
+        res["impl"] = args.impl
         res.update(m=args.tokens, n=args.n, k=args.k, bytes=args.n * args.k * 2 + args.tokens * (args.k * 2 + args.n * od.itemsize),
                    flops=2 * args.tokens * args.n * args.k)
 

@@ -342,6 +342,7 @@ def sampler_uniform(seed: int, counter: int) -> float:
 
 
 # ------------------------------------------------------------------------------------------
+_skinny_scratch: Dict[str, torch.Tensor] = {}
 SKINNY_MAX_ROWS = 0      # rows up to which `linear` prefers the engine's own kernel (0: never; see linear_skinny)
 
 
@@ -358,8 +359,16 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         raise KernelError("x and weight disagree on K")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    f = _fn("gemm_skinny", "llm_linear_skinny", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), M, N, K, _stream()), "linear_skinny")
+    key = str(x.device)
+    scratch = _skinny_scratch.get(key)
+    if scratch is None:
+        need = _fn("gemm_skinny", "llm_linear_skinny_scratch_floats", [], restype=c_longlong)()
+        scratch = _skinny_scratch[key] = torch.empty(int(need), dtype=torch.float32, device=x.device)
+    f = _fn("gemm_skinny", "llm_linear_skinny",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), M, N, K, _stream()), "linear_skinny")
+    global launch_count
+    launch_count += 1                             # the kernel that adds the pieces of shared tiles
     return out
 
 
