@@ -343,6 +343,22 @@ def sampler_uniform(seed: int, counter: int) -> float:
 
 # ------------------------------------------------------------------------------------------
 _skinny_scratch: Dict[str, torch.Tensor] = {}
+
+
+def skinny_scratch(device, floats: int) -> Optional[torch.Tensor]:
+    """Scratch for the streaming product's k-splits; grown on demand, never freed."""
+    if floats <= 0:
+        return None
+    key = str(device)
+    t = _skinny_scratch.get(key)
+    if t is None or t.numel() < floats:
+        if t is not None:
+            _scratch_retired.append(t)
+        t = torch.empty(max(2 * floats, 1 << 22), dtype=torch.float32, device=device)
+        _skinny_scratch[key] = t
+    return t
+
+
 SKINNY_MAX_ROWS = 0      # rows up to which `linear` prefers the engine's own kernel (0: never; see linear_skinny)
 
 
@@ -359,16 +375,14 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         raise KernelError("x and weight disagree on K")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    key = str(x.device)
-    scratch = _skinny_scratch.get(key)
-    if scratch is None:
-        need = _fn("gemm_skinny", "llm_linear_skinny_scratch_floats", [], restype=c_longlong)()
-        scratch = _skinny_scratch[key] = torch.empty(int(need), dtype=torch.float32, device=x.device)
+    need = _fn("gemm_skinny", "llm_linear_skinny_scratch_floats", [c_int, c_int, c_int], restype=c_longlong)(M, N, K)
+    scratch = skinny_scratch(x.device, int(need))
     f = _fn("gemm_skinny", "llm_linear_skinny",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), M, N, K, _stream()), "linear_skinny")
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
+             M, N, K, _stream()), "linear_skinny")
     global launch_count
-    launch_count += 1                             # the kernel that adds the pieces of shared tiles
+    launch_count += 1 if need else 0              # the kernel that adds the k-splits
     return out
 
 
