@@ -359,7 +359,7 @@ def skinny_scratch(device, floats: int) -> Optional[torch.Tensor]:
     return t
 
 
-SKINNY_MAX_ROWS = 0      # rows up to which `linear` prefers the engine's own kernel (0: never; see linear_skinny)
+SKINNY_MAX_ROWS = 16     # rows up to which `linear` may take the engine's own streaming kernel
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
@@ -387,13 +387,15 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's own
-    weight-streaming kernel; everything else through the library matrix product (the reference
-    uses cuBLAS for all its products, src/layers/linear.cu:169-215).  bfloat16 operands accumulate
-    in float32; a float32 weight keeps its product in true float32 (no TF32), whatever x is."""
+    """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) against a long-K or
+    very tall weight go through the engine's own weight-streaming kernel, which measured faster
+    there (K = 12288: 32 us against 36; N = 151936: 203 us against 218 on a B200); everything else
+    goes through the library matrix product (the reference uses cuBLAS for all its products,
+    src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a float32 weight
+    keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
-            and x.shape[1] % 8 == 0):
+            and x.shape[1] % 8 == 0 and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)):
         return linear_skinny(x, weight, out_dtype or x.dtype)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
