@@ -1,6 +1,6 @@
 // Paged causal attention for prompt portions, bfloat16, on the tensor cores.
 //
-// A CTA takes 64 consecutive query rows of one request (a "tile" from the host-built tile
+// A CTA takes 128 consecutive query rows of one request (a "tile" from the host-built tile
 // list) for one query head and walks the request's keys in tiles of 64, reading keys and
 // values straight from the cache pages (the step's own keys were written there first, so a
 // portion at any past length takes the same path):
@@ -10,14 +10,16 @@
 //     running maximum and sum per row in 32-bit (src/ops/attention.cu:204-249 folds one key at a
 //     time; here a tile of 64), P rounded to bfloat16 for the second product, O += P V in 32-bit.
 // K and V tiles are staged in shared memory with cp.async, double-buffered, XOR-swizzled in
-// 16-byte chunks so that ldmatrix reads are conflict-free.  Four warps, 16 query rows each.
+// 16-byte chunks so that ldmatrix reads are conflict-free.  Eight warps, 16 query rows each; the
+// host lists the tiles longest first (the last rows of a prompt see the most keys).
 // Built for head sizes 64 and 128; other sizes use the generic kernel.
 #include "common.cuh"
 #include <math_constants.h>
 
-#define AP_BM 64
-#define AP_BN 64
-#define AP_THREADS 128
+#define AP_WARPS 8
+#define AP_BM (16 * AP_WARPS)      // query rows per CTA
+#define AP_BN 64                   // keys per tile
+#define AP_THREADS (32 * AP_WARPS)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     constexpr int CH = D / 8;                     // 16-byte chunks per row
     constexpr int KB = D / 16;                    // k-blocks of the first product
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                    // [64][D]
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                    // [BM][D]
     bf16* k_s = q_s + AP_BM * D;                                      // [2][64][D]
     bf16* v_s = k_s + 2 * AP_BN * D;                                  // [2][64][D]
 
@@ -86,8 +88,9 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const size_t page_stride = 2 * static_cast<size_t>(nkv) * head_stride;
     const size_t v_shift = static_cast<size_t>(nkv) * head_stride;
 
-    // each pair of threads copies one row: thread (row, half) takes chunks 2*i + half
-    const int ld_row = tid >> 1, ld_half = tid & 1;
+    // a group of TPR threads copies one key row: thread (row, sub) takes chunks TPR*i + sub
+    constexpr int TPR = AP_THREADS / AP_BN;
+    const int ld_row = tid / TPR, ld_sub = tid % TPR;
 
     auto load_kv = [&](int kt, int buf) {
         const int key = kt + ld_row;
@@ -107,20 +110,22 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
         bf16* kd = k_s + buf * AP_BN * D;
         bf16* vd = v_s + buf * AP_BN * D;
 #pragma unroll
-        for (int i = 0; i < CH / 2; ++i) {
-            const int c = 2 * i + ld_half;
+        for (int i = 0; i < CH / TPR; ++i) {
+            const int c = TPR * i + ld_sub;
             cp_async16(tile_at<D>(kd, ld_row, c), src + c * 8, valid);
             cp_async16(tile_at<D>(vd, ld_row, c), src + v_shift + c * 8, valid);
         }
     };
 
-    {   // Q tile
-        const bool valid = ld_row < rows_here;
-        const bf16* src = q + (static_cast<size_t>(row_base + (valid ? ld_row : 0)) * nq + h) * D;
+    {   // Q tile: TPQ threads per query row
+        constexpr int TPQ = AP_THREADS / AP_BM;
+        const int qr = tid / TPQ, qsub = tid % TPQ;
+        const bool valid = qr < rows_here;
+        const bf16* src = q + (static_cast<size_t>(row_base + (valid ? qr : 0)) * nq + h) * D;
 #pragma unroll
-        for (int i = 0; i < CH / 2; ++i) {
-            const int c = 2 * i + ld_half;
-            cp_async16(tile_at<D>(q_s, ld_row, c), src + c * 8, valid);
+        for (int i = 0; i < CH / TPQ; ++i) {
+            const int c = TPQ * i + qsub;
+            cp_async16(tile_at<D>(q_s, qr, c), src + c * 8, valid);
         }
     }
     load_kv(k_lo, 0);
@@ -148,6 +153,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
             for (int kb = 0; kb < KB; ++kb)
                 ldmatrix_x4(qf[kb], tile_at<D>(q_s, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kb * 2 + (lane >> 4)));
         }
+        if (kt > past + q0 + warp * 16 + 15) continue;              // every key of the tile lies after this warp's rows
         const bf16* kd = k_s + buf * AP_BN * D;
         const bf16* vd = v_s + buf * AP_BN * D;
 
@@ -246,7 +252,8 @@ extern "C" int llm_paged_prefill_supported(int d) { return d == 64 || d == 128; 
 extern "C" int llm_paged_prefill_tile_rows() { return AP_BM; }
 
 // q, out: bfloat16 [T, nq*d]; cache: bfloat16 [pages, 2, nkv, page_size, d];
-// tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), each tile 64 rows.
+// tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), each tile
+// llm_paged_prefill_tile_rows() rows.
 extern "C" int llm_paged_attention_prefill(
     const void* q, void* out, const void* cache, const int32_t* tiles, int n_tiles, const int32_t* entry_slot,
     const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,

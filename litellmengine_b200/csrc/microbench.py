@@ -128,8 +128,9 @@ def main():
         args.batch, args.context = 1, args.tokens
         cache, table, q, pos, ent, slot = paged_setup(args, dev, args.tokens)
         out = torch.empty_like(q)
-        n_tiles = (args.tokens + 63) // 64
-        tiles = torch.tensor([[0, 64 * i] for i in range(n_tiles)], dtype=torch.int32, device=dev)
+        R = ops.PREFILL_TILE_ROWS
+        n_tiles = (args.tokens + R - 1) // R
+        tiles = torch.tensor([[0, R * i] for i in reversed(range(n_tiles))], dtype=torch.int32, device=dev)
         i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
         fn = lambda: ops.paged_attention_prefill(q, out, cache, tiles, n_tiles, slot, i32(0), i32(args.tokens),
                                                  i32(args.tokens), table, nq, nkv, d, P, None, scale, status)

@@ -235,7 +235,7 @@ def fast_attention_supported(d: int, group: int) -> bool:
     return bool(a(d, group)) and bool(b(d))
 
 
-PREFILL_TILE_ROWS = 64
+PREFILL_TILE_ROWS = 128
 _scratch: Dict[str, torch.Tensor] = {}
 _scratch_retired = []          # outgrown buffers stay alive: a captured graph may still point at them
 
@@ -286,8 +286,8 @@ def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
                             n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
                             block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
                             window: Optional[int], scale: float, status: torch.Tensor) -> torch.Tensor:
-    """Attention for prompt portions: `tiles` int32 [n_tiles, 2] = (entry, first row of a 64-row
-    tile inside the entry).  bfloat16 only."""
+    """Attention for prompt portions: `tiles` int32 [n_tiles, 2] = (entry, first row of a
+    PREFILL_TILE_ROWS-row tile inside the entry).  bfloat16 only."""
     _dev(q, out, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the prefill attention kernel is bfloat16 only")

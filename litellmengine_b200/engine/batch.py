@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 
-PREFILL_TILE_ROWS = 64          # query rows per tile of the tensor-core prefill attention kernel
+PREFILL_TILE_ROWS = 128         # query rows per tile of the tensor-core prefill attention kernel
 
 
 @dataclass
@@ -140,6 +140,11 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
         row += n
     counts = hv("counts")
     counts[0], counts[1], counts[2], counts[3], counts[4] = T, B, w, n_dec, n_tiles
+    if n_tiles > 1:
+        # longest first: a tile late in a long prompt walks the most keys, so it should start early
+        tl = tiles[:2 * n_tiles].reshape(n_tiles, 2)
+        cost = np.array([entries[int(e)].past + int(q0) for e, q0 in tl])
+        tl[:] = tl[np.argsort(-cost, kind="stable")]
     for g, (idx, val) in enumerate(updates):
         if len(idx) > buffers.max_updates:
             raise ValueError("more block-table changes than the step buffer holds")

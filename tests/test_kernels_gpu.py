@@ -353,7 +353,7 @@ def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1,
         kv_len.append(n)
         if nqr == 1:
             dec_rows.append(row)
-        for q0 in range(0, nqr, 64):
+        for q0 in range(0, nqr, ops().PREFILL_TILE_ROWS):
             tiles += [b, q0]
         row += nqr
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
