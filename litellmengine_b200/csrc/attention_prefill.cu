@@ -160,17 +160,34 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
         float s[AP_BN / 8][4];
 #pragma unroll
         for (int nb = 0; nb < AP_BN / 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+        {
+            // S = Q K^T as KB * 4 steps of (one ldmatrix.x4 of K, two mma); fragments are fetched two
+            // steps ahead of the mma that uses them, so the shared-memory latency hides behind the math.
+            constexpr int NST = KB * (AP_BN / 16);
+            unsigned kf[3][4];
+            auto k_addr = [&](int st) {
+                const int kb = st / (AP_BN / 16), np = st % (AP_BN / 16);
+                return tile_at<D>(const_cast<bf16*>(kd), np * 16 + (lane & 7) + (lane >> 4) * 8, kb * 2 + ((lane >> 3) & 1));
+            };
+            ldmatrix_x4(kf[0], k_addr(0));
+            ldmatrix_x4(kf[1], k_addr(1));
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-#pragma unroll
-            for (int np = 0; np < AP_BN / 16; ++np) {               // two key blocks of 8 per ldmatrix.x4
-                unsigned b[4];
-                ldmatrix_x4(b, tile_at<D>(const_cast<bf16*>(kd), np * 16 + (lane & 7) + (lane >> 4) * 8,
-                                          kb * 2 + ((lane >> 3) & 1)));
-                mma_bf16(s[2 * np], qf[kb], b[0], b[1]);
-                mma_bf16(s[2 * np + 1], qf[kb], b[2], b[3]);
+            for (int st = 0; st < NST; ++st) {
+                if (st + 2 < NST) ldmatrix_x4(kf[(st + 2) % 3], k_addr(st + 2));
+                const int kb = st / (AP_BN / 16), np = st % (AP_BN / 16);
+                mma_bf16(s[2 * np], qf[kb], kf[st % 3][0], kf[st % 3][1]);
+                mma_bf16(s[2 * np + 1], qf[kb], kf[st % 3][2], kf[st % 3][3]);
             }
         }
+        // the first value fragments start their way now; the softmax arithmetic below covers them
+        constexpr int VST = (AP_BN / 16) * (D / 16);
+        unsigned vf[3][4];
+        auto v_addr = [&](int st) {
+            const int kb = st / (D / 16), np = st % (D / 16);
+            return tile_at<D>(const_cast<bf16*>(vd), kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4));
+        };
+        ldmatrix_x4_trans(vf[0], v_addr(0));
+        ldmatrix_x4_trans(vf[1], v_addr(1));
         // mask, scale into the exp2 domain, running max
         const bool need_mask = (kt + AP_BN - 1 > pos_first) || (window > 0);
         float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
@@ -222,17 +239,13 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
             o[nb][0] *= al0; o[nb][1] *= al0;
             o[nb][2] *= al1; o[nb][3] *= al1;
         }
-        // O += P V
+        // O += P V, value fragments two steps ahead
 #pragma unroll
-        for (int kb = 0; kb < AP_BN / 16; ++kb) {
-#pragma unroll
-            for (int np = 0; np < D / 16; ++np) {
-                unsigned b[4];
-                ldmatrix_x4_trans(b, tile_at<D>(const_cast<bf16*>(vd), kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                                np * 2 + (lane >> 4)));
-                mma_bf16(o[2 * np], pf[kb], b[0], b[1]);
-                mma_bf16(o[2 * np + 1], pf[kb], b[2], b[3]);
-            }
+        for (int st = 0; st < VST; ++st) {
+            if (st + 2 < VST) ldmatrix_x4_trans(vf[(st + 2) % 3], v_addr(st + 2));
+            const int kb = st / (D / 16), np = st % (D / 16);
+            mma_bf16(o[2 * np], pf[kb], vf[st % 3][0], vf[st % 3][1]);
+            mma_bf16(o[2 * np + 1], pf[kb], vf[st % 3][2], vf[st % 3][3]);
         }
     }
     cp_async_wait_all();
