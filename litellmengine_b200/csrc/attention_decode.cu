@@ -19,10 +19,10 @@
 // Built for head sizes 64 and 128 and groups up to 16; other sizes use the generic kernel.
 #include "common.cuh"
 #include <math_constants.h>
+#include <stdlib.h>
 
 #define AD_BN 64
 #define AD_THREADS 128
-#define AD_STAGES 3          // key/value tiles in shared memory: one being read, two in flight
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
@@ -57,7 +57,7 @@ __device__ __forceinline__ bf16* tile_at(bf16* base, int row, int chunk) {
     return base + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
-template <int D>
+template <int D, int AD_STAGES>
 __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ cache, const int32_t* __restrict__ rows,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
@@ -282,14 +282,14 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
     }
 }
 
-template <int D>
+template <int D, int AD_STAGES>
 static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, const int32_t* positions,
                          const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
                          int table_stride, float* part_acc, float* part_ml, bf16* out, int n_rows, int nq, int nkv,
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
                          cudaStream_t s) {
     const size_t smem = static_cast<size_t>(16 + 2 * AD_STAGES * AD_BN) * D * sizeof(bf16);
-    auto kern = paged_decode_attention_kernel<D>;
+    auto kern = paged_decode_attention_kernel<D, AD_STAGES>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -333,15 +333,30 @@ extern "C" int llm_paged_attention_decode(
     float* part_acc = scratch;
     float* part_ml = scratch ? scratch + static_cast<size_t>(n_rows) * nq * num_splits * d : nullptr;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (d == 64)
-        return launch_decode<64>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions,
-                                 token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,
-                                 static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages,
-                                 num_splits, status, s);
-    return launch_decode<128>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions,
-                              token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,
-                              static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages,
-                              num_splits, status, s);
+    // Tiles in shared memory: one being read, the rest in flight.  More in flight per SM is what
+    // brings the kernel closer to the memory bandwidth; the count is a tuning knob.
+    static int stages = 0;
+    if (stages == 0) {
+        const char* e = getenv("LLM_DECODE_STAGES");
+        stages = e ? atoi(e) : 3;
+        if (stages != 3 && stages != 4 && stages != 6 && stages != 7) stages = 3;
+    }
+#define GO(DD, SS)                                                                                              \
+    return launch_decode<DD, SS>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions, \
+                                 token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,         \
+                                 static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages, \
+                                 num_splits, status, s)
+    if (d == 64) {
+        if (stages == 7) GO(64, 7);
+        if (stages == 6) GO(64, 6);
+        if (stages == 4) GO(64, 4);
+        GO(64, 3);
+    }
+    if (stages == 7) GO(128, 7);
+    if (stages == 6) GO(128, 6);
+    if (stages == 4) GO(128, 4);
+    GO(128, 3);
+#undef GO
 }
 
 // ---- the entry point that allocates nothing (declared and explained in attention_decode_noalloc.h) ----
