@@ -90,20 +90,24 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const size_t v_shift = static_cast<size_t>(nkv) * head_stride;
     const int ld_row = tid >> 1, ld_half = tid & 1;                // a pair of threads copies one row
 
-    auto load_kv = [&](int kt, int buf) {
+    // The page number of this thread's row is looked up one tile ahead of the copy that needs it,
+    // so the table read's latency passes behind the arithmetic of a whole tile.
+    auto lookup = [&](int kt) -> int {
         const int key = kt + ld_row;
-        bool valid = key < k_end;
+        if (key >= k_end) return -2;                                // past the split: zero-fill
+        const int logical = key / page_size;
+        return logical < table_stride ? __ldg(table + logical) : -1;
+    };
+    auto load_kv = [&](int kt, int buf, int page) {
+        const int key = kt + ld_row;
+        bool valid = page >= 0;
         const bf16* src = cache;
-        if (valid) {
-            const int logical = key / page_size;
-            const int page = logical < table_stride ? table[logical] : -1;
-            if (page < 0 || page >= num_pages) {
-                if (atomicCAS(status, 0, 4) == 0) status[1] = t;
-                valid = false;
-            } else {
-                src = cache + static_cast<size_t>(page) * page_stride + kvh * head_stride +
-                      static_cast<size_t>(key - logical * page_size) * D;
-            }
+        if (page == -1 || page >= num_pages) {
+            if (atomicCAS(status, 0, 4) == 0) status[1] = t;
+            valid = false;
+        } else if (valid) {
+            src = cache + static_cast<size_t>(page) * page_stride + kvh * head_stride +
+                  static_cast<size_t>(key % page_size) * D;
         }
         bf16* kd = k_s + buf * AD_BN * D;
         bf16* vd = v_s + buf * AD_BN * D;
@@ -125,14 +129,15 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
                 cp_async16(tile_at<D>(q_s, ld_row, c), src + c * 8, valid);
             }
         }
-        load_kv(k_begin, 0);
+        load_kv(k_begin, 0, lookup(k_begin));
     }
     cp_async_commit();
 #pragma unroll
     for (int st = 1; st < AD_STAGES - 1; ++st) {
-        if (st < n_tiles) load_kv(k_begin + st * AD_BN, st);
+        if (st < n_tiles) load_kv(k_begin + st * AD_BN, st, lookup(k_begin + st * AD_BN));
         cp_async_commit();
     }
+    int page_ahead = (AD_STAGES - 1 < n_tiles) ? lookup(k_begin + (AD_STAGES - 1) * AD_BN) : -2;
 
     unsigned qf[KB][4];
     float o[D / 8][4];
@@ -144,8 +149,9 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
         const int kt = k_begin + it * AD_BN, buf = it % AD_STAGES;
         cp_async_wait<AD_STAGES - 2>();                             // tile `it` has landed; later ones may be in flight
         __syncthreads();                                            // and every warp is done with tile it-1's buffer
-        if (it + AD_STAGES - 1 < n_tiles) load_kv(kt + (AD_STAGES - 1) * AD_BN, (it + AD_STAGES - 1) % AD_STAGES);
+        if (it + AD_STAGES - 1 < n_tiles) load_kv(kt + (AD_STAGES - 1) * AD_BN, (it + AD_STAGES - 1) % AD_STAGES, page_ahead);
         cp_async_commit();
+        page_ahead = (it + AD_STAGES < n_tiles) ? lookup(kt + AD_STAGES * AD_BN) : -2;
         if (it == 0) {
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb)
