@@ -263,6 +263,8 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     }
 }
 
+#include "attention_decode_tma.cuh"
+
 // One block per (token row, query head): merge the splits (m in the base-2 domain).
 template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -301,9 +303,27 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     dim3 grid(num_splits, nkv, n_rows);
-    kern<<<grid, AD_THREADS, smem, s>>>(q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
-                                        part_acc, part_ml, out, nq, nkv, page_size, window,
-                                        scale * 1.4426950408889634f, num_pages, num_splits, status);
+    static int use_tma = -1;                                        // LLM_DECODE_TMA=0 keeps the cp.async kernel
+    if (use_tma < 0) {
+        const char* e = getenv("LLM_DECODE_TMA");
+        use_tma = (e && e[0] == '0') ? 0 : 1;
+    }
+    const CUtensorMap* map = (use_tma && decode_tma_page_ok(page_size))
+                                 ? kv_tensor_map(cache, num_pages, nkv, page_size, D) : nullptr;
+    if (map != nullptr) {
+        constexpr int TS = 3;
+        const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;
+        auto tk = paged_decode_attention_tma_kernel<D, TS>;
+        const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tsmem));
+        if (te != cudaSuccess) return static_cast<int>(te);
+        tk<<<grid, AD_THREADS + 32, tsmem, s>>>(*map, q, rows, positions, token_entry, entry_slot, block_table, table_stride,
+                                                part_acc, part_ml, out, nq, nkv, page_size, window,
+                                                scale * 1.4426950408889634f, num_pages, num_splits, status);
+    } else {
+        kern<<<grid, AD_THREADS, smem, s>>>(q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
+                                            part_acc, part_ml, out, nq, nkv, page_size, window,
+                                            scale * 1.4426950408889634f, num_pages, num_splits, status);
+    }
     int rc = launch_status();
     if (rc != LLM_OK || num_splits == 1) return rc;
     dim3 cgrid(n_rows, nq);

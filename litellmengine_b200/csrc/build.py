@@ -35,7 +35,7 @@ FAMILIES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu"],
     "gemm_skinny": ["gemm_skinny.cu"],
 }
-HEADERS = ["common.cuh", "attention_decode_noalloc.h"]
+HEADERS = ["common.cuh", "attention_decode_noalloc.h", "attention_decode_tma.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

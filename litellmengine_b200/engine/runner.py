@@ -19,7 +19,8 @@ from .batch import StepBatch, StepBuffers, StepEntry, pack_step
 STATUS_TEXT = {1: "a token id outside the vocabulary reached the embedding kernel",
                2: "a block-table update pointed outside the table",
                3: "the cache write met a page number outside the pool",
-               4: "attention met a page number outside the pool"}
+               4: "attention met a page number outside the pool",
+               5: "a wait on a copy barrier in the decode attention kernel ran out"}
 
 
 class ModelRunner:
