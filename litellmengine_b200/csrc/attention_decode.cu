@@ -311,14 +311,25 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
     const CUtensorMap* map = (use_tma && decode_tma_page_ok(page_size))
                                  ? kv_tensor_map(cache, num_pages, nkv, page_size, D) : nullptr;
     if (map != nullptr) {
-        constexpr int TS = 3;
-        const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;
-        auto tk = paged_decode_attention_tma_kernel<D, TS>;
-        const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tsmem));
-        if (te != cudaSuccess) return static_cast<int>(te);
-        tk<<<grid, AD_THREADS + 32, tsmem, s>>>(*map, q, rows, positions, token_entry, entry_slot, block_table, table_stride,
-                                                part_acc, part_ml, out, nq, nkv, page_size, window,
-                                                scale * 1.4426950408889634f, num_pages, num_splits, status);
+        static int ts = 0;                                          // tiles in shared memory for the TMA kernel
+        if (ts == 0) {
+            const char* e = getenv("LLM_DECODE_TMA_STAGES");
+            ts = e ? atoi(e) : 3;
+            if (ts != 3 && ts != 4 && ts != 6) ts = 3;
+        }
+#define TMA_GO(TS)                                                                                                   \
+    {                                                                                                                \
+        const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;                     \
+        auto tk = paged_decode_attention_tma_kernel<D, TS>;                                                          \
+        const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
+                                                    static_cast<int>(tsmem));                                        \
+        if (te != cudaSuccess) return static_cast<int>(te);                                                          \
+        tk<<<grid, AD_THREADS + 32, tsmem, s>>>(*map, q, rows, positions, token_entry, entry_slot, block_table,      \
+                                                table_stride, part_acc, part_ml, out, nq, nkv, page_size, window,    \
+                                                scale * 1.4426950408889634f, num_pages, num_splits, status);         \
+    }
+        if (ts == 6) TMA_GO(6) else if (ts == 4) TMA_GO(4) else TMA_GO(3)
+#undef TMA_GO
     } else {
         kern<<<grid, AD_THREADS, smem, s>>>(q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
                                             part_acc, part_ml, out, nq, nkv, page_size, window,
