@@ -119,7 +119,8 @@ def main():
         cache, table, q, pos, ent, slot = paged_setup(args, dev, 1)
         out = torch.empty_like(q)
         work = args.batch * nkv
-        splits = args.splits or max(1, min(32, -(-444 // work), -(-args.context // 128)))
+        slots = 2 * torch.cuda.get_device_properties(dev).multi_processor_count
+        splits = args.splits or max(1, min(16, slots // work, args.context // 256))
         fn = lambda: ops.paged_attention_decode(q, out, cache, None, args.batch, pos, ent, slot, table, nq, nkv, d, P,
                                                 None, scale, splits, status)
         nbytes = args.batch * args.context * 2 * nkv * d * 2

@@ -94,6 +94,16 @@ class AttentionMixer:
         return ops.linear(a, self.w_o, out_dtype=torch.float32)        # joins the float32 residual
 
 
+_slots = {}
+
+
+def _cta_slots(device) -> int:
+    n = _slots.get(device)
+    if n is None:
+        n = _slots[device] = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
 def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,
                          window: Optional[int], scale: float) -> torch.Tensor:
     """Pick the attention kernels for this batch.  Every choice reads the same pages and gives
@@ -106,8 +116,10 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
     if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and ops.fast_attention_supported(d, nq // nkv)):
         out = torch.empty_like(q)
         if b.num_decode:
+            # Key splits: as many as keep the whole grid resident at once (two CTAs per SM), since
+            # a second, partial wave costs more than it balances; at least 256 keys per split.
             work = b.num_decode * nkv
-            splits = max(1, min(32, -(-444 // work), -(-b.max_kv_len // 128)))
+            splits = max(1, min(16, _cta_slots(q.device) // work, b.max_kv_len // 256))
             ops.paged_attention_decode(q, out, cache, None if b.num_decode == b.num_tokens else b.decode_rows,
                                        b.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
                                        nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
