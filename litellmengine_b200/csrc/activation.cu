@@ -10,6 +10,7 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
 template <typename T>
 __global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                                     long long total) {
+    pdl_begin();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     if ((inter & 7) == 0) {
         const long long groups = total / 8;
@@ -44,10 +45,10 @@ extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_to
     const int blocks = static_cast<int>(std::min<long long>((work + threads - 1) / threads, 148LL * 16));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
-        silu_and_mul_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(gu),
+        launch_pdl((silu_and_mul_kernel<float>), dim3(blocks), dim3(threads), 0, s, static_cast<const float*>(gu),
                                                               static_cast<float*>(out), inter, total);
     else if (dtype == LLM_DT_BF16)
-        silu_and_mul_kernel<bf16><<<blocks, threads, 0, s>>>(static_cast<const bf16*>(gu),
+        launch_pdl((silu_and_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, static_cast<const bf16*>(gu),
                                                              static_cast<bf16*>(out), inter, total);
     else
         return LLM_REFUSED_DTYPE;
@@ -56,6 +57,7 @@ extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_to
 
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, long long n) {
+    pdl_begin();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride)
         h[i] += to_f32(delta[i]);
@@ -67,9 +69,9 @@ extern "C" int llm_residual_add(float* h, const void* delta, int delta_dtype, lo
     const int blocks = static_cast<int>(std::min<long long>((n + threads - 1) / threads, 148LL * 16));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (delta_dtype == LLM_DT_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, s>>>(h, static_cast<const float*>(delta), n);
+        launch_pdl((residual_add_kernel<float>), dim3(blocks), dim3(threads), 0, s, h, static_cast<const float*>(delta), n);
     else if (delta_dtype == LLM_DT_BF16)
-        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>(h, static_cast<const bf16*>(delta), n);
+        launch_pdl((residual_add_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, h, static_cast<const bf16*>(delta), n);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
     int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
+    pdl_begin();
     constexpr int CH = D / 8, KB = D / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][D]
@@ -270,6 +271,7 @@ template <int D>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                             const int32_t* __restrict__ rows, bf16* __restrict__ out, int nq,
                                             int num_splits) {
+    pdl_begin();
     const int r = blockIdx.x, h = blockIdx.y;
     const int t = rows ? rows[r] : r;
     const size_t hrow = static_cast<size_t>(r) * nq + h;
@@ -324,21 +326,21 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
         const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                                     static_cast<int>(tsmem));                                        \
         if (te != cudaSuccess) return static_cast<int>(te);                                                          \
-        tk<<<grid, AD_THREADS + 32, tsmem, s>>>(*map, q, rows, positions, token_entry, entry_slot, block_table,      \
+        launch_pdl(tk, dim3(grid), dim3(AD_THREADS + 32), tsmem, s, *map, q, rows, positions, token_entry, entry_slot, block_table,      \
                                                 table_stride, part_acc, part_ml, out, nq, nkv, page_size, window,    \
                                                 scale * 1.4426950408889634f, num_pages, num_splits, status);         \
     }
         if (ts == 6) TMA_GO(6) else if (ts == 4) TMA_GO(4) else TMA_GO(3)
 #undef TMA_GO
     } else {
-        kern<<<grid, AD_THREADS, smem, s>>>(q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
+        launch_pdl(kern, dim3(grid), dim3(AD_THREADS), smem, s, q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
                                             part_acc, part_ml, out, nq, nkv, page_size, window,
                                             scale * 1.4426950408889634f, num_pages, num_splits, status);
     }
     int rc = launch_status();
     if (rc != LLM_OK || num_splits == 1) return rc;
     dim3 cgrid(n_rows, nq);
-    paged_decode_combine_kernel<D><<<cgrid, D <= 64 ? 64 : 128, 0, s>>>(part_acc, part_ml, rows, out, nq, num_splits);
+    launch_pdl((paged_decode_combine_kernel<D>), cgrid, dim3(D <= 64 ? 64 : 128), 0, s, part_acc, part_ml, rows, out, nq, num_splits);
     return launch_status();
 }
 

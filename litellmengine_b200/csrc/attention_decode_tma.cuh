@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
     int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
+    pdl_begin();
     constexpr int CH = D / 8, KB = D / 16;
     constexpr int TILE = AD_BN * D;                                  // elements of one K (or V) tile
     extern __shared__ unsigned char smem_dyn[];

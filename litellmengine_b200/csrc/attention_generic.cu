@@ -28,6 +28,7 @@ __global__ void paged_attention_generic_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     int num_tokens, int nq, int nkv, int d, int page_size, int window, float scale, int num_pages,
     int32_t* __restrict__ status) {
+    pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = static_cast<long long>(blockIdx.x) * AG_WARPS + warp;
@@ -120,7 +121,7 @@ extern "C" int llm_paged_attention_generic(
     const unsigned blocks = static_cast<unsigned>((items + AG_WARPS - 1) / AG_WARPS);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(T, TC)                                                                              \
-    paged_attention_generic_kernel<T, TC><<<blocks, AG_WARPS * 32, smem, s>>>(                     \
+    launch_pdl((paged_attention_generic_kernel<T, TC>), dim3(blocks), dim3(AG_WARPS * 32), smem, s,                      \
         static_cast<const T*>(q), static_cast<T*>(out), static_cast<const TC*>(cache), positions,  \
         token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, page_size,     \
         window, scale, num_pages, status)

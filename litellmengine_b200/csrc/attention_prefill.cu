@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
     const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
     float scale_log2e, int num_pages, int32_t* __restrict__ status) {
+    pdl_begin();
     constexpr int CH = D / 8;                     // 16-byte chunks per row
     constexpr int KB = D / 16;                    // k-blocks of the first product
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -285,7 +286,7 @@ extern "C" int llm_paged_attention_prefill(
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                                    static_cast<int>(smem));                                    \
         if (e != cudaSuccess) return static_cast<int>(e);                                                      \
-        kern<<<grid, AP_THREADS, smem, s>>>(static_cast<const bf16*>(q), static_cast<bf16*>(out),              \
+        launch_pdl(kern, dim3(grid), dim3(AP_THREADS), smem, s, static_cast<const bf16*>(q), static_cast<bf16*>(out),              \
                                             static_cast<const bf16*>(cache), tiles, entry_slot, entry_q_start, \
                                             entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv,     \
                                             page_size, window, scale_log2e, num_pages, status);                \

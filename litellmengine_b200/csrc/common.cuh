@@ -88,6 +88,52 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Every kernel of the engine is launched with the "programmatic stream serialization" attribute
+// and begins with `pdl_begin()`: it lets the NEXT kernel in the stream be scheduled onto SMs
+// as they become free (instead of after this grid has completely drained) and then waits until
+// the PREVIOUS kernel has finished and its writes are visible.  A kernel that has work that does
+// not depend on its predecessor (the streaming product fetches weights) does that work between
+// the two halves.  Big grids do not invite their successor early: its blocks would only take
+// room from blocks of this grid that have not started yet.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_invite() {
+    if (gridDim.x * gridDim.y * gridDim.z <= 1184u) pdl_launch_dependents();
+}
+__device__ __forceinline__ void pdl_begin() {
+    pdl_invite();
+    pdl_wait();
+}
+
+#include <cstdlib>
+#include <utility>
+
+static inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("LLM_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+
 static inline int launch_status() {
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? LLM_OK : static_cast<int>(e);

@@ -10,6 +10,7 @@ template <typename T>
 __global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
                                         int32_t* __restrict__ status) {
+    pdl_begin();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + static_cast<size_t>(t) * hidden;
@@ -39,10 +40,10 @@ extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int t
     const int threads = hidden >= 2048 ? 256 : 128;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (table_dtype == LLM_DT_F32)
-        embedding_gather_kernel<float><<<num_tokens, threads, 0, s>>>(
+        launch_pdl((embedding_gather_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, 
             ids, static_cast<const float*>(table), out, hidden, vocab, status);
     else if (table_dtype == LLM_DT_BF16)
-        embedding_gather_kernel<bf16><<<num_tokens, threads, 0, s>>>(
+        launch_pdl((embedding_gather_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, 
             ids, static_cast<const bf16*>(table), out, hidden, vocab, status);
     else
         return LLM_REFUSED_DTYPE;
@@ -56,6 +57,7 @@ __global__ void scatter_int32_kernel(int32_t* __restrict__ dst, long long dst_le
                                      const int32_t* __restrict__ index, const int32_t* __restrict__ value,
                                      const int32_t* __restrict__ count, int max_count,
                                      int32_t* __restrict__ status) {
+    pdl_begin();
     const int n = min(*count, max_count);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const long long at = index[i];
@@ -73,7 +75,7 @@ extern "C" int llm_scatter_int32(int32_t* dst, long long dst_len, const int32_t*
     if (max_count <= 0) return LLM_OK;
     const int threads = 256;
     const int blocks = min((max_count + threads - 1) / threads, 64);
-    scatter_int32_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(scatter_int32_kernel, dim3(blocks), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), 
         dst, dst_len, index, value, count, max_count, status);
     return launch_status();
 }

@@ -61,16 +61,19 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
     const int nk = kt_end - kt_begin;
     constexpr int CPR = GS_BK / 8;                                       // 16-byte chunks per row of a stage
 
-    auto load_stage = [&](int i) {                                       // k-tile kt_begin + i into stage i % STAGES
+    auto load_w = [&](int i) {                                           // weights of k-tile kt_begin + i into stage i % STAGES
         const int k0 = (kt_begin + i) * GS_BK;
         bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
-        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
 #pragma unroll
         for (int j = 0; j < GS_ROWS * CPR / GS_THREADS; ++j) {
             const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
             const bool valid = (n0 + row < N) && (k0 + ch * 8 < K);
             gs_cp_async16(gs_at(ws, row, ch), w + (valid ? static_cast<size_t>(n0 + row) * K + k0 + ch * 8 : 0), valid);
         }
+    };
+    auto load_x = [&](int i) {                                           // the tokens' rows for the same k-tile
+        const int k0 = (kt_begin + i) * GS_BK;
+        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
 #pragma unroll
         for (int j = 0; j < MT * CPR / GS_THREADS; ++j) {
             const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
@@ -79,10 +82,17 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
         }
     };
 
+    // The weights do not depend on the kernel before this one: start streaming them at once, and
+    // only then wait for that kernel (whose output is x) to finish.
+    pdl_invite();
+#pragma unroll
+    for (int s = 0; s < GS_STAGES - 1; ++s)
+        if (s < nk) load_w(s);
+    pdl_wait();
 #pragma unroll
     for (int s = 0; s < GS_STAGES - 1; ++s) {
-        if (s < nk) load_stage(s);
-        gs_commit();
+        if (s < nk) load_x(s);
+        gs_commit();                                                     // group 0 also holds every weight copy above
     }
     float acc[MT / 8][4];
 #pragma unroll
@@ -91,7 +101,10 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
     for (int i = 0; i < nk; ++i) {
         gs_wait<GS_STAGES - 2>();
         __syncthreads();
-        if (i + GS_STAGES - 1 < nk) load_stage(i + GS_STAGES - 1);
+        if (i + GS_STAGES - 1 < nk) {
+            load_w(i + GS_STAGES - 1);
+            load_x(i + GS_STAGES - 1);
+        }
         gs_commit();
         bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
         bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
@@ -128,6 +141,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
 // y[tok, f] = sum over splits of partial[split, tok, f], in split order.
 template <typename TO>
 __global__ void linear_skinny_sum_kernel(const float* __restrict__ partial, TO* __restrict__ y, long long mn, int splits) {
+    pdl_begin();
     const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     if (i >= mn) return;
     float v = 0.0f;
@@ -175,11 +189,11 @@ static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, 
     int splits = skinny_splits(N, K);
     if (splits > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(splits) * M * N)) splits = 1;
     dim3 grid((N + GS_ROWS - 1) / GS_ROWS, splits);
-    kern<<<grid, GS_THREADS, smem, s>>>(x, w, static_cast<TO*>(y), scratch, M, N, K);
+    launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K);
     int rc = launch_status();
     if (rc != LLM_OK || splits == 1) return rc;
     const long long mn = static_cast<long long>(M) * N;
-    linear_skinny_sum_kernel<TO><<<static_cast<unsigned>((mn + 255) / 256), 256, 0, s>>>(scratch, static_cast<TO*>(y), mn, splits);
+    launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, splits);
     return launch_status();
 }
 

@@ -15,6 +15,7 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
                                const float* __restrict__ w, TO* __restrict__ out,
                                const int32_t* __restrict__ rows, int hidden, float eps,
                                int write_sum, int vec) {
+    pdl_begin();
     extern __shared__ __align__(16) float smem[];   // hidden floats (padded to 8) + 33 for the reduction
     float* v = smem;
     float* scratch = smem + ((hidden + 7) & ~7);
@@ -76,7 +77,7 @@ static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out,
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
-    kern<<<num_rows, threads, smem, s>>>(static_cast<TX*>(x), static_cast<const TD*>(delta), w,
+    launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, static_cast<TX*>(x), static_cast<const TD*>(delta), w,
                                          static_cast<TO*>(out), rows, hidden, eps, write_sum, vec);
     return launch_status();
 }

@@ -8,6 +8,7 @@ compiler or library surfaces as `BuildError`.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int32, c_longlong, c_uint32, c_uint64, c_void_p
 from typing import Dict, Optional
 
@@ -360,6 +361,7 @@ def skinny_scratch(device, floats: int) -> Optional[torch.Tensor]:
 
 
 SKINNY_MAX_ROWS = 16     # rows up to which `linear` may take the engine's own streaming kernel
+_SKINNY_POLICY = os.environ.get("LLM_SKINNY", "auto")     # all | auto | off: which products of few rows take it
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
@@ -395,7 +397,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
-            and x.shape[1] % 8 == 0 and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)):
+            and x.shape[1] % 8 == 0 and (_SKINNY_POLICY == "all" or (
+                _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
         return linear_skinny(x, weight, out_dtype or x.dtype)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())

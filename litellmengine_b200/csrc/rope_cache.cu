@@ -28,6 +28,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int rotary_dim, int num_tokens, int nq, int nkv, int d,
     int page_size, int has_kv, int num_pages, int32_t* __restrict__ status) {
+    pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
@@ -105,7 +106,7 @@ extern "C" int llm_qk_norm_rope_kv_write(
     const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(TI, T, TC)                                                                           \
-    qk_norm_rope_kv_write_kernel<TI, T, TC><<<blocks, RC_WARPS * 32, smem, s>>>(                    \
+    launch_pdl((qk_norm_rope_kv_write_kernel<TI, T, TC>), dim3(blocks), dim3(RC_WARPS * 32), smem, s,                     \
         static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions,    \
         token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq,      \
         rotary_dim, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status)

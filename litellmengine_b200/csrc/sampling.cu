@@ -65,6 +65,7 @@ __device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx*
 }
 
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, int32_t* __restrict__ out) {
+    pdl_begin();
     __shared__ MaxIdx sh[33];
     const MaxIdx r = block_argmax(logits + static_cast<size_t>(blockIdx.x) * vocab, vocab, sh);
     if (threadIdx.x == 0) out[blockIdx.x] = r.i;
@@ -75,6 +76,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int vocab, 
 // because `better` compares indices and chunks are index ranges.
 __global__ void argmax_chunks_kernel(const float* __restrict__ logits, int vocab, int chunk,
                                      float* __restrict__ part_val, int32_t* __restrict__ part_idx) {
+    pdl_begin();
     __shared__ MaxIdx sh[33];
     const int row = blockIdx.y, c0 = blockIdx.x * chunk, n = min(chunk, vocab - c0);
     MaxIdx r = block_argmax(logits + static_cast<size_t>(row) * vocab + c0, n, sh);
@@ -86,6 +88,7 @@ __global__ void argmax_chunks_kernel(const float* __restrict__ logits, int vocab
 
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
                                     int chunks, int32_t* __restrict__ out) {
+    pdl_begin();
     MaxIdx best = {-CUDART_INF_F, 0x7fffffff};
     for (int c = threadIdx.x; c < chunks; c += 32)
         best = better(best, MaxIdx{part_val[blockIdx.x * chunks + c], part_idx[blockIdx.x * chunks + c]});
@@ -115,21 +118,22 @@ extern "C" int llm_argmax_rows(const float* logits, int num_rows, int vocab, int
         chunks = (vocab + chunk - 1) / chunk;
     }
     if (chunks <= 1 || scratch == nullptr || num_rows > 65535) {
-        argmax_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, s>>>(logits, vocab, out);
+        launch_pdl(argmax_rows_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, s, logits, vocab, out);
         return launch_status();
     }
     float* part_val = static_cast<float*>(scratch);
     int32_t* part_idx = reinterpret_cast<int32_t*>(part_val + static_cast<size_t>(num_rows) * chunks);
-    argmax_chunks_kernel<<<dim3(chunks, num_rows), 256, 0, s>>>(logits, vocab, chunk, part_val, part_idx);
+    launch_pdl(argmax_chunks_kernel, dim3(dim3(chunks, num_rows)), dim3(256), 0, s, logits, vocab, chunk, part_val, part_idx);
     int rc = launch_status();
     if (rc != LLM_OK) return rc;
-    argmax_merge_kernel<<<num_rows, 32, 0, s>>>(part_val, part_idx, chunks, out);
+    launch_pdl(argmax_merge_kernel, dim3(num_rows), dim3(32), 0, s, part_val, part_idx, chunks, out);
     return launch_status();
 }
 
 __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
                                    const int32_t* __restrict__ row_slot, int32_t* __restrict__ sampler_state,
                                    int32_t* __restrict__ out) {
+    pdl_begin();
     __shared__ MaxIdx sh[33];
     __shared__ float fs[33];
     __shared__ float warp_tot[32];
@@ -189,7 +193,7 @@ extern "C" int llm_sample_rows(const float* logits, int num_rows, int vocab, con
                                int32_t* sampler_state, int32_t* out, uintptr_t stream) {
     if (num_rows <= 0) return LLM_OK;
     if (vocab <= 0) return LLM_REFUSED_SIZE;
-    sample_rows_kernel<<<num_rows, SAMPLE_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(sample_rows_kernel, dim3(num_rows), dim3(SAMPLE_THREADS), 0, reinterpret_cast<cudaStream_t>(stream), 
         logits, vocab, row_slot, sampler_state, out);
     return launch_status();
 }
