@@ -172,9 +172,22 @@ extern "C" long long llm_linear_skinny_scratch_floats(int M, int N, int K) {
     return s > 1 ? static_cast<long long>(s) * M * N : 0;
 }
 
+// The number of k-splits a product of these sizes is cut into on the current device.
+extern "C" int llm_linear_skinny_splits(int M, int N, int K) {
+    if (g_skinny_slots == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            return 1;
+        g_skinny_slots = sms * 2;
+    }
+    (void)M;
+    return skinny_splits(N, K);
+}
+
 template <int MT, typename TO>
 static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, long long scratch_floats, int M, int N,
-                         int K, cudaStream_t s) {
+                         int K, int keep_partials, cudaStream_t s) {
     if (g_skinny_slots == 0) {
         int dev = 0, sms = 0;
         if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -191,7 +204,7 @@ static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, 
     dim3 grid((N + GS_ROWS - 1) / GS_ROWS, splits);
     launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K);
     int rc = launch_status();
-    if (rc != LLM_OK || splits == 1) return rc;
+    if (rc != LLM_OK || splits == 1 || keep_partials) return rc;     // the caller's next kernel adds the splits itself
     const long long mn = static_cast<long long>(M) * N;
     launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, splits);
     return launch_status();
@@ -199,19 +212,21 @@ static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, 
 
 // x: bfloat16 [M, K]; w: bfloat16 [N, K]; y: [M, N] float32 (out_dtype 0) or bfloat16 (1);
 // scratch: float32 of scratch_floats elements (without enough scratch K is not split).
+// keep_partials: with more than one split, leave the splits' sums in scratch as [splits, M, N]
+// and write nothing to y (llm_linear_skinny_splits tells the count beforehand).
 extern "C" int llm_linear_skinny(const void* x, const void* w, void* y, int out_dtype, float* scratch,
-                                 long long scratch_floats, int M, int N, int K, uintptr_t stream) {
+                                 long long scratch_floats, int M, int N, int K, int keep_partials, uintptr_t stream) {
     if (!llm_linear_skinny_supported(M, N, K)) return LLM_REFUSED_SIZE;
     if (!aligned16(x) || !aligned16(w)) return LLM_REFUSED_ALIGN;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bf16* xp = static_cast<const bf16*>(x);
     const bf16* wp = static_cast<const bf16*>(w);
     if (M <= 8) {
-        if (out_dtype == LLM_DT_F32) return launch_skinny<8, float>(xp, wp, y, scratch, scratch_floats, M, N, K, s);
-        if (out_dtype == LLM_DT_BF16) return launch_skinny<8, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, s);
+        if (out_dtype == LLM_DT_F32) return launch_skinny<8, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
+        if (out_dtype == LLM_DT_BF16) return launch_skinny<8, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
     } else {
-        if (out_dtype == LLM_DT_F32) return launch_skinny<16, float>(xp, wp, y, scratch, scratch_floats, M, N, K, s);
-        if (out_dtype == LLM_DT_BF16) return launch_skinny<16, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, s);
+        if (out_dtype == LLM_DT_F32) return launch_skinny<16, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
+        if (out_dtype == LLM_DT_BF16) return launch_skinny<16, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
     }
     return LLM_REFUSED_DTYPE;
 }

@@ -14,7 +14,7 @@ template <typename TX, typename TD, typename TO>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
                                const float* __restrict__ w, TO* __restrict__ out,
                                const int32_t* __restrict__ rows, int hidden, float eps,
-                               int write_sum, int vec) {
+                               int write_sum, int vec, int delta_parts, long long delta_part_stride) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];   // hidden floats (padded to 8) + 33 for the reduction
     float* v = smem;
@@ -29,10 +29,12 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
             float a[8];
             load8(xr + h, a);
             if (dr) {
-                float b[8];
-                load8(dr + h, b);
+                for (int part = 0; part < delta_parts; ++part) {    // delta may come as the k-splits of a product
+                    float b[8];
+                    load8(dr + part * delta_part_stride + h, b);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) a[i] += b[i];
+                    for (int i = 0; i < 8; ++i) a[i] += b[i];
+                }
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss += a[i] * a[i];
@@ -42,7 +44,8 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
     } else {
         for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
             float a = to_f32(xr[h]);
-            if (dr) a += to_f32(dr[h]);
+            if (dr)
+                for (int part = 0; part < delta_parts; ++part) a += to_f32(dr[part * delta_part_stride + h]);
             v[h] = a;
             ss += a * a;
             if (write_sum) xr[h] = from_f32<TX>(a);
@@ -66,7 +69,8 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
 
 template <typename TX, typename TD, typename TO>
 static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out, const int32_t* rows,
-                          int num_rows, int hidden, float eps, int write_sum, cudaStream_t s) {
+                          int num_rows, int hidden, float eps, int write_sum, int delta_parts,
+                          long long delta_part_stride, cudaStream_t s) {
     const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33) * sizeof(float);
     const int vec = (hidden % 8 == 0) && aligned16(x) && aligned16(out) && aligned16(w) && (!delta || aligned16(delta));
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
@@ -78,15 +82,17 @@ static int launch_rmsnorm(void* x, const void* delta, const float* w, void* out,
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
     launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, static_cast<TX*>(x), static_cast<const TD*>(delta), w,
-                                         static_cast<TO*>(out), rows, hidden, eps, write_sum, vec);
+                                         static_cast<TO*>(out), rows, hidden, eps, write_sum, vec, delta_parts, delta_part_stride);
     return launch_status();
 }
 
 // x: [*, hidden] (x_dtype), delta: same shape or null (delta_dtype), w: float32 [hidden],
-// out: [num_rows, hidden] (out_dtype), rows: int32 [num_rows] or null.
+// out: [num_rows, hidden] (out_dtype), rows: int32 [num_rows] or null.  delta may be given as
+// delta_parts tensors of x's shape, delta_part_stride elements apart, that are added up on the fly.
 extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dtype, const float* w,
                            void* out, int out_dtype, const int32_t* rows, int num_rows, int hidden,
-                           float eps, int write_sum, uintptr_t stream) {
+                           float eps, int write_sum, int delta_parts, long long delta_part_stride,
+                           uintptr_t stream) {
     if (num_rows <= 0) return LLM_OK;
     if (hidden <= 0) return LLM_REFUSED_SIZE;
     if (write_sum && rows) return LLM_REFUSED_SIZE;
@@ -95,7 +101,8 @@ extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dt
     const int key = x_dtype * 4 + delta_dtype * 2 + out_dtype;
 #define CASE(k, TX, TD, TO)                                                                     \
     case k:                                                                                       \
-        return launch_rmsnorm<TX, TD, TO>(x, delta, w, out, rows, num_rows, hidden, eps, write_sum, s);
+        return launch_rmsnorm<TX, TD, TO>(x, delta, w, out, rows, num_rows, hidden, eps, write_sum,       \
+                                          delta_parts < 1 ? 1 : delta_parts, delta_part_stride, s);
     switch (key) {
         CASE(0, float, float, float)
         CASE(1, float, float, bf16)

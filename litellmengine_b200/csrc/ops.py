@@ -49,6 +49,27 @@ def _fn(family: str, name: str, argtypes, restype=c_int):
     return f
 
 
+class PartialSum:
+    """A product left as its k-splits: float32 [splits, rows, cols] whose sum over the first axis
+    is the result.  The engine's norm and q/k kernels add the splits while they read, which
+    saves a kernel per product in decode steps; `as_tensor` adds them for anyone else."""
+
+    def __init__(self, parts: torch.Tensor):
+        self.parts = parts
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def dtype(self):
+        return self.parts.dtype
+
+
+def as_tensor(x):
+    return x.parts.sum(dim=0) if isinstance(x, PartialSum) else x
+
+
 launch_count = 0          # launches of the engine's own kernels since import (library products are not counted)
 
 
@@ -125,6 +146,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
             write_sum: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = rmsnorm(x (+ delta)) * weight over the last dim; with `write_sum`, x += delta in place.
     `rows` (int32) selects which rows are normalised (out has len(rows) rows)."""
+    parts, part_stride = 1, 0
+    if isinstance(delta, PartialSum):
+        parts, part_stride = delta.parts.shape[0], delta.parts.stride(0)
+        delta = delta.parts[0]
     _dev(x, weight, delta, rows, out)
     _i32(rows, "rows")
     H = x.shape[-1]
@@ -137,9 +162,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         out = torch.empty((n, H), dtype=out_dtype, device=x.device)
     f = _fn("norm", "llm_rmsnorm",
             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
-             c_int, c_void_p])
+             c_int, c_int, c_longlong, c_void_p])
     _check(f(_ptr(x), _dt(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight), _ptr(out),
-             _dt(out), _ptr(rows), n, H, float(eps), 1 if write_sum else 0, _stream()), "rmsnorm")
+             _dt(out), _ptr(rows), n, H, float(eps), 1 if write_sum else 0, parts, part_stride, _stream()), "rmsnorm")
     return out
 
 
@@ -157,6 +182,7 @@ def silu_and_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> t
 
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """h (float32) += delta, in place."""
+    delta = as_tensor(delta)
     _dev(h, delta)
     if h.dtype != torch.float32 or h.shape != delta.shape:
         raise KernelError("residual_add wants a float32 residual and a delta of its shape")
@@ -173,6 +199,10 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
     """Normalise and rotate q and k, write k and v into the cache pages, return q [T, nq*d]
     in `q_dtype` (default: qkv's).
     cache: [num_pages, 2, nkv, page_size, d] of one stage (None with has_kv False)."""
+    parts, part_stride = 1, 0
+    if isinstance(qkv, PartialSum):
+        parts, part_stride = qkv.parts.shape[0], qkv.parts.stride(0)
+        qkv = qkv.parts[0]
     _dev(qkv, cache, positions, token_entry, entry_slot, block_table, q_norm_w, k_norm_w, inv_freq, status, q_out)
     for t, n in ((positions, "positions"), (token_entry, "token_entry"), (entry_slot, "entry_slot"),
                  (block_table, "block_table")):
@@ -194,13 +224,14 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
     f = _fn("rope_cache", "llm_qk_norm_rope_kv_write",
             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p])
+             c_void_p, c_int, c_longlong, c_void_p])
     _check(f(_ptr(qkv), _dt(qkv), _ptr(q_out), _dt(q_out), _ptr(cache),
              _dt(cache) if cache is not None else _dt(q_out),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
              _ptr(inv_freq), rotary_dim if inv_freq is not None else 0, T, nq, nkv, d, page_size,
-             1 if has_kv else 0, cache.shape[0] if cache is not None else 0, _ptr(status), _stream()),
+             1 if has_kv else 0, cache.shape[0] if cache is not None else 0, _ptr(status), parts, part_stride,
+             _stream()),
            "qk_norm_rope_kv_write")
     return q_out
 
@@ -365,9 +396,10 @@ _SKINNY_POLICY = os.environ.get("LLM_SKINNY", "all")     # all | auto | off: whi
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, partials_ok: bool = False):
     """x [M <= 16, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16
-    operands, float32 accumulation, float32 or bfloat16 result)."""
+    operands, float32 accumulation, float32 or bfloat16 result).  With `partials_ok` a product
+    that is cut into k-splits comes back as a `PartialSum` instead of being added up."""
     _dev(x, weight, out)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("the skinny product takes bfloat16 operands")
@@ -375,20 +407,25 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     N = weight.shape[0]
     if weight.shape[1] != K:
         raise KernelError("x and weight disagree on K")
+    global launch_count
+    f = _fn("gemm_skinny", "llm_linear_skinny",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    splits = _fn("gemm_skinny", "llm_linear_skinny_splits", [c_int, c_int, c_int])(M, N, K)
+    if partials_ok and splits > 1 and out is None and out_dtype == torch.float32:
+        parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        _check(f(_ptr(x), _ptr(weight), None, 0, _ptr(parts), parts.numel(), M, N, K, 1, _stream()), "linear_skinny")
+        return PartialSum(parts)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    need = _fn("gemm_skinny", "llm_linear_skinny_scratch_floats", [c_int, c_int, c_int], restype=c_longlong)(M, N, K)
-    scratch = skinny_scratch(x.device, int(need))
-    f = _fn("gemm_skinny", "llm_linear_skinny",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    scratch = skinny_scratch(x.device, splits * M * N if splits > 1 else 0)
     _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
-             M, N, K, _stream()), "linear_skinny")
-    global launch_count
-    launch_count += 1 if need else 0              # the kernel that adds the k-splits
+             M, N, K, 0, _stream()), "linear_skinny")
+    launch_count += 1 if splits > 1 else 0        # the kernel that adds the k-splits
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           partials_ok: bool = False):
     """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's
     own weight-streaming kernel: alone it is level with the library for N = 4096..24576 and
     faster for K = 12288 (32 us against 36) and N = 151936 (203 against 218), and in a step it
@@ -401,7 +438,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
             and x.shape[1] % 8 == 0 and (_SKINNY_POLICY == "all" or (
                 _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
-        return linear_skinny(x, weight, out_dtype or x.dtype)
+        return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
         want = out_dtype or x.dtype

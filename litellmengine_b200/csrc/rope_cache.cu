@@ -27,7 +27,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int rotary_dim, int num_tokens, int nq, int nkv, int d,
-    int page_size, int has_kv, int num_pages, int32_t* __restrict__ status) {
+    int page_size, int has_kv, int num_pages, int32_t* __restrict__ status, int qkv_parts,
+    long long qkv_part_stride) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -41,7 +42,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
 
     float ss = 0.0f;
     for (int i = lane; i < d; i += 32) {
-        const float v = to_f32(src[i]);
+        float v = to_f32(src[i]);
+        for (int part = 1; part < qkv_parts; ++part) v += to_f32(src[part * qkv_part_stride + i]);   // k-splits of the product
         x[i] = v;
         ss += v * v;
     }
@@ -94,7 +96,7 @@ extern "C" int llm_qk_norm_rope_kv_write(
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rotary_dim,
     int num_tokens, int nq, int nkv, int d, int page_size, int has_kv, int num_pages, int32_t* status,
-    uintptr_t stream) {
+    int qkv_parts, long long qkv_part_stride, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > d ||
         (rotary_dim & 1))
@@ -109,7 +111,8 @@ extern "C" int llm_qk_norm_rope_kv_write(
     launch_pdl((qk_norm_rope_kv_write_kernel<TI, T, TC>), dim3(blocks), dim3(RC_WARPS * 32), smem, s,                     \
         static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions,    \
         token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq,      \
-        rotary_dim, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status)
+        rotary_dim, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status,                    \
+        qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride)
     const int key = qkv_dtype * 4 + q_dtype * 2 + cache_dtype;
     if (key == 0) LAUNCH(float, float, float);
     else if (key == 3) LAUNCH(float, bf16, bf16);

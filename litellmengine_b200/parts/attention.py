@@ -78,7 +78,7 @@ class AttentionMixer:
 
     def forward(self, x: torch.Tensor, ctx: StageContext) -> torch.Tensor:
         b = ctx.batch
-        qkv = ops.linear(x, self.w_qkv, out_dtype=torch.float32)    # normalised and rotated in 32-bit
+        qkv = ops.linear(x, self.w_qkv, out_dtype=torch.float32, partials_ok=True)   # normalised, rotated in 32-bit
         has_kv = self.spec.has_kv and ctx.writes_cache
         if self.spec.has_kv and not ctx.writes_cache:
             raise RuntimeError("a mixer with its own keys and values was given a borrowed cache")
@@ -91,7 +91,8 @@ class AttentionMixer:
             self.position.inv_freq, self.position.rotary_dim, self.nq, self.nkv, self.d,
             ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype)
         a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
-        return ops.linear(a, self.w_o, out_dtype=torch.float32)        # joins the float32 residual
+        # joins the float32 residual; may stay a sum of k-splits if the layer's norm adds them itself
+        return ops.linear(a, self.w_o, out_dtype=torch.float32, partials_ok=getattr(ctx, "partials_ok", False))
 
 
 _slots = {}

@@ -54,8 +54,15 @@ def pre_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: 
     that has not been added yet.  Each add is fused into the norm that follows it, so the
     layer returns its own feed-forward output as the next pending delta.
     """
+    from ..csrc import ops
+    if not getattr(block.mixer_norm, "accepts_partials", False):
+        delta = ops.as_tensor(delta)
     x = block.mixer_norm.forward(h, block.dtype, delta=delta, write_sum=delta is not None)
+    ctx.partials_ok = getattr(block.feed_forward_norm, "accepts_partials", False)
     a = block.mixer.forward(x, ctx)
     y = block.feed_forward_norm.forward(h, block.dtype, delta=a, write_sum=True)
-    f = block.feed_forward.forward(y)
+    if getattr(block.feed_forward, "supports_partials", False):
+        f = block.feed_forward.forward(y, partials_ok=True)     # the next norm (or `pre_norm` above) adds the splits
+    else:
+        f = block.feed_forward.forward(y)
     return h, f

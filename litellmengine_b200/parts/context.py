@@ -21,6 +21,8 @@ class StageContext:
     writes_cache False when the cache belongs to another stage.
     state        [slots, *shape] tensor if the mixer asked for fixed-size state, else None.
     status       device int32 [2] where kernels record a refused index instead of trapping.
+    partials_ok  True when whoever consumes the mixer's output adds up an `ops.PartialSum`
+                 itself, so the mixer may return one instead of a tensor.
     """
     batch: Any
     stage: int
@@ -30,3 +32,4 @@ class StageContext:
     writes_cache: bool
     state: Optional[torch.Tensor]
     status: torch.Tensor
+    partials_ok: bool = False

@@ -36,6 +36,9 @@ class SwiGLU:
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = t["down_proj.weight"].contiguous()
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    supports_partials = True   # forward(x, partials_ok=True) may return an ops.PartialSum
+
+    def forward(self, x: torch.Tensor, partials_ok: bool = False):
         gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype)
-        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=torch.float32)   # joins the residual
+        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=torch.float32,
+                          partials_ok=partials_ok)                                    # joins the residual

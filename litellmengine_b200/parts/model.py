@@ -104,6 +104,8 @@ class Model:
             h, delta = block.forward(h, delta, self.stage_context(s, batch, cache))
         if batch.num_want == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        if not getattr(self.final_norm, "accepts_partials", False):
+            delta = ops.as_tensor(delta)
         hn = self.final_norm.forward(h, self.dtype, delta=delta, rows=batch.want_rows)
         return ops.linear(hn, self.output, out_dtype=torch.float32)
 

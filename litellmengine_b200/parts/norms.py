@@ -16,6 +16,8 @@ class RMSNorm:
     """out = v * rsqrt(mean(v^2) + eps) * weight with v = x (+ delta), everything in 32-bit
     (src/layers/rms_norm.cu:77-93).  The weight multiplies directly (no 1 + w)."""
 
+    accepts_partials = True    # `delta` may be an ops.PartialSum: the kernel adds the k-splits as it reads
+
     def __init__(self, spec: NormSpec, size: int):
         self.eps = float(spec.eps)
         self.size = size

@@ -22,6 +22,11 @@ changes.  The interfaces:
                  forward(x [T, hidden]) -> [T, hidden]
   arrangement    a function (block, h, delta, ctx) -> (h, delta) wiring a layer's parts
 
+In decode steps a product may be returned as `ops.PartialSum` (its k-splits, not yet added) to
+a consumer that says it adds them itself: a norm with `accepts_partials = True` (its `delta`
+may then be one), a feed-forward with `supports_partials = True` (it is then called with
+`partials_ok=True`), a mixer through `ctx.partials_ok`.  Parts that say nothing never see one.
+
 A mixer or feed-forward whose forward only launches kernels on the current stream (no host
 reads, no loops over host data) may set the class attribute `graph_safe = True`; decode steps
 of a model whose parts all do are replayed as CUDA graphs.
