@@ -7,49 +7,45 @@
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
 
+// grid (blocks along the row, tokens): a thread takes 8 consecutive features of one token.
 template <typename T>
-__global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
-                                    long long total) {
+__global__ void silu_and_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
     pdl_begin();
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const size_t t = blockIdx.y;
+    const T* g = gu + t * 2 * inter;
+    const T* u = g + inter;
+    T* o = out + t * inter;
     if ((inter & 7) == 0) {
-        const long long groups = total / 8;
-        const int per_row = inter / 8;
-        for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < groups; g += stride) {
-            const long long t = g / per_row;
-            const int i = static_cast<int>(g - t * per_row) * 8;
+        const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+        if (i < inter) {
             float a[8], b[8], r[8];
-            load8(gu + t * 2 * inter + i, a);
-            load8(gu + t * 2 * inter + inter + i, b);
+            load8(g + i, a);
+            load8(u + i, b);
 #pragma unroll
             for (int k = 0; k < 8; ++k) r[k] = silu(a[k]) * b[k];
-            store8(out + t * inter + i, r);
+            store8(o + i, r);
         }
     } else {
-        for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total; e += stride) {
-            const long long t = e / inter;
-            const int i = static_cast<int>(e - t * inter);
-            out[e] = from_f32<T>(silu(to_f32(gu[t * 2 * inter + i])) * to_f32(gu[t * 2 * inter + inter + i]));
-        }
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter; i += gridDim.x * blockDim.x)
+            o[i] = from_f32<T>(silu(to_f32(g[i])) * to_f32(u[i]));
     }
 }
 
 extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_tokens, int inter,
                                 uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (inter <= 0) return LLM_REFUSED_SIZE;
+    if (inter <= 0 || num_tokens > 65535) return LLM_REFUSED_SIZE;
     if ((inter & 7) == 0 && (!aligned16(gu) || !aligned16(out))) return LLM_REFUSED_ALIGN;
-    const long long total = static_cast<long long>(num_tokens) * inter;
     const int threads = 256;
-    const long long work = (inter & 7) == 0 ? total / 8 : total;
-    const int blocks = static_cast<int>(std::min<long long>((work + threads - 1) / threads, 148LL * 16));
+    const int per_row = (inter & 7) == 0 ? inter / 8 : inter;
+    const dim3 grid(std::min((per_row + threads - 1) / threads, 4096), num_tokens);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
-        launch_pdl((silu_and_mul_kernel<float>), dim3(blocks), dim3(threads), 0, s, static_cast<const float*>(gu),
-                                                              static_cast<float*>(out), inter, total);
+        launch_pdl((silu_and_mul_kernel<float>), grid, dim3(threads), 0, s, static_cast<const float*>(gu),
+                   static_cast<float*>(out), inter);
     else if (dtype == LLM_DT_BF16)
-        launch_pdl((silu_and_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, static_cast<const bf16*>(gu),
-                                                             static_cast<bf16*>(out), inter, total);
+        launch_pdl((silu_and_mul_kernel<bf16>), grid, dim3(threads), 0, s, static_cast<const bf16*>(gu),
+                   static_cast<bf16*>(out), inter);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();
