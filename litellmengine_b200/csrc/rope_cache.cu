@@ -14,12 +14,11 @@
 // (the address rule of src/engine/block_table_manager.cpp:91-122, with the tables on the device).
 // A page number outside [0, num_pages) is recorded in `status` and the write is skipped.
 //
-// One warp handles one (token, head), in registers.  Norm weights and inv_freq may be null (no norm, no
+// One warp handles one (token, head).  Norm weights and inv_freq may be null (no norm, no
 // rotation); rotary_dim <= head_dim.  With has_kv == 0 the input holds only queries.
 #include "common.cuh"
 
 #define RC_WARPS 4
-#define RC_MAX_PAIRS 4        // pairs per lane: head sizes up to 256
 
 template <typename TI, typename T, typename TC>
 __global__ void qk_norm_rope_kv_write_kernel(
@@ -31,95 +30,49 @@ __global__ void qk_norm_rope_kv_write_kernel(
     int page_size, int has_kv, int num_pages, int32_t* __restrict__ status, int qkv_parts,
     long long qkv_part_stride) {
     pdl_begin();
+    extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
     const long long item = static_cast<long long>(blockIdx.x) * RC_WARPS + warp;
     if (item >= static_cast<long long>(num_tokens) * heads_total) return;
     const int t = static_cast<int>(item / heads_total);
     const int head = static_cast<int>(item - static_cast<long long>(t) * heads_total);
+    float* x = smem + warp * d;
     const TI* src = qkv + static_cast<size_t>(t) * heads_total * d + static_cast<size_t>(head) * d;
+
+    float ss = 0.0f;
+    for (int i = lane; i < d; i += 32) {
+        float v = to_f32(src[i]);
+        for (int part = 1; part < qkv_parts; ++part) v += to_f32(src[part * qkv_part_stride + i]);   // k-splits of the product
+        x[i] = v;
+        ss += v * v;
+    }
+    __syncwarp();
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
-    const int half = rotary_dim >> 1;
-
-    // A lane keeps rotation pairs (i, i + half), i = lane + 32 j, in registers, and the
-    // unrotated tail [rotary_dim, d) in strides of 32 as well: nothing goes through shared memory.
-    float lo[RC_MAX_PAIRS], hi[RC_MAX_PAIRS], tail[RC_MAX_PAIRS * 2];
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < RC_MAX_PAIRS; ++j) {
-        const int i = lane + 32 * j;
-        lo[j] = hi[j] = 0.0f;
-        if (i < half) {
-            float a = to_f32(src[i]), b = to_f32(src[i + half]);
-            for (int part = 1; part < qkv_parts; ++part) {            // k-splits of the product
-                a += to_f32(src[part * qkv_part_stride + i]);
-                b += to_f32(src[part * qkv_part_stride + i + half]);
-            }
-            lo[j] = a;
-            hi[j] = b;
-            ss += a * a + b * b;
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < RC_MAX_PAIRS * 2; ++j) {
-        const int i = rotary_dim + lane + 32 * j;
-        tail[j] = 0.0f;
-        if (i < d) {
-            float a = to_f32(src[i]);
-            for (int part = 1; part < qkv_parts; ++part) a += to_f32(src[part * qkv_part_stride + i]);
-            tail[j] = a;
-            ss += a * a;
-        }
-    }
     const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
     if (nw) {
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / static_cast<float>(d) + eps);
-#pragma unroll
-        for (int j = 0; j < RC_MAX_PAIRS; ++j) {
-            const int i = lane + 32 * j;
-            if (i < half) {
-                lo[j] = lo[j] * inv * nw[i];
-                hi[j] = hi[j] * inv * nw[i + half];
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < RC_MAX_PAIRS * 2; ++j) {
-            const int i = rotary_dim + lane + 32 * j;
-            if (i < d) tail[j] = tail[j] * inv * nw[i];
-        }
+        for (int i = lane; i < d; i += 32) x[i] = x[i] * inv * nw[i];
+        __syncwarp();
     }
     const int pos = positions[t];
     if ((is_q || is_k) && inv_freq) {
-#pragma unroll
-        for (int j = 0; j < RC_MAX_PAIRS; ++j) {
-            const int i = lane + 32 * j;
-            if (i < half) {
-                const float ang = static_cast<float>(pos) * inv_freq[i];
-                float s, c;
-                sincosf(ang, &s, &c);
-                const float x1 = lo[j], x2 = hi[j];
-                lo[j] = x1 * c - x2 * s;
-                hi[j] = x2 * c + x1 * s;
-            }
+        const int half = rotary_dim >> 1;
+        for (int i = lane; i < half; i += 32) {
+            const float ang = static_cast<float>(pos) * inv_freq[i];
+            float s, c;
+            sincosf(ang, &s, &c);
+            const float x1 = x[i], x2 = x[i + half];
+            x[i] = x1 * c - x2 * s;
+            x[i + half] = x2 * c + x1 * s;
         }
+        __syncwarp();
     }
     if (is_q) {
         T* dst = q_out + static_cast<size_t>(t) * nq * d + static_cast<size_t>(head) * d;
-#pragma unroll
-        for (int j = 0; j < RC_MAX_PAIRS; ++j) {
-            const int i = lane + 32 * j;
-            if (i < half) {
-                dst[i] = from_f32<T>(lo[j]);
-                dst[i + half] = from_f32<T>(hi[j]);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < RC_MAX_PAIRS * 2; ++j) {
-            const int i = rotary_dim + lane + 32 * j;
-            if (i < d) dst[i] = from_f32<T>(tail[j]);
-        }
+        for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(x[i]);
         return;
     }
     const int kv_head = is_k ? head - nq : head - nq - nkv;
@@ -133,21 +86,10 @@ __global__ void qk_norm_rope_kv_write_kernel(
     }
     TC* dst = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * nkv + kv_head) * page_size * d +
               static_cast<size_t>(pos % page_size) * d;
-#pragma unroll
-    for (int j = 0; j < RC_MAX_PAIRS; ++j) {
-        const int i = lane + 32 * j;
-        if (i < half) {
-            dst[i] = from_f32<TC>(lo[j]);
-            dst[i + half] = from_f32<TC>(hi[j]);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < RC_MAX_PAIRS * 2; ++j) {
-        const int i = rotary_dim + lane + 32 * j;
-        if (i < d) dst[i] = from_f32<TC>(tail[j]);
-    }
+    for (int i = lane; i < d; i += 32) dst[i] = from_f32<TC>(x[i]);
 }
 
+// qkv: [T, heads_total * d] (qkv_dtype); q_out: [T, nq * d] (q_dtype); cache (cache_dtype).
 extern "C" int llm_qk_norm_rope_kv_write(
     const void* qkv, int qkv_dtype, void* q_out, int q_dtype, void* cache, int cache_dtype,
     const int32_t* positions,
@@ -159,8 +101,8 @@ extern "C" int llm_qk_norm_rope_kv_write(
     if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > d ||
         (rotary_dim & 1))
         return LLM_REFUSED_SIZE;
-    if (d > 64 * RC_MAX_PAIRS) return LLM_REFUSED_SIZE;
-    const size_t smem = 0;
+    const size_t smem = static_cast<size_t>(RC_WARPS) * d * sizeof(float);
+    if (smem > 48 * 1024) return LLM_REFUSED_SIZE;
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
     const long long items = static_cast<long long>(num_tokens) * heads_total;
     const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
