@@ -1,0 +1,394 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores: tcgen05.mma with
+// accumulators in tensor memory (TMEM), operands fetched by TMA, bfloat16, head size 128.
+//
+// A CTA takes 128 consecutive query rows of one request for one query head (a tile of the same
+// host-built list the mma.sync kernel uses) and walks the request's keys in tiles of 128, TWICE:
+//   pass A:  S = Q K^T (tcgen05.mma, M 128 x N 128 x K 128 -> TMEM), row maxima m over visible keys;
+//   pass B:  S again, P = exp2(S*scale*log2e - m) (exact softmax numerators: m is final, so the
+//            output accumulator never has to be rescaled), l += row sums, P rounded to bfloat16
+//            goes back into TMEM, O += P V (tcgen05.mma with A from TMEM, V as an MN-major
+//            shared-memory operand), and at the end out = O / l.
+// Running S twice costs half as much again in tensor work and removes the correction step of
+// the running-maximum form (src/ops/attention.cu:204-249) from the critical path; the numbers
+// are those of a two-pass softmax (src/ops/paged_attention.cpp:159-217).
+//
+// Roles (192 threads): warp 0 feeds the copy engine (Q once, then K or K+V tiles, one box per
+// page and 64-column half, two stages); one lane of warp 1 issues the MMAs and owns the TMEM
+// allocation; warps 2..5 are the softmax: thread i owns query row i = TMEM lane i.
+// S and P are double-buffered in TMEM (S0 S1 O P0 P1 = 128+128+128+64+64 = 512 columns), so
+// the S of the next tile is computed while the softmax of this one runs.
+// Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, records status
+// code 6, lets its copies land (bounded) and frees its TMEM before it returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <math_constants.h>
+
+#define T5_BM 128
+#define T5_BN 128
+#define T5_D 128
+#define T5_STAGES 2
+#define T5_THREADS 192
+#define T5_WAIT_LIMIT (1 << 22)
+#define T5_HALF (T5_BN * 64)                  // elements of one 64-column half of a 128-row tile
+#define T5_TILE (2 * T5_HALF)
+
+__device__ __forceinline__ unsigned t5_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void t5_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void t5_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(t5_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool t5_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(t5_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
+                                        int32_t* status, int where) {
+    for (int i = 0; i < T5_WAIT_LIMIT; ++i) {
+        if (t5_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (atomicCAS(status, 0, 6) == 0) status[1] = where;
+    return false;
+}
+__device__ __forceinline__ void t5_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                     "r"(t5_smem(dst)), "l"(map), "r"(x), "r"(y), "r"(t5_smem(bar)) : "memory");
+}
+
+// ---- tcgen05 -------------------------------------------------------------------------------------
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_smem(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void t5_mma_ss(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::
+                     "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void t5_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::
+                     "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void t5_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void t5_st16(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::
+            "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void t5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory operand descriptor, 128-byte swizzle, version 1.  lbo, sbo in bytes.
+__device__ __forceinline__ unsigned long long t5_desc(const void* smem, unsigned lbo, unsigned sbo) {
+    unsigned long long d = 0;
+    d |= static_cast<unsigned long long>((t5_smem(smem) & 0x3FFFF) >> 4);
+    d |= static_cast<unsigned long long>((lbo >> 4) & 0x3FFF) << 16;
+    d |= static_cast<unsigned long long>((sbo >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;                      // descriptor version of this architecture
+    d |= 2ull << 61;                      // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, M x N, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr unsigned t5_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<unsigned>(b_mn_major) << 16) |
+           (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(m >> 4) << 24);
+}
+__device__ __forceinline__ unsigned t5_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+__global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
+    const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
+    const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
+    const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
+    float scale_log2e, int num_pages, int32_t* __restrict__ status) {
+    pdl_begin();
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [2][128][64]
+    bf16* k_s = q_s + T5_TILE;                                    // [STAGES][2][128][64]
+    bf16* v_s = k_s + T5_STAGES * T5_TILE;                        // [STAGES][2][128][64]
+    __shared__ __align__(8) unsigned long long q_full, kv_full[T5_STAGES], kv_empty[T5_STAGES], s_full[2], s_free[2],
+        p_full[2], p_free[2], o_done;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_flag;
+
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int kvh = h / (nq / nkv);
+    const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
+    const int past = kv_len - q_len;
+    const int row_base = entry_q_start[e] + q0;
+    const int rows_here = min(T5_BM, q_len - q0);
+    const int32_t* table = block_table + static_cast<size_t>(entry_slot[e]) * table_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
+    const int k_lo = (window > 0 && pos_first - window + 1 > 0) ? ((pos_first - window + 1) / T5_BN) * T5_BN : 0;
+    const int n_tiles = (pos_last - k_lo) / T5_BN + 1;
+    const int total = 2 * n_tiles;                                // pass A then pass B over the same tiles
+
+    if (tid == 0) {
+        abort_flag = 0;
+        t5_mbar_init(&q_full, 1);
+        for (int s = 0; s < T5_STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) {
+            t5_mbar_init(&s_full[s], 1);
+            t5_mbar_init(&s_free[s], 128);
+            t5_mbar_init(&p_full[s], 128);
+            t5_mbar_init(&p_free[s], 1);
+        }
+        t5_mbar_init(&o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {                                              // one warp allocates all 512 TMEM columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(t5_smem(&tmem_base_s)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    t5_fence_before();
+    __syncthreads();
+    t5_fence_after();
+    const unsigned tmem = tmem_base_s;
+    const unsigned S_COL[2] = {0u, 128u}, O_COL = 256u, P_COL[2] = {384u, 448u};
+
+    if (warp == 0) {
+        // ---- producer ----
+        if (lane == 0) {
+            t5_expect_tx(&q_full, T5_TILE * sizeof(bf16));
+            t5_tma_2d(q_s, &q_map, h * T5_D, row_base, &q_full);
+            t5_tma_2d(q_s + T5_HALF, &q_map, h * T5_D + 64, row_base, &q_full);
+            const int boxes = T5_BN / page_size;
+            const int last_logical = pos_last / page_size;
+            int issued = 0;
+            for (int u = 0; u < total; ++u) {
+                const int st = u % T5_STAGES, it = u % n_tiles;
+                const bool with_v = u >= n_tiles;
+                if (u >= T5_STAGES && !t5_wait(&kv_empty[st], ((u / T5_STAGES) - 1) & 1, &abort_flag, status, row_base)) break;
+                t5_expect_tx(&kv_full[st], (with_v ? 2u : 1u) * T5_TILE * sizeof(bf16));
+                const int first_logical = (k_lo + it * T5_BN) / page_size;
+                for (int j = 0; j < boxes; ++j) {
+                    const int logical = min(first_logical + j, last_logical);
+                    int page = logical < table_stride ? __ldg(table + logical) : -1;
+                    if (page < 0 || page >= num_pages) {
+                        if (atomicCAS(status, 0, 4) == 0) status[1] = row_base;
+                        page = 0;
+                    }
+                    const int k_row = ((page * 2) * nkv + kvh) * page_size;
+                    const int v_row = ((page * 2 + 1) * nkv + kvh) * page_size;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        t5_tma_2d(k_s + st * T5_TILE + half * T5_HALF + j * page_size * 64, &kv_map, half * 64, k_row, &kv_full[st]);
+                        if (with_v)
+                            t5_tma_2d(v_s + st * T5_TILE + half * T5_HALF + j * page_size * 64, &kv_map, half * 64, v_row, &kv_full[st]);
+                    }
+                }
+                issued = u + 1;
+            }
+            if (abort_flag)
+                for (int u = max(0, issued - T5_STAGES); u < issued; ++u)
+                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&kv_full[u % T5_STAGES], (u / T5_STAGES) & 1); ++i) {}
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr unsigned IDESC_QK = t5_idesc(T5_BM, T5_BN, 0);
+            constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
+            bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
+            auto issue_qk = [&](int u) -> bool {
+                const int st = u % T5_STAGES, sb = u & 1;
+                if (!t5_wait(&kv_full[st], (u / T5_STAGES) & 1, &abort_flag, status, row_base)) return false;
+                if (u >= 2 && !t5_wait(&s_free[sb], ((u >> 1) - 1) & 1, &abort_flag, status, row_base)) return false;
+                t5_fence_after();
+#pragma unroll
+                for (int k = 0; k < T5_D / 16; ++k) {
+                    const bf16* qa = q_s + (k >> 2) * T5_HALF + (k & 3) * 16;
+                    const bf16* kb = k_s + st * T5_TILE + (k >> 2) * T5_HALF + (k & 3) * 16;
+                    t5_mma_ss(tmem + S_COL[sb], t5_desc(qa, 16, 1024), t5_desc(kb, 16, 1024), IDESC_QK, k > 0);
+                }
+                t5_commit(&s_full[sb]);
+                if (u < n_tiles) t5_commit(&kv_empty[st]);        // pass A: the keys are all this stage held
+                return true;
+            };
+            if (ok && total > 0) ok = issue_qk(0);
+            for (int u = 0; ok && u < total; ++u) {
+                if (u + 1 < total) ok = issue_qk(u + 1);          // the next S while this tile's softmax runs
+                if (!ok || u < n_tiles) continue;
+                const int st = u % T5_STAGES, pb = u & 1, v = u - n_tiles;
+                if (!t5_wait(&p_full[pb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                t5_fence_after();
+#pragma unroll
+                for (int k = 0; k < T5_BN / 16; ++k) {
+                    const bf16* vb = v_s + st * T5_TILE + k * 16 * 64;          // 16 keys further, both 64-column halves
+                    t5_mma_ts(tmem + O_COL, tmem + P_COL[pb] + k * 8, t5_desc(vb, T5_HALF * sizeof(bf16), 1024), IDESC_PV,
+                              (v > 0 || k > 0) ? 1u : 0u);
+                }
+                t5_commit(&kv_empty[st]);
+                t5_commit(&p_free[pb]);
+                if (u == total - 1) t5_commit(&o_done);
+            }
+        }
+    } else {
+        // ---- softmax: thread `row` owns query row `row` = TMEM lane `row` ----
+        const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
+        const int pos = (row < rows_here) ? past + q0 + row : -1;
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        float m = -CUDART_INF_F, l = 0.0f;
+        bool ok = true;
+        for (int u = 0; ok && u < total; ++u) {
+            const int sb = u & 1, it = u % n_tiles, kt = k_lo + it * T5_BN;
+            if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            t5_fence_after();
+            if (u < n_tiles) {                                    // pass A: maxima
+#pragma unroll 1
+                for (int c = 0; c < T5_BN; c += 32) {
+                    unsigned r[32];
+                    t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kt + c + i;
+                        if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
+                    }
+                }
+                t5_fence_before();
+                t5_arrive(&s_free[sb]);
+            } else {                                              // pass B: numerators with the final maximum
+                const int v = u - n_tiles, pb = u & 1;
+                const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
+                if (v >= 2 && !t5_wait(&p_free[pb], ((v >> 1) - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+#pragma unroll 1
+                for (int c = 0; c < T5_BN; c += 32) {
+                    unsigned r[32], pk[16];
+                    t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = kt + c + i;
+                        const float p0 = (key <= pos && key >= lo) ? exp2f(__uint_as_float(r[i]) * scale_log2e - msub) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? exp2f(__uint_as_float(r[i + 1]) * scale_log2e - msub) : 0.0f;
+                        l += p0 + p1;
+                        pk[i >> 1] = t5_pack(p0, p1);
+                    }
+                    t5_st16(tmem + lane_addr + P_COL[pb] + (c >> 1), pk);
+                }
+                t5_wait_st();
+                t5_fence_before();
+                t5_arrive(&p_full[pb]);
+                t5_arrive(&s_free[sb]);
+            }
+        }
+        if (ok && t5_wait(&o_done, 0, &abort_flag, status, row_base)) {
+            t5_fence_after();
+            const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h) * T5_D;
+#pragma unroll 1
+            for (int c = 0; c < T5_D; c += 32) {
+                unsigned r[32];
+                t5_ld32(tmem + lane_addr + O_COL + c, r);
+                if (row < rows_here) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = t5_pack(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        w.y = t5_pack(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        w.z = t5_pack(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        w.w = t5_pack(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    t5_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        t5_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*T5EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static T5EncodeFn g_t5_encode = nullptr;
+static int g_t5_state = 0;
+
+static bool t5_encode_2d(CUtensorMap* map, const void* base, long long cols, long long rows, int box_cols, int box_rows) {
+    if (g_t5_state == 0) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess && fn != nullptr) {
+            g_t5_encode = reinterpret_cast<T5EncodeFn>(fn);
+            g_t5_state = 1;
+        } else {
+            (void)cudaGetLastError();
+            g_t5_state = -1;
+        }
+    }
+    if (g_t5_state < 0 || rows >= (1LL << 31)) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(bf16)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return g_t5_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+extern "C" int llm_paged_prefill_tcgen05_supported(int d, int page_size) {
+    return d == T5_D && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
+}
+extern "C" int llm_paged_prefill_tcgen05_tile_rows() { return T5_BM; }
+
+// q, out: bfloat16 [num_tokens, nq*128]; cache: bfloat16 [pages, 2, nkv, page_size, 128];
+// tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), 128 rows each.
+extern "C" int llm_paged_attention_prefill_tcgen05(
+    const void* q, void* out, const void* cache, int num_tokens, const int32_t* tiles, int n_tiles,
+    const int32_t* entry_slot, const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
+    const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
+    int num_pages, int32_t* status, uintptr_t stream) {
+    if (n_tiles <= 0) return LLM_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !llm_paged_prefill_tcgen05_supported(d, page_size) || nq > 65535)
+        return LLM_REFUSED_SIZE;
+    if (!aligned16(q) || !aligned16(out) || !aligned16(cache)) return LLM_REFUSED_ALIGN;
+    CUtensorMap q_map, kv_map;
+    if (!t5_encode_2d(&q_map, q, static_cast<long long>(nq) * d, num_tokens, 64, T5_BM)) return LLM_REFUSED_SIZE;
+    if (!t5_encode_2d(&kv_map, cache, d, static_cast<long long>(num_pages) * 2 * nkv * page_size, 64, page_size))
+        return LLM_REFUSED_SIZE;
+    const size_t smem = static_cast<size_t>(1 + 2 * T5_STAGES) * T5_TILE * sizeof(bf16) + 1024;
+    auto kern = paged_prefill_attention_tcgen05_kernel;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    launch_pdl(kern, dim3(n_tiles, nq), dim3(T5_THREADS), smem, reinterpret_cast<cudaStream_t>(stream), q_map, kv_map,
+               static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table,
+               table_stride, nq, nkv, page_size, window, scale * 1.4426950408889634f, num_pages, status);
+    return launch_status();
+}

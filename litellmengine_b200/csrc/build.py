@@ -32,6 +32,7 @@ FAMILIES: Dict[str, List[str]] = {
     "attention_generic": ["attention_generic.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
+    "attention_prefill_tcgen05": ["attention_prefill_tcgen05.cu"],
     "sampling": ["sampling.cu"],
     "gemm_skinny": ["gemm_skinny.cu"],
 }

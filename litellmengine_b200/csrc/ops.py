@@ -335,6 +335,32 @@ def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
     return out
 
 
+def prefill_tcgen05_supported(d: int, page_size: int) -> bool:
+    f = _fn("attention_prefill_tcgen05", "llm_paged_prefill_tcgen05_supported", [c_int, c_int])
+    return bool(f(d, page_size))
+
+
+def paged_attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor,
+                                    n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                                    block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                                    window: Optional[int], scale: float, status: torch.Tensor) -> torch.Tensor:
+    """The prompt-portion attention on tcgen05/TMEM with TMA loads (head size 128, pages of 8..128);
+    same arguments as `paged_attention_prefill`."""
+    _dev(q, out, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tcgen05 prefill attention kernel is bfloat16 only")
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    f = _fn("attention_prefill_tcgen05", "llm_paged_attention_prefill_tcgen05",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(cache), q.shape[0], _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
+             _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
+             int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _stream()),
+           "paged_attention_prefill_tcgen05")
+    return out
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(logits, out)
     if logits.dtype != torch.float32 or logits.dim() != 2:

@@ -367,9 +367,9 @@ def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1,
         ops().paged_attention_decode(q_all, out, cache, rows, len(dec_rows), i32(pos_l), i32(ent_l),
                                      i32(list(range(B))), table.to(DEV), nq, nkv, d, page, window, scale, splits, st)
     else:
-        ops().paged_attention_prefill(q_all, out, cache, i32(tiles).view(-1, 2), len(tiles) // 2, i32(list(range(B))),
-                                      i32(q_start), i32(q_len), i32(kv_len), table.to(DEV), nq, nkv, d, page, window,
-                                      scale, st)
+        fn = ops().paged_attention_prefill_tcgen05 if kernel == "prefill_tcgen05" else ops().paged_attention_prefill
+        fn(q_all, out, cache, i32(tiles).view(-1, 2), len(tiles) // 2, i32(list(range(B))),
+           i32(q_start), i32(q_len), i32(kv_len), table.to(DEV), nq, nkv, d, page, window, scale, st)
     assert st.tolist() == [0, 0]
     return out.view(-1, nq, d), torch.cat(refs)
 
@@ -455,3 +455,33 @@ def test_skinny_product(M, N, K, out_dtype):
     close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
     lib = torch.mm(x.to(DEV), w.to(DEV).t(), out_dtype=torch.float32)
     close(got, lib, 2e-5 if out_dtype == "float32" else 6e-3)      # and against the library product
+
+
+# ---- the tcgen05 / TMEM / TMA prompt-portion attention kernel ------------------------------------
+@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 64), (3, 1, 8), (6, 2, 128), (4, 2, 32)])
+def test_prefill_tcgen05_kernel(nq, nkv, page):
+    reqs = [(2, 2), (64, 64), (129, 129), (130, 3), (200, 7), (333, 129), (400, 400), (128, 128), (257, 130)]
+    out, ref = fast_case("prefill_tcgen05", nq, nkv, 128, page, reqs)
+    close(out, ref, 1e-2)
+
+
+@pytest.mark.parametrize("key", [0, 15, 16, 127, 128, 129, 255, 256, 300, 383, 384, 400, 449])
+def test_prefill_tcgen05_finds_a_far_key(key):
+    n, nqr = 450, 66
+    out, ref = fast_case("prefill_tcgen05", 4, 2, 128, 16, [(30, 30), (n, nqr)], spike=(1, key), seed=key)
+    close(out, ref, 1e-2)
+    first_q = n - nqr
+    means = out[30:].float().mean(dim=(1, 2))
+    for i in range(nqr):
+        assert (float(means[i]) > 90.0) == (first_q + i >= key)
+
+
+@pytest.mark.parametrize("window", [1, 5, 128, 129, 200])
+def test_prefill_tcgen05_window_edges(window):
+    n, nqr = 300, 150
+    for inside in (True, False):
+        qpos = n - 1
+        key = qpos - window + 1 if inside else qpos - window
+        out, ref = fast_case("prefill_tcgen05", 4, 2, 128, 16, [(n, nqr)], window=window, spike=(0, key), seed=window)
+        close(out, ref, 1e-2)
+        assert (float(out[-1].float().mean()) > 90.0) == inside
