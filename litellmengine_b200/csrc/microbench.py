@@ -100,7 +100,7 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--out-dtype", default="bfloat16")
-    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own"],
+    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -133,8 +133,10 @@ def main():
         n_tiles = (args.tokens + R - 1) // R
         tiles = torch.tensor([[0, R * i] for i in reversed(range(n_tiles))], dtype=torch.int32, device=dev)
         i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
-        fn = lambda: ops.paged_attention_prefill(q, out, cache, tiles, n_tiles, slot, i32(0), i32(args.tokens),
-                                                 i32(args.tokens), table, nq, nkv, d, P, None, scale, status)
+        kern = ops.paged_attention_prefill_tcgen05 if args.impl == "tcgen05" else ops.paged_attention_prefill
+        fn = lambda: kern(q, out, cache, tiles, n_tiles, slot, i32(0), i32(args.tokens),
+                          i32(args.tokens), table, nq, nkv, d, P, None, scale, status)
+        res["impl"] = args.impl
         res.update(tokens=args.tokens, flops=4 * nq * d * args.tokens * (args.tokens + 1) // 2)
     elif args.kernel == "rmsnorm":
         x = torch.randn(args.tokens, args.hidden, device=dev)
