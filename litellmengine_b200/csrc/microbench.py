@@ -134,8 +134,9 @@ def main():
         tiles = torch.tensor([[0, R * i] for i in reversed(range(n_tiles))], dtype=torch.int32, device=dev)
         i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=dev)
         kern = ops.paged_attention_prefill_tcgen05 if args.impl == "tcgen05" else ops.paged_attention_prefill
-        fn = lambda: kern(q, out, cache, tiles, n_tiles, slot, i32(0), i32(args.tokens),
-                          i32(args.tokens), table, nq, nkv, d, P, None, scale, status)
+        q_start, q_len, kv_len = i32(0), i32(args.tokens), i32(args.tokens)
+        fn = lambda: kern(q, out, cache, tiles, n_tiles, slot, q_start, q_len, kv_len, table, nq, nkv, d, P, None,
+                          scale, status)
         res["impl"] = args.impl
         res.update(tokens=args.tokens, flops=4 * nq * d * args.tokens * (args.tokens + 1) // 2)
     elif args.kernel == "rmsnorm":
