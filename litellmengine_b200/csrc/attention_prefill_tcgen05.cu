@@ -12,9 +12,11 @@
 // the running-maximum form (src/ops/attention.cu:204-249) from the critical path; the numbers
 // are those of a two-pass softmax (src/ops/paged_attention.cpp:159-217).
 //
-// Roles (192 threads): warp 0 feeds the copy engine (Q once, then K or K+V tiles, one box per
+// Roles (320 threads): warp 0 feeds the copy engine (Q once, then K or K+V tiles, one box per
 // page and 64-column half, two stages); one lane of warp 1 issues the MMAs and owns the TMEM
-// allocation; warps 2..5 are the softmax: thread i owns query row i = TMEM lane i.
+// allocation; warps 2..9 are the softmax: two warps share each quarter of the TMEM lanes (a warp
+// can only reach the 32 lanes of its quarter) and split the tile's 128 columns between them, so a
+// query row's maximum and sum are kept in two halves that meet in shared memory.
 // S and P are double-buffered in TMEM (S0 S1 O P0 P1 = 128+128+128+64+64 = 512 columns), so
 // the S of the next tile is computed while the softmax of this one runs.
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, records status
@@ -27,7 +29,7 @@
 #define T5_BN 128
 #define T5_D 128
 #define T5_STAGES 2
-#define T5_THREADS 192
+#define T5_THREADS 320                    // producer warp, MMA warp, eight softmax warps
 #define T5_WAIT_LIMIT (1 << 22)
 #define T5_HALF (T5_BN * 64)                  // elements of one 64-column half of a 128-row tile
 #define T5_TILE (2 * T5_HALF)
@@ -118,6 +120,11 @@ __host__ __device__ constexpr unsigned t5_idesc(int m, int n, int b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<unsigned>(b_mn_major) << 16) |
            (static_cast<unsigned>(n >> 3) << 17) | (static_cast<unsigned>(m >> 4) << 24);
 }
+__device__ __forceinline__ float t5_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned t5_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&v);
@@ -139,6 +146,7 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
         p_full[2], p_free[2], o_done;
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
+    __shared__ float half_max[2][T5_BM], half_sum[2][T5_BM];     // the two column halves of a row's statistics
 
     const int tile = blockIdx.x, h = blockIdx.y;
     const int kvh = h / (nq / nkv);
@@ -160,8 +168,8 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
         for (int s = 0; s < T5_STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
             t5_mbar_init(&s_full[s], 1);
-            t5_mbar_init(&s_free[s], 128);
-            t5_mbar_init(&p_full[s], 128);
+            t5_mbar_init(&s_free[s], 256);
+            t5_mbar_init(&p_full[s], 256);
             t5_mbar_init(&p_free[s], 1);
         }
         t5_mbar_init(&o_done, 1);
@@ -254,61 +262,89 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             }
         }
     } else {
-        // ---- softmax: thread `row` owns query row `row` = TMEM lane `row` ----
+        // ---- softmax: thread (row, half) owns 64 columns of query row `row` = TMEM lane `row` ----
+        const int sw = warp - 2;                                  // 0..7
         const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
+        const int chalf = sw >> 2;                                // warps 2..5 take columns 0..63, warps 6..9 columns 64..127
         const int row = quarter * 32 + lane;
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         const int pos = (row < rows_here) ? past + q0 + row : -1;
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int c0 = chalf * 64;
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
-        for (int u = 0; ok && u < total; ++u) {
-            const int sb = u & 1, it = u % n_tiles, kt = k_lo + it * T5_BN;
+        // Both exchanges below are reached by all 256 softmax threads whatever happened in the loops.
+        for (int u = 0; ok && u < n_tiles; ++u) {                 // pass A: maxima
+            const int sb = u & 1, kt = k_lo + u * T5_BN;
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
-            if (u < n_tiles) {                                    // pass A: maxima
+            const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
 #pragma unroll 1
-                for (int c = 0; c < T5_BN; c += 32) {
-                    unsigned r[32];
-                    t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+            for (int c = c0; c < c0 + 64; c += 32) {
+                unsigned r[32];
+                t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+                if (full_tile) {                                  // every row of the CTA sees every key of the tile
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
+                } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = kt + c + i;
                         if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
                     }
                 }
-                t5_fence_before();
-                t5_arrive(&s_free[sb]);
-            } else {                                              // pass B: numerators with the final maximum
-                const int v = u - n_tiles, pb = u & 1;
-                const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
-                if (v >= 2 && !t5_wait(&p_free[pb], ((v >> 1) - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            }
+            t5_fence_before();
+            t5_arrive(&s_free[sb]);
+        }
+        half_max[chalf][row] = m;                                 // the two column halves agree on the maximum
+        asm volatile("bar.sync 2, 256;\n" ::: "memory");
+        m = fmaxf(half_max[0][row], half_max[1][row]);
+        const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
+        for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
+            const int sb = u & 1, pb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
+            if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            t5_fence_after();
+            if (v >= 2 && !t5_wait(&p_free[pb], ((v >> 1) - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
 #pragma unroll 1
-                for (int c = 0; c < T5_BN; c += 32) {
-                    unsigned r[32], pk[16];
-                    t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+            for (int c = c0; c < c0 + 64; c += 32) {
+                unsigned r[32], pk[16];
+                t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
+                if (full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const int key = kt + c + i;
-                        const float p0 = (key <= pos && key >= lo) ? exp2f(__uint_as_float(r[i]) * scale_log2e - msub) : 0.0f;
-                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? exp2f(__uint_as_float(r[i + 1]) * scale_log2e - msub) : 0.0f;
+                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
+                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
                         l += p0 + p1;
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
-                    t5_st16(tmem + lane_addr + P_COL[pb] + (c >> 1), pk);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = kt + c + i;
+                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                        l += p0 + p1;
+                        pk[i >> 1] = t5_pack(p0, p1);
+                    }
                 }
-                t5_wait_st();
-                t5_fence_before();
-                t5_arrive(&p_full[pb]);
-                t5_arrive(&s_free[sb]);
+                t5_st16(tmem + lane_addr + P_COL[pb] + (c >> 1), pk);
             }
+            t5_wait_st();
+            t5_fence_before();
+            t5_arrive(&p_full[pb]);
+            t5_arrive(&s_free[sb]);
         }
+        half_sum[chalf][row] = l;
+        asm volatile("bar.sync 2, 256;\n" ::: "memory");
+        l = half_sum[0][row] + half_sum[1][row];
         if (ok && t5_wait(&o_done, 0, &abort_flag, status, row_base)) {
             t5_fence_after();
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
             bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h) * T5_D;
 #pragma unroll 1
-            for (int c = 0; c < T5_D; c += 32) {
+            for (int c = c0; c < c0 + 64; c += 32) {              // each half writes its 64 output columns
                 unsigned r[32];
                 t5_ld32(tmem + lane_addr + O_COL + c, r);
                 if (row < rows_here) {
