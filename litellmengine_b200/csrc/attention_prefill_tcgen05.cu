@@ -2,8 +2,8 @@
 // accumulators in tensor memory (TMEM), operands fetched by TMA, bfloat16, head size 128.
 //
 // A CTA takes 128 consecutive query rows of one request for one query head (a tile of the same
-// host-built list the mma.sync kernel uses) and walks the request's keys in tiles of 128, TWICE:
-//   pass A:  S = Q K^T (tcgen05.mma, M 128 x N 128 x K 128 -> TMEM), row maxima m over visible keys;
+// host-built list the mma.sync kernel uses) and walks the request's keys in tiles of 64, TWICE:
+//   pass A:  S = Q K^T (tcgen05.mma, M 128 x N 64 x K 128 -> TMEM), row maxima m over visible keys;
 //   pass B:  S again, P = exp2(S*scale*log2e - m) (exact softmax numerators: m is final, so the
 //            output accumulator never has to be rescaled), l += row sums, P rounded to bfloat16
 //            goes back into TMEM, O += P V (tcgen05.mma with A from TMEM, V as an MN-major
@@ -17,8 +17,10 @@
 // allocation; warps 2..9 are the softmax: two warps share each quarter of the TMEM lanes (a warp
 // can only reach the 32 lanes of its quarter) and split the tile's 128 columns between them, so a
 // query row's maximum and sum are kept in two halves that meet in shared memory.
-// S and P are double-buffered in TMEM (S0 S1 O P0 P1 = 128+128+128+64+64 = 512 columns), so
-// the S of the next tile is computed while the softmax of this one runs.
+// S is double-buffered in TMEM and P overwrites its own S in place (S0 S1 O = 64+64+128 = 256
+// columns), so the S of the next tile is computed while the softmax of this one runs, and two
+// CTAs fit an SM (256 of 512 TMEM columns and 97 KB of shared memory each): one CTA's waits are
+// the other's work.
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, records status
 // code 6, lets its copies land (bounded) and frees its TMEM before it returns.
 #include "common.cuh"
@@ -26,13 +28,15 @@
 #include <math_constants.h>
 
 #define T5_BM 128
-#define T5_BN 128
+#define T5_BN 64
 #define T5_D 128
 #define T5_STAGES 2
 #define T5_THREADS 320                    // producer warp, MMA warp, eight softmax warps
 #define T5_WAIT_LIMIT (1 << 22)
-#define T5_HALF (T5_BN * 64)                  // elements of one 64-column half of a 128-row tile
+#define T5_QHALF (T5_BM * 64)                 // elements of one 64-column half of the 128-row query tile
+#define T5_HALF (T5_BN * 64)                  // elements of one 64-column half of a key or value tile
 #define T5_TILE (2 * T5_HALF)
+#define T5_TMEM_COLS 256
 
 __device__ __forceinline__ unsigned t5_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, int count) {
@@ -140,10 +144,10 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [2][128][64]
-    bf16* k_s = q_s + T5_TILE;                                    // [STAGES][2][128][64]
-    bf16* v_s = k_s + T5_STAGES * T5_TILE;                        // [STAGES][2][128][64]
-    __shared__ __align__(8) unsigned long long q_full, kv_full[T5_STAGES], kv_empty[T5_STAGES], s_full[2], s_free[2],
-        p_full[2], p_free[2], o_done;
+    bf16* k_s = q_s + 2 * T5_QHALF;                               // [STAGES][2][BN][64]
+    bf16* v_s = k_s + T5_STAGES * T5_TILE;                        // [STAGES][2][BN][64]
+    __shared__ __align__(8) unsigned long long q_full, kv_full[T5_STAGES], kv_empty[T5_STAGES], s_full[2], s_read[2],
+        p_full[2], s_used[2], o_done;
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
     __shared__ float half_max[2][T5_BM], half_sum[2][T5_BM];     // the two column halves of a row's statistics
@@ -168,29 +172,29 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
         for (int s = 0; s < T5_STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
             t5_mbar_init(&s_full[s], 1);
-            t5_mbar_init(&s_free[s], 256);
-            t5_mbar_init(&p_full[s], 256);
-            t5_mbar_init(&p_free[s], 1);
+            t5_mbar_init(&s_read[s], 256);        // pass A: every softmax thread has read its part of S
+            t5_mbar_init(&p_full[s], 256);        // pass B: every softmax thread has put its part of P over S
+            t5_mbar_init(&s_used[s], 1);          // pass B: the P V product that reads this buffer has finished
         }
         t5_mbar_init(&o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {                                              // one warp allocates all 512 TMEM columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(t5_smem(&tmem_base_s)) : "memory");
+    if (warp == 1) {                                              // one warp allocates this CTA's 256 TMEM columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(t5_smem(&tmem_base_s)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     t5_fence_before();
     __syncthreads();
     t5_fence_after();
     const unsigned tmem = tmem_base_s;
-    const unsigned S_COL[2] = {0u, 128u}, O_COL = 256u, P_COL[2] = {384u, 448u};
+    const unsigned S_COL[2] = {0u, 64u}, O_COL = 128u;           // P lives in its S buffer: columns +0..15 and +32..47
 
     if (warp == 0) {
         // ---- producer ----
         if (lane == 0) {
-            t5_expect_tx(&q_full, T5_TILE * sizeof(bf16));
+            t5_expect_tx(&q_full, 2 * T5_QHALF * sizeof(bf16));
             t5_tma_2d(q_s, &q_map, h * T5_D, row_base, &q_full);
-            t5_tma_2d(q_s + T5_HALF, &q_map, h * T5_D + 64, row_base, &q_full);
+            t5_tma_2d(q_s + T5_QHALF, &q_map, h * T5_D + 64, row_base, &q_full);
             const int boxes = T5_BN / page_size;
             const int last_logical = pos_last / page_size;
             int issued = 0;
@@ -231,11 +235,17 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             auto issue_qk = [&](int u) -> bool {
                 const int st = u % T5_STAGES, sb = u & 1;
                 if (!t5_wait(&kv_full[st], (u / T5_STAGES) & 1, &abort_flag, status, row_base)) return false;
-                if (u >= 2 && !t5_wait(&s_free[sb], ((u >> 1) - 1) & 1, &abort_flag, status, row_base)) return false;
+                if (u >= 2) {                                     // the buffer's previous tile must be done with it
+                    const int prev = u - 2;
+                    const bool a = prev < n_tiles;
+                    if (!t5_wait(a ? &s_read[sb] : &s_used[sb], ((a ? prev : prev - n_tiles) >> 1) & 1, &abort_flag, status,
+                                 row_base))
+                        return false;
+                }
                 t5_fence_after();
 #pragma unroll
                 for (int k = 0; k < T5_D / 16; ++k) {
-                    const bf16* qa = q_s + (k >> 2) * T5_HALF + (k & 3) * 16;
+                    const bf16* qa = q_s + (k >> 2) * T5_QHALF + (k & 3) * 16;
                     const bf16* kb = k_s + st * T5_TILE + (k >> 2) * T5_HALF + (k & 3) * 16;
                     t5_mma_ss(tmem + S_COL[sb], t5_desc(qa, 16, 1024), t5_desc(kb, 16, 1024), IDESC_QK, k > 0);
                 }
@@ -247,17 +257,18 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             for (int u = 0; ok && u < total; ++u) {
                 if (u + 1 < total) ok = issue_qk(u + 1);          // the next S while this tile's softmax runs
                 if (!ok || u < n_tiles) continue;
-                const int st = u % T5_STAGES, pb = u & 1, v = u - n_tiles;
-                if (!t5_wait(&p_full[pb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                const int st = u % T5_STAGES, sb = u & 1, v = u - n_tiles;
+                if (!t5_wait(&p_full[sb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
                 t5_fence_after();
 #pragma unroll
                 for (int k = 0; k < T5_BN / 16; ++k) {
                     const bf16* vb = v_s + st * T5_TILE + k * 16 * 64;          // 16 keys further, both 64-column halves
-                    t5_mma_ts(tmem + O_COL, tmem + P_COL[pb] + k * 8, t5_desc(vb, T5_HALF * sizeof(bf16), 1024), IDESC_PV,
+                    const unsigned p_col = S_COL[sb] + (k >> 1) * 32 + (k & 1) * 8;   // where the softmax halves left P
+                    t5_mma_ts(tmem + O_COL, tmem + p_col, t5_desc(vb, T5_HALF * sizeof(bf16), 1024), IDESC_PV,
                               (v > 0 || k > 0) ? 1u : 0u);
                 }
                 t5_commit(&kv_empty[st]);
-                t5_commit(&p_free[pb]);
+                t5_commit(&s_used[sb]);
                 if (u == total - 1) t5_commit(&o_done);
             }
         }
@@ -270,7 +281,7 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         const int pos = (row < rows_here) ? past + q0 + row : -1;
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        const int c0 = chalf * 64;
+        const int c0 = chalf * 32;                                // this warp's 32 of the tile's 64 columns
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
         // Both exchanges below are reached by all 256 softmax threads whatever happened in the loops.
@@ -279,62 +290,55 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-#pragma unroll 1
-            for (int c = c0; c < c0 + 64; c += 32) {
-                unsigned r[32];
-                t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
-                if (full_tile) {                                  // every row of the CTA sees every key of the tile
+            unsigned r[32];
+            t5_ld32(tmem + lane_addr + S_COL[sb] + c0, r);
+            if (full_tile) {                                      // every row of the CTA sees every key of the tile
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
-                } else {
+                for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = kt + c + i;
-                        if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    const int key = kt + c0 + i;
+                    if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
                 }
             }
             t5_fence_before();
-            t5_arrive(&s_free[sb]);
+            t5_arrive(&s_read[sb]);
         }
         half_max[chalf][row] = m;                                 // the two column halves agree on the maximum
         asm volatile("bar.sync 2, 256;\n" ::: "memory");
         m = fmaxf(half_max[0][row], half_max[1][row]);
         const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
         for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
-            const int sb = u & 1, pb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
+            const int sb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
-            if (v >= 2 && !t5_wait(&p_free[pb], ((v >> 1) - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-#pragma unroll 1
-            for (int c = c0; c < c0 + 64; c += 32) {
-                unsigned r[32], pk[16];
-                t5_ld32(tmem + lane_addr + S_COL[sb] + c, r);
-                if (full_tile) {
+            unsigned r[32], pk[16];
+            t5_ld32(tmem + lane_addr + S_COL[sb] + c0, r);
+            if (full_tile) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
-                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
-                        l += p0 + p1;
-                        pk[i >> 1] = t5_pack(p0, p1);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = kt + c + i;
-                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
-                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
-                        l += p0 + p1;
-                        pk[i >> 1] = t5_pack(p0, p1);
-                    }
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
+                    const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
+                    l += p0 + p1;
+                    pk[i >> 1] = t5_pack(p0, p1);
                 }
-                t5_st16(tmem + lane_addr + P_COL[pb] + (c >> 1), pk);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = kt + c0 + i;
+                    const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
+                    const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                    l += p0 + p1;
+                    pk[i >> 1] = t5_pack(p0, p1);
+                }
             }
+            // P goes over the first half of the very columns this thread has just read
+            t5_st16(tmem + lane_addr + S_COL[sb] + c0, pk);
             t5_wait_st();
             t5_fence_before();
-            t5_arrive(&p_full[pb]);
-            t5_arrive(&s_free[sb]);
+            t5_arrive(&p_full[sb]);
         }
         half_sum[chalf][row] = l;
         asm volatile("bar.sync 2, 256;\n" ::: "memory");
@@ -344,7 +348,7 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
             bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h) * T5_D;
 #pragma unroll 1
-            for (int c = c0; c < c0 + 64; c += 32) {              // each half writes its 64 output columns
+            for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {   // each half writes its 64 output columns
                 unsigned r[32];
                 t5_ld32(tmem + lane_addr + O_COL + c, r);
                 if (row < rows_here) {
@@ -365,7 +369,7 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
     __syncthreads();
     if (warp == 1) {
         t5_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
     }
 }
 
@@ -419,7 +423,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
     if (!t5_encode_2d(&q_map, q, static_cast<long long>(nq) * d, num_tokens, 64, T5_BM)) return LLM_REFUSED_SIZE;
     if (!t5_encode_2d(&kv_map, cache, d, static_cast<long long>(num_pages) * 2 * nkv * page_size, 64, page_size))
         return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(1 + 2 * T5_STAGES) * T5_TILE * sizeof(bf16) + 1024;
+    const size_t smem = static_cast<size_t>(2 * T5_QHALF + 2 * T5_STAGES * T5_TILE) * sizeof(bf16) + 1024;
     auto kern = paged_prefill_attention_tcgen05_kernel;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
