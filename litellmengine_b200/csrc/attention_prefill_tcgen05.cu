@@ -12,15 +12,17 @@
 // the running-maximum form (src/ops/attention.cu:204-249) from the critical path; the numbers
 // are those of a two-pass softmax (src/ops/paged_attention.cpp:159-217).
 //
-// Roles (320 threads): warp 0 feeds the copy engine (Q once, then K or K+V tiles, one box per
-// page and 64-column half, two stages); one lane of warp 1 issues the MMAs and owns the TMEM
-// allocation; warps 2..9 are the softmax: two warps share each quarter of the TMEM lanes (a warp
-// can only reach the 32 lanes of its quarter) and split the tile's 128 columns between them, so a
-// query row's maximum and sum are kept in two halves that meet in shared memory.
-// S is double-buffered in TMEM and P overwrites its own S in place (S0 S1 O = 64+64+128 = 256
-// columns), so the S of the next tile is computed while the softmax of this one runs, and two
-// CTAs fit an SM (256 of 512 TMEM columns and 97 KB of shared memory each): one CTA's waits are
-// the other's work.
+// A CTA serves TWO query heads of the same kv head when the group size is even (one otherwise):
+// they share every key/value tile in shared memory, which halves the L2 traffic and the number
+// of copy-engine operations per unit of tensor work (with 16-token pages a tile is 4 pages x 2
+// halves x K and V = 16 boxes of 2 KB, and the copy engine's time per box is what the first
+// version of this kernel waited for).
+// Roles: warp 0 feeds the copy engine (Q once, then K or K+V tiles, four stages); one lane of
+// warp 1 issues the MMAs and owns the TMEM allocation; then four softmax warps per head: a
+// thread owns one query row = one TMEM lane (a warp can only reach the 32 lanes of its quarter).
+// Per head S is double-buffered in TMEM and P overwrites the first half of its own S in place
+// (S0 S1 O = 64+64+128 = 256 columns per head), so the S of the next tile is computed while the
+// softmax of this one runs.
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, records status
 // code 6, lets its copies land (bounded) and frees its TMEM before it returns.
 #include "common.cuh"
@@ -30,13 +32,11 @@
 #define T5_BM 128
 #define T5_BN 64
 #define T5_D 128
-#define T5_STAGES 2
-#define T5_THREADS 320                    // producer warp, MMA warp, eight softmax warps
-#define T5_WAIT_LIMIT (1 << 22)
+#define T5_WAIT_LIMIT 200000
 #define T5_QHALF (T5_BM * 64)                 // elements of one 64-column half of the 128-row query tile
 #define T5_HALF (T5_BN * 64)                  // elements of one 64-column half of a key or value tile
 #define T5_TILE (2 * T5_HALF)
-#define T5_TMEM_COLS 256
+
 
 __device__ __forceinline__ unsigned t5_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, int count) {
@@ -134,26 +134,31 @@ __device__ __forceinline__ unsigned t5_pack(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-__global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_kernel(
+// HEADS query heads of one kv head share every key/value tile (HEADS = 2 when the group size is
+// even, else 1); STAGES key/value tiles sit in shared memory.
+template <int HEADS, int STAGES>
+__global__ void __launch_bounds__(64 + 128 * HEADS) paged_prefill_attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
     const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
     const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
     float scale_log2e, int num_pages, int32_t* __restrict__ status) {
     pdl_begin();
+    constexpr int SOFTMAX_THREADS = 128 * HEADS;
+    constexpr unsigned TMEM_COLS = 256 * HEADS;                   // per head: S0 S1 (64 each) and O (128)
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [2][128][64]
-    bf16* k_s = q_s + 2 * T5_QHALF;                               // [STAGES][2][BN][64]
-    bf16* v_s = k_s + T5_STAGES * T5_TILE;                        // [STAGES][2][BN][64]
-    __shared__ __align__(8) unsigned long long q_full, kv_full[T5_STAGES], kv_empty[T5_STAGES], s_full[2], s_read[2],
+    bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [HEADS][2][128][64]
+    bf16* k_s = q_s + HEADS * 2 * T5_QHALF;                       // [STAGES][2][BN][64]
+    bf16* v_s = k_s + STAGES * T5_TILE;                           // [STAGES][2][BN][64]
+    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_read[2],
         p_full[2], s_used[2], o_done;
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
-    __shared__ float half_max[2][T5_BM], half_sum[2][T5_BM];     // the two column halves of a row's statistics
 
-    const int tile = blockIdx.x, h = blockIdx.y;
-    const int kvh = h / (nq / nkv);
+    const int tile = blockIdx.x;
+    const int h0 = blockIdx.y * HEADS;                            // first query head of this CTA
+    const int kvh = h0 / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
     const int past = kv_len - q_len;
@@ -169,39 +174,44 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
     if (tid == 0) {
         abort_flag = 0;
         t5_mbar_init(&q_full, 1);
-        for (int s = 0; s < T5_STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
         for (int s = 0; s < 2; ++s) {
             t5_mbar_init(&s_full[s], 1);
-            t5_mbar_init(&s_read[s], 256);        // pass A: every softmax thread has read its part of S
-            t5_mbar_init(&p_full[s], 256);        // pass B: every softmax thread has put its part of P over S
-            t5_mbar_init(&s_used[s], 1);          // pass B: the P V product that reads this buffer has finished
+            t5_mbar_init(&s_read[s], SOFTMAX_THREADS);   // pass A: every softmax thread has read its row of S
+            t5_mbar_init(&p_full[s], SOFTMAX_THREADS);   // pass B: every softmax thread has put its row of P over S
+            t5_mbar_init(&s_used[s], 1);                 // pass B: the P V products that read this buffer have finished
         }
         t5_mbar_init(&o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {                                              // one warp allocates this CTA's 256 TMEM columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;\n" ::"r"(t5_smem(&tmem_base_s)) : "memory");
+    if (warp == 1) {                                              // one warp allocates this CTA's TMEM columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_smem(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     t5_fence_before();
     __syncthreads();
     t5_fence_after();
     const unsigned tmem = tmem_base_s;
-    const unsigned S_COL[2] = {0u, 64u}, O_COL = 128u;           // P lives in its S buffer: columns +0..15 and +32..47
+    // columns of head g: S buffer b at g*256 + b*64, O at g*256 + 128; P lives in the first 32 columns of its S
+    auto s_col = [](int g, int b) { return static_cast<unsigned>(g * 256 + b * 64); };
+    auto o_col = [](int g) { return static_cast<unsigned>(g * 256 + 128); };
 
     if (warp == 0) {
         // ---- producer ----
         if (lane == 0) {
-            t5_expect_tx(&q_full, 2 * T5_QHALF * sizeof(bf16));
-            t5_tma_2d(q_s, &q_map, h * T5_D, row_base, &q_full);
-            t5_tma_2d(q_s + T5_QHALF, &q_map, h * T5_D + 64, row_base, &q_full);
+            t5_expect_tx(&q_full, HEADS * 2 * T5_QHALF * sizeof(bf16));
+#pragma unroll
+            for (int g = 0; g < HEADS; ++g) {
+                t5_tma_2d(q_s + g * 2 * T5_QHALF, &q_map, (h0 + g) * T5_D, row_base, &q_full);
+                t5_tma_2d(q_s + g * 2 * T5_QHALF + T5_QHALF, &q_map, (h0 + g) * T5_D + 64, row_base, &q_full);
+            }
             const int boxes = T5_BN / page_size;
             const int last_logical = pos_last / page_size;
             int issued = 0;
             for (int u = 0; u < total; ++u) {
-                const int st = u % T5_STAGES, it = u % n_tiles;
+                const int st = u % STAGES, it = u % n_tiles;
                 const bool with_v = u >= n_tiles;
-                if (u >= T5_STAGES && !t5_wait(&kv_empty[st], ((u / T5_STAGES) - 1) & 1, &abort_flag, status, row_base)) break;
+                if (u >= STAGES && !t5_wait(&kv_empty[st], ((u / STAGES) - 1) & 1, &abort_flag, status, row_base)) break;
                 t5_expect_tx(&kv_full[st], (with_v ? 2u : 1u) * T5_TILE * sizeof(bf16));
                 const int first_logical = (k_lo + it * T5_BN) / page_size;
                 for (int j = 0; j < boxes; ++j) {
@@ -223,8 +233,8 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
                 issued = u + 1;
             }
             if (abort_flag)
-                for (int u = max(0, issued - T5_STAGES); u < issued; ++u)
-                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&kv_full[u % T5_STAGES], (u / T5_STAGES) & 1); ++i) {}
+                for (int u = max(0, issued - STAGES); u < issued; ++u)
+                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&kv_full[u % STAGES], (u / STAGES) & 1); ++i) {}
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
@@ -233,8 +243,8 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
             auto issue_qk = [&](int u) -> bool {
-                const int st = u % T5_STAGES, sb = u & 1;
-                if (!t5_wait(&kv_full[st], (u / T5_STAGES) & 1, &abort_flag, status, row_base)) return false;
+                const int st = u % STAGES, sb = u & 1;
+                if (!t5_wait(&kv_full[st], (u / STAGES) & 1, &abort_flag, status, row_base)) return false;
                 if (u >= 2) {                                     // the buffer's previous tile must be done with it
                     const int prev = u - 2;
                     const bool a = prev < n_tiles;
@@ -244,11 +254,13 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
                 }
                 t5_fence_after();
 #pragma unroll
-                for (int k = 0; k < T5_D / 16; ++k) {
-                    const bf16* qa = q_s + (k >> 2) * T5_QHALF + (k & 3) * 16;
-                    const bf16* kb = k_s + st * T5_TILE + (k >> 2) * T5_HALF + (k & 3) * 16;
-                    t5_mma_ss(tmem + S_COL[sb], t5_desc(qa, 16, 1024), t5_desc(kb, 16, 1024), IDESC_QK, k > 0);
-                }
+                for (int g = 0; g < HEADS; ++g)
+#pragma unroll
+                    for (int k = 0; k < T5_D / 16; ++k) {
+                        const bf16* qa = q_s + g * 2 * T5_QHALF + (k >> 2) * T5_QHALF + (k & 3) * 16;
+                        const bf16* kb = k_s + st * T5_TILE + (k >> 2) * T5_HALF + (k & 3) * 16;
+                        t5_mma_ss(tmem + s_col(g, sb), t5_desc(qa, 16, 1024), t5_desc(kb, 16, 1024), IDESC_QK, k > 0);
+                    }
                 t5_commit(&s_full[sb]);
                 if (u < n_tiles) t5_commit(&kv_empty[st]);        // pass A: the keys are all this stage held
                 return true;
@@ -257,100 +269,106 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
             for (int u = 0; ok && u < total; ++u) {
                 if (u + 1 < total) ok = issue_qk(u + 1);          // the next S while this tile's softmax runs
                 if (!ok || u < n_tiles) continue;
-                const int st = u % T5_STAGES, sb = u & 1, v = u - n_tiles;
+                const int st = u % STAGES, sb = u & 1, v = u - n_tiles;
                 if (!t5_wait(&p_full[sb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
                 t5_fence_after();
 #pragma unroll
-                for (int k = 0; k < T5_BN / 16; ++k) {
-                    const bf16* vb = v_s + st * T5_TILE + k * 16 * 64;          // 16 keys further, both 64-column halves
-                    const unsigned p_col = S_COL[sb] + (k >> 1) * 32 + (k & 1) * 8;   // where the softmax halves left P
-                    t5_mma_ts(tmem + O_COL, tmem + p_col, t5_desc(vb, T5_HALF * sizeof(bf16), 1024), IDESC_PV,
-                              (v > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int g = 0; g < HEADS; ++g)
+#pragma unroll
+                    for (int k = 0; k < T5_BN / 16; ++k) {
+                        const bf16* vb = v_s + st * T5_TILE + k * 16 * 64;      // 16 keys further, both 64-column halves
+                        t5_mma_ts(tmem + o_col(g), tmem + s_col(g, sb) + k * 8, t5_desc(vb, T5_HALF * sizeof(bf16), 1024),
+                                  IDESC_PV, (v > 0 || k > 0) ? 1u : 0u);
+                    }
                 t5_commit(&kv_empty[st]);
                 t5_commit(&s_used[sb]);
                 if (u == total - 1) t5_commit(&o_done);
             }
         }
     } else {
-        // ---- softmax: thread (row, half) owns 64 columns of query row `row` = TMEM lane `row` ----
-        const int sw = warp - 2;                                  // 0..7
+        // ---- softmax: a thread owns one query row of one head = one TMEM lane, all 64 columns of a tile ----
+        const int sw = warp - 2;
+        const int g = sw >> 2;                                    // warps 2..5: head h0, warps 6..9: head h0 + 1
         const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
-        const int chalf = sw >> 2;                                // warps 2..5 take columns 0..63, warps 6..9 columns 64..127
         const int row = quarter * 32 + lane;
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         const int pos = (row < rows_here) ? past + q0 + row : -1;
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        const int c0 = chalf * 32;                                // this warp's 32 of the tile's 64 columns
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
-        // Both exchanges below are reached by all 256 softmax threads whatever happened in the loops.
         for (int u = 0; ok && u < n_tiles; ++u) {                 // pass A: maxima
             const int sb = u & 1, kt = k_lo + u * T5_BN;
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-            unsigned r[32];
-            t5_ld32(tmem + lane_addr + S_COL[sb] + c0, r);
-            if (full_tile) {                                      // every row of the CTA sees every key of the tile
 #pragma unroll
-                for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
-            } else {
+            for (int c = 0; c < T5_BN; c += 32) {
+                unsigned r[32];
+                t5_ld32(tmem + lane_addr + s_col(g, sb) + c, r);
+                if (full_tile) {                                  // every row of the CTA sees every key of the tile
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = kt + c0 + i;
-                    if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
+                    for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kt + c + i;
+                        if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
+                    }
                 }
             }
             t5_fence_before();
             t5_arrive(&s_read[sb]);
         }
-        half_max[chalf][row] = m;                                 // the two column halves agree on the maximum
-        asm volatile("bar.sync 2, 256;\n" ::: "memory");
-        m = fmaxf(half_max[0][row], half_max[1][row]);
         const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
         for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
             const int sb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-            unsigned r[32], pk[16];
-            t5_ld32(tmem + lane_addr + S_COL[sb] + c0, r);
-            if (full_tile) {
+            unsigned pk[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
-                    const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
-                    l += p0 + p1;
-                    pk[i >> 1] = t5_pack(p0, p1);
-                }
-            } else {
+            for (int c = 0; c < T5_BN; c += 32) {
+                unsigned r[32];
+                t5_ld32(tmem + lane_addr + s_col(g, sb) + c, r);
+                if (full_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = kt + c0 + i;
-                    const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
-                    const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
-                    l += p0 + p1;
-                    pk[i >> 1] = t5_pack(p0, p1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
+                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
+                        l += p0 + p1;
+                        pk[(c + i) >> 1] = t5_pack(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = kt + c + i;
+                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                        l += p0 + p1;
+                        pk[(c + i) >> 1] = t5_pack(p0, p1);
+                    }
                 }
             }
-            // P goes over the first half of the very columns this thread has just read
-            t5_st16(tmem + lane_addr + S_COL[sb] + c0, pk);
+            // the whole row of S is in registers: P goes over its first 32 columns
+            {
+                unsigned a[16], b[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { a[i] = pk[i]; b[i] = pk[16 + i]; }
+                t5_st16(tmem + lane_addr + s_col(g, sb), a);
+                t5_st16(tmem + lane_addr + s_col(g, sb) + 16, b);
+            }
             t5_wait_st();
             t5_fence_before();
             t5_arrive(&p_full[sb]);
         }
-        half_sum[chalf][row] = l;
-        asm volatile("bar.sync 2, 256;\n" ::: "memory");
-        l = half_sum[0][row] + half_sum[1][row];
         if (ok && t5_wait(&o_done, 0, &abort_flag, status, row_base)) {
             t5_fence_after();
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h) * T5_D;
+            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h0 + g) * T5_D;
 #pragma unroll 1
-            for (int c = chalf * 64; c < chalf * 64 + 64; c += 32) {   // each half writes its 64 output columns
+            for (int c = 0; c < T5_D; c += 32) {
                 unsigned r[32];
-                t5_ld32(tmem + lane_addr + O_COL + c, r);
+                t5_ld32(tmem + lane_addr + o_col(g) + c, r);
                 if (row < rows_here) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -369,7 +387,7 @@ __global__ void __launch_bounds__(T5_THREADS) paged_prefill_attention_tcgen05_ke
     __syncthreads();
     if (warp == 1) {
         t5_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;\n" ::"r"(tmem) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -404,7 +422,7 @@ static bool t5_encode_2d(CUtensorMap* map, const void* base, long long cols, lon
 }
 
 extern "C" int llm_paged_prefill_tcgen05_supported(int d, int page_size) {
-    return d == T5_D && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128);
+    return d == T5_D && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 extern "C" int llm_paged_prefill_tcgen05_tile_rows() { return T5_BM; }
 
@@ -423,12 +441,21 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
     if (!t5_encode_2d(&q_map, q, static_cast<long long>(nq) * d, num_tokens, 64, T5_BM)) return LLM_REFUSED_SIZE;
     if (!t5_encode_2d(&kv_map, cache, d, static_cast<long long>(num_pages) * 2 * nkv * page_size, 64, page_size))
         return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(2 * T5_QHALF + 2 * T5_STAGES * T5_TILE) * sizeof(bf16) + 1024;
-    auto kern = paged_prefill_attention_tcgen05_kernel;
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    launch_pdl(kern, dim3(n_tiles, nq), dim3(T5_THREADS), smem, reinterpret_cast<cudaStream_t>(stream), q_map, kv_map,
-               static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table,
-               table_stride, nq, nkv, page_size, window, scale * 1.4426950408889634f, num_pages, status);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const float sl2 = scale * 1.4426950408889634f;
+    const int group = nq / nkv;
+#define T5_GO(HEADS, STAGES)                                                                                         \
+    {                                                                                                                \
+        const size_t smem = static_cast<size_t>(HEADS * 2 * T5_QHALF + 2 * STAGES * T5_TILE) * sizeof(bf16) + 1024;  \
+        auto kern = paged_prefill_attention_tcgen05_kernel<HEADS, STAGES>;                                           \
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                                                   static_cast<int>(smem));                                          \
+        if (e != cudaSuccess) return static_cast<int>(e);                                                            \
+        launch_pdl(kern, dim3(n_tiles, nq / HEADS), dim3(64 + 128 * HEADS), smem, s, q_map, kv_map,                  \
+                   static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,             \
+                   block_table, table_stride, nq, nkv, page_size, window, sl2, num_pages, status);                   \
+    }
+    if (group % 2 == 0) T5_GO(2, 4) else T5_GO(1, 4)
+#undef T5_GO
     return launch_status();
 }

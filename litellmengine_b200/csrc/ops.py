@@ -344,7 +344,7 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: t
                                     n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
                                     block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
                                     window: Optional[int], scale: float, status: torch.Tensor) -> torch.Tensor:
-    """The prompt-portion attention on tcgen05/TMEM with TMA loads (head size 128, pages of 8..128);
+    """The prompt-portion attention on tcgen05/TMEM with TMA loads (head size 128, pages of 8..64);
     same arguments as `paged_attention_prefill`."""
     _dev(q, out, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:

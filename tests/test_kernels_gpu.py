@@ -458,7 +458,7 @@ def test_skinny_product(M, N, K, out_dtype):
 
 
 # ---- the tcgen05 / TMEM / TMA prompt-portion attention kernel ------------------------------------
-@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 64), (3, 1, 8), (6, 2, 128), (4, 2, 32)])
+@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 64), (3, 1, 8), (6, 2, 64), (4, 2, 32), (5, 5, 16)])
 def test_prefill_tcgen05_kernel(nq, nkv, page):
     reqs = [(2, 2), (64, 64), (129, 129), (130, 3), (200, 7), (333, 129), (400, 400), (128, 128), (257, 130)]
     out, ref = fast_case("prefill_tcgen05", nq, nkv, 128, page, reqs)
