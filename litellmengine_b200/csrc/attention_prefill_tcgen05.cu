@@ -99,8 +99,8 @@ __device__ __forceinline__ void t5_ld32(unsigned taddr, unsigned (&r)[32]) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void t5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void t5_st16(unsigned taddr, const unsigned (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::
@@ -137,7 +137,7 @@ __device__ __forceinline__ unsigned t5_pack(float lo, float hi) {
 // HEADS query heads of one kv head share every key/value tile (HEADS = 2 when the group size is
 // even, else 1); STAGES key/value tiles sit in shared memory.
 template <int HEADS, int STAGES>
-__global__ void __launch_bounds__(64 + 128 * HEADS) paged_prefill_attention_tcgen05_kernel(
+__global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
     const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
@@ -301,23 +301,25 @@ __global__ void __launch_bounds__(64 + 128 * HEADS) paged_prefill_attention_tcge
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
+            unsigned r[2][32];                                    // both halves of the row are requested at once
+            t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
+            t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
+            t5_wait_ld();
+            t5_fence_before();
+            t5_arrive(&s_read[sb]);                               // S is in registers: the buffer may be overwritten
 #pragma unroll
-            for (int c = 0; c < T5_BN; c += 32) {
-                unsigned r[32];
-                t5_ld32(tmem + lane_addr + s_col(g, sb) + c, r);
+            for (int cc = 0; cc < 2; ++cc) {
                 if (full_tile) {                                  // every row of the CTA sees every key of the tile
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[i]));
+                    for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(r[cc][i]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = kt + c + i;
-                        if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[i]));
+                        const int key = kt + cc * 32 + i;
+                        if (key <= pos && key >= lo) m = fmaxf(m, __uint_as_float(r[cc][i]));
                     }
                 }
             }
-            t5_fence_before();
-            t5_arrive(&s_read[sb]);
         }
         const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
         for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
@@ -325,27 +327,28 @@ __global__ void __launch_bounds__(64 + 128 * HEADS) paged_prefill_attention_tcge
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-            unsigned pk[32];
+            unsigned pk[32], r[2][32];
+            t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
+            t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
+            t5_wait_ld();
 #pragma unroll
-            for (int c = 0; c < T5_BN; c += 32) {
-                unsigned r[32];
-                t5_ld32(tmem + lane_addr + s_col(g, sb) + c, r);
+            for (int cc = 0; cc < 2; ++cc) {
                 if (full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
-                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
+                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[cc][i]), scale_log2e, -msub));
+                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[cc][i + 1]), scale_log2e, -msub));
                         l += p0 + p1;
-                        pk[(c + i) >> 1] = t5_pack(p0, p1);
+                        pk[(cc * 32 + i) >> 1] = t5_pack(p0, p1);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const int key = kt + c + i;
-                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
-                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                        const int key = kt + cc * 32 + i;
+                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[cc][i]), scale_log2e, -msub)) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[cc][i + 1]), scale_log2e, -msub)) : 0.0f;
                         l += p0 + p1;
-                        pk[(c + i) >> 1] = t5_pack(p0, p1);
+                        pk[(cc * 32 + i) >> 1] = t5_pack(p0, p1);
                     }
                 }
             }
@@ -369,6 +372,7 @@ __global__ void __launch_bounds__(64 + 128 * HEADS) paged_prefill_attention_tcge
             for (int c = 0; c < T5_D; c += 32) {
                 unsigned r[32];
                 t5_ld32(tmem + lane_addr + o_col(g) + c, r);
+                t5_wait_ld();
                 if (row < rows_here) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {

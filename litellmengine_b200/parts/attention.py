@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -96,6 +97,7 @@ class AttentionMixer:
 
 
 _slots = {}
+_PREFILL_KERNEL = os.environ.get("LLM_PREFILL", "tcgen05")     # "mma" keeps the mma.sync kernel everywhere
 
 
 def _cta_slots(device) -> int:
@@ -125,9 +127,11 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
                                        b.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
                                        nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
         if b.num_prefill_tiles:
-            ops.paged_attention_prefill(q, out, cache, b.prefill_tiles, b.num_prefill_tiles, b.entry_slot,
-                                        b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv,
-                                        d, ctx.page_size, window, scale, ctx.status)
+            kernel = (ops.paged_attention_prefill_tcgen05
+                      if _PREFILL_KERNEL != "mma" and ops.prefill_tcgen05_supported(d, ctx.page_size)
+                      else ops.paged_attention_prefill)       # tcgen05/TMEM/TMA where it applies, mma.sync otherwise
+            kernel(q, out, cache, b.prefill_tiles, b.num_prefill_tiles, b.entry_slot, b.entry_q_start, b.entry_q_len,
+                   b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)
         return out
     return ops.paged_attention_generic(q, cache, b.positions, b.token_entry, b.entry_slot,
                                        ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

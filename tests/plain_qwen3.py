@@ -78,10 +78,12 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                     window: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
+                     window: Optional[int] = None, scale: Optional[float] = None, act=None) -> torch.Tensor:
     """q [T,nq,d], k/v [T,nkv,d] -> [T,nq,d].  kv_head = q_head // (nq/nkv); score =
     (q.k) / sqrt(d); key j visible to query i iff j <= i (and i-j < window if a window
-    is given); softmax in float32; out = sum p_j v_j.
+    is given); softmax in float32; out = sum p_j v_j.  `act` rounds the weights
+    exp(score - row max) on their way into the second product, as a bfloat16 engine does
+    (the row sum is taken before the rounding).
     src/ops/attention.cu:188-250 (the reference computes the same sum with a running
     max; the two-pass form here is its CPU paged variant, src/ops/paged_attention.cpp:159-217)."""
     T, nq, d = q.shape
@@ -98,8 +100,9 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         kh = h // group
         s = (q[:, h, :] @ k[:, kh, :].T) * scale
         s = s.masked_fill(~visible, float("-inf"))
-        p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, kh, :]
+        e = torch.exp(s - s.max(dim=-1, keepdim=True).values)          # 0 where masked
+        total = e.sum(dim=-1, keepdim=True)
+        out[:, h, :] = ((e if act is None else act(e)) @ v[:, kh, :]) / total
     return out
 
 
@@ -120,14 +123,16 @@ def attention_qkv(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.T
 
 
 def attention_block(x: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
-                    prefix: str, cfg: dict, window: Optional[int] = None, act=identity, kv=None) -> torch.Tensor:
+                    prefix: str, cfg: dict, window: Optional[int] = None, act=identity, kv=None,
+                    attn_act=None) -> torch.Tensor:
     """Attention over this layer's own keys and values, or over `kv` = (k, v) of another layer
-    when given; then the output projection.  src/model/qwen3.cpp:550-567"""
+    when given; then the output projection.  `attn_act` rounds the attention weights (see
+    `causal_attention`).  src/model/qwen3.cpp:550-567"""
     T = x.shape[0]
     q, k, v = attention_qkv(x, positions, w, prefix, cfg, act, with_kv=kv is None)
     if kv is not None:
         k, v = kv
-    a = act(causal_attention(q, k, v, window=window))
+    a = act(causal_attention(q, k, v, window=window, act=attn_act))
     return a.reshape(T, -1) @ w[f"{prefix}.o_proj.weight"].T
 
 
@@ -144,18 +149,19 @@ def swiglu(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, act=identit
 
 
 def decoder_layer(h: torch.Tensor, positions: torch.Tensor, w: Dict[str, torch.Tensor],
-                  layer: int, cfg: dict, window: Optional[int] = None, act=identity) -> torch.Tensor:
+                  layer: int, cfg: dict, window: Optional[int] = None, act=identity, attn_act=None) -> torch.Tensor:
     """h += attn(norm_in(h)); h += mlp(norm_post(h)).  src/model/qwen3.cpp:948-968"""
     p = f"model.layers.{layer}"
     a = attention_block(act(rms_norm(h, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])),
-                        positions, w, f"{p}.self_attn", cfg, window, act)
+                        positions, w, f"{p}.self_attn", cfg, window, act, attn_act=attn_act)
     h = h + a
     f = swiglu(act(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])), w, f"{p}.mlp", act)
     return h + f
 
 
 def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
-                   layer_order: Optional[List[int]] = None, act=identity, wd=torch.float32) -> torch.Tensor:
+                   layer_order: Optional[List[int]] = None, act=identity, wd=torch.float32,
+                   attn_act=None) -> torch.Tensor:
     """Logits [T, V] for a whole sequence starting at position 0: embedding, the
     layers in order, final RMSNorm, output head (the embedding table when tied and
     `lm_head.weight` is absent).  src/model/qwen3.cpp:1242-1278,1501"""
@@ -165,7 +171,7 @@ def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
     h = embedding(ids, w["model.embed_tokens.weight"]).to(wd)
     order = layer_order if layer_order is not None else list(range(cfg["num_hidden_layers"]))
     for layer in order:
-        h = decoder_layer(h, positions, w, layer, cfg, act=act)
+        h = decoder_layer(h, positions, w, layer, cfg, act=act, attn_act=attn_act)
     hn = act(rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w.get("lm_head.weight")
     if head is None:

@@ -162,12 +162,20 @@ def run_trace(runner, steps: List[dict]) -> Dict[Tuple[str, int], np.ndarray]:
     return collect(steps, got)
 
 
+def rounds_attention_weights(cfg: dict) -> bool:
+    """The tensor-core attention kernels (head sizes 64 and 128) hand the weights exp(score - max)
+    to the second product as bfloat16; the generic kernel, which every other head size runs,
+    keeps them in float32."""
+    return cfg["head_dim"] in (64, 128)
+
+
 def plain_rows(cfg: dict, weights, reqs: Dict[str, List[int]], dtype: str = "float32") -> Dict[str, np.ndarray]:
     """Whole-sequence logits from the plain code.  For a float32 run the oracle works in double
     precision, so that the error measured is the engine's own; for a bfloat16 run it works in
     float32 and rounds to bfloat16 where the engine does."""
     if dtype == "bfloat16":
-        return {r: pq.forward_logits(t, weights, cfg, act=pq.to_bf16).numpy() for r, t in reqs.items()}
+        attn_act = pq.to_bf16 if rounds_attention_weights(cfg) else None
+        return {r: pq.forward_logits(t, weights, cfg, act=pq.to_bf16, attn_act=attn_act).numpy() for r, t in reqs.items()}
     return {r: pq.forward_logits(t, weights, cfg, wd=torch.float64).numpy() for r, t in reqs.items()}
 
 

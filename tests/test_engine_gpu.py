@@ -15,9 +15,20 @@ MODELS = {
     "B": (tm.TINY_B, tm.TINY_B_SEED, tm.TINY_B_PAGE),
     "C": (tm.TINY_C, tm.TINY_C_SEED, tm.TINY_C_PAGE),
     "D": (tm.TINY_D, tm.TINY_D_SEED, tm.TINY_D_PAGE),
+    "E": (tm.TINY_E, tm.TINY_E_SEED, tm.TINY_E_PAGE),
+    "F": (tm.TINY_F, tm.TINY_F_SEED, tm.TINY_F_PAGE),
 }
 LENGTHS = {"A": [5, 9, 13, 40, 77], "B": [1, 7, 16, 33, 70, 121], "C": [64, 97, 150, 333],
-           "D": [2, 63, 64, 65, 129, 200, 333, 700]}
+           "D": [2, 63, 64, 65, 129, 200, 333, 700], "E": [2, 64, 127, 128, 129, 200, 333, 700],
+           "F": [3, 65, 130, 257, 500]}
+
+
+# Factor on the q-norm weights.  Head size 128 gets a smaller one: with 4 the plain code's own
+# bfloat16 emulation is 3e-2 (E) and 5e-2 (F) of the largest logit away from exact arithmetic, against
+# 1.6e-2 for D, and a comparison at 1e-2 would only measure on which side single roundings fall (the
+# worst positions are then scattered decoded tokens, a different one for each way of cutting).  With 2
+# the emulation's own error is 9e-3 and 7e-3.
+SHARPEN = {"A": 4.0, "B": 4.0, "C": 4.0, "D": 4.0, "E": 2.0, "F": 2.0}
 
 
 def setup(name, dtype, sharp=True):
@@ -25,13 +36,13 @@ def setup(name, dtype, sharp=True):
     bf = dtype == "bfloat16"
     w = tm.make_weights(cfg, seed, bf16_exact=bf)
     if sharp:
-        w = rh.sharpen(w, 4.0, bf16_exact=bf)
+        w = rh.sharpen(w, SHARPEN[name], bf16_exact=bf)
     reqs = rh.requests_for(cfg, LENGTHS[name], seed)
     return cfg, page, w, reqs
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
     cfg, page, w, reqs = setup(name, dtype)
     ref = rh.plain_rows(cfg, w, reqs, dtype)
@@ -58,7 +69,7 @@ def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype):
         rh.assert_rows_match(results[what], whole, cut_tol, f"{name} {dtype} {what} against whole")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_bfloat16_against_the_plain_float32_code(name):
     """Unsharpened N(0, 0.02) weights, bfloat16 run, plain code in float32 without any rounding."""
     cfg, page, w, reqs = setup(name, "bfloat16", sharp=False)

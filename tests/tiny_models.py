@@ -1,4 +1,4 @@
-"""The two tiny Qwen3 configurations the tests use, and their seeded weights.
+"""The tiny Qwen3 configurations the tests use, and their seeded weights.
 
 They differ in every size and option: layer count, hidden size, head counts and
 group size, head_dim (A: heads*head_dim == hidden; B: != hidden), intermediate size,
@@ -51,6 +51,27 @@ TINY_D = dict(
     torch_dtype="bfloat16",
 )
 TINY_D_PAGE, TINY_D_SEED = 16, 11
+
+
+# Head size 128: prompt portions run the tcgen05 kernel.  E has groups of two query heads
+# (two heads share a key/value tile in one CTA), F a group of three (one head per CTA).
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=160, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=128, intermediate_size=192, vocab_size=307, rope_theta=1000000.0,
+    rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=False,
+    torch_dtype="bfloat16",
+)
+TINY_E_PAGE, TINY_E_SEED = 16, 13
+
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=112, num_attention_heads=3, num_key_value_heads=1,
+    head_dim=128, intermediate_size=144, vocab_size=199, rope_theta=10000.0,
+    rms_norm_eps=2e-6, max_position_embeddings=2048, tie_word_embeddings=True,
+    torch_dtype="bfloat16",
+)
+TINY_F_PAGE, TINY_F_SEED = 32, 17
 
 
 def tensor_shapes(cfg: dict) -> dict:
