@@ -51,6 +51,43 @@ extern "C" int llm_silu_and_mul(const void* gu, void* out, int dtype, int num_to
     return launch_status();
 }
 
+// The same over a product left as `slices` float32 partial sums [slices, tokens, 2*inter]: the
+// slices are added in order and, for a bfloat16 result, rounded to bfloat16 first, which is
+// what reading the finished bfloat16 product would have given.
+template <typename T>
+__global__ void silu_and_mul_parts_kernel(const float* __restrict__ parts, int slices, T* __restrict__ out, int inter,
+                                          long long slice_stride) {
+    pdl_begin();
+    const size_t t = blockIdx.y;
+    const float* g = parts + t * 2 * inter;
+    T* o = out + t * inter;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter; i += gridDim.x * blockDim.x) {
+        float a = 0.0f, b = 0.0f;
+        for (int z = 0; z < slices; ++z) {
+            a += g[z * slice_stride + i];
+            b += g[z * slice_stride + inter + i];
+        }
+        o[i] = from_f32<T>(silu(to_f32(from_f32<T>(a))) * to_f32(from_f32<T>(b)));
+    }
+}
+
+extern "C" int llm_silu_and_mul_parts(const float* parts, int slices, void* out, int dtype, int num_tokens, int inter,
+                                      uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (inter <= 0 || num_tokens > 65535 || slices < 1) return LLM_REFUSED_SIZE;
+    const int threads = 256;
+    const dim3 grid(std::min((inter + threads - 1) / threads, 4096), num_tokens);
+    const long long stride = static_cast<long long>(num_tokens) * 2 * inter;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == LLM_DT_F32)
+        launch_pdl((silu_and_mul_parts_kernel<float>), grid, dim3(threads), 0, s, parts, slices, static_cast<float*>(out), inter, stride);
+    else if (dtype == LLM_DT_BF16)
+        launch_pdl((silu_and_mul_parts_kernel<bf16>), grid, dim3(threads), 0, s, parts, slices, static_cast<bf16*>(out), inter, stride);
+    else
+        return LLM_REFUSED_DTYPE;
+    return launch_status();
+}
+
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, long long n) {
     pdl_begin();

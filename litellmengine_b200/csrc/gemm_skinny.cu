@@ -1,15 +1,18 @@
 // y[M, N] = x[M, K] . w[N, K]^T for a handful of rows (decode steps): a weight-streaming kernel.
 //
 // With few rows the product is bound by reading w once, and what decides the speed is how many
-// bytes of w each SM keeps in flight.  The library's kernels for these shapes do well when N is
-// large and reach only 40-60 % of the memory bandwidth when N is small (N = 4096 or 6144 gives
-// fewer thread blocks than the GPU has SMs).  Here a CTA owns 64 output features (one 16-row
-// tensor-core tile per warp) and a slice of K, and streams its part of w through six (five for
-// 16 tokens) shared-memory stages of 128 k-values with cp.async (16 KB of w and up to 4 KB of x per stage),
-// two CTAs per SM.  The K dimension is split so that the grid fills the GPU once or twice
-// exactly; each split writes float32 partial sums to scratch and a second small kernel adds them
-// in a fixed order (no atomics: the result does not depend on timing).  With one split the
-// result is written directly.
+// bytes of w each SM keeps in flight and whether every SM is busy until the end.  The library's
+// kernels for these shapes reach 40-60 % of the memory bandwidth when N is small (N = 4096 or 6144
+// gives fewer thread blocks than the GPU has SMs).  Here the work is cut into items of 64 output
+// features (one 16-row tensor-core tile per warp) by 128 k-values, numbered feature tile by
+// feature tile, and the grid is persistent: two CTAs per SM, each taking one contiguous run of
+// items of (nearly) the same length, whatever N and K are.  A CTA streams its items through six
+// (five for 16 tokens) shared-memory stages with cp.async (16 KB of w and up to 4 KB of x per
+// stage) without draining the pipeline between feature tiles.  A feature tile whose items lie in
+// several CTAs gets one float32 partial sum from each, in a slice numbered by the CTA's place
+// among them (the CTA that finishes the tile zeroes the slices nobody uses); a second small
+// kernel, or the consumer, adds the slices in order (no atomics: the result does not depend on
+// timing).  When every tile lies in one CTA the result is written directly.
 // The product runs on the tensor cores with the roles swapped: w is the 16-row A operand of
 // mma.sync m16n8k16 and the tokens are the 8 columns of B (8 tokens use a full instruction,
 // 16 tokens two).  Accumulation is float32; the result is float32 or bfloat16.
@@ -20,7 +23,6 @@
 #define GS_BK 128           // k-values per stage
 #define GS_STAGES_FOR(MT) ((MT) <= 8 ? 6 : 5)   // two CTAs per SM must fit: (64 + MT) rows * 256 B per stage
 #define GS_THREADS 128
-#define GS_MAX_SPLITS 16
 
 __device__ __forceinline__ void gs_cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
@@ -44,25 +46,41 @@ __device__ __forceinline__ bf16* gs_at(bf16* base, int row, int chunk) {
     return base + row * GS_BK + ((chunk ^ (row & 7)) << 3);
 }
 
-// MT: token tile (8 or 16).  grid (feature tiles, k splits).
+// Which CTA of `ctas` holds item `item` when CTA c takes items [c*total/ctas, (c+1)*total/ctas).
+__host__ __device__ __forceinline__ long long gs_cta_of(long long item, long long total, long long ctas) {
+    return ((item + 1) * ctas - 1) / total;
+}
+
+// MT: token tile (8 or 16).  grid: the persistent CTAs.  slices: float32 partial-sum slices of
+// [M, N] in `partial` (1: none, y is written directly).
 template <int MT, typename TO>
 __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* __restrict__ x,
                                                                    const bf16* __restrict__ w, TO* __restrict__ y,
-                                                                   float* __restrict__ partial, int M, int N, int K) {
+                                                                   float* __restrict__ partial, int M, int N, int K,
+                                                                   int slices, int per_tile) {
     constexpr int GS_STAGES = GS_STAGES_FOR(MT);
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK]
     bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * GS_ROWS;
-    const int nk_all = (K + GS_BK - 1) / GS_BK, splits = gridDim.y;
-    const int kt_begin = static_cast<int>(static_cast<long long>(blockIdx.y) * nk_all / splits);
-    const int kt_end = static_cast<int>(static_cast<long long>(blockIdx.y + 1) * nk_all / splits);
-    const int nk = kt_end - kt_begin;
+    const int nk = (K + GS_BK - 1) / GS_BK, tiles = (N + GS_ROWS - 1) / GS_ROWS;
+    const long long total = static_cast<long long>(tiles) * nk, ctas = gridDim.x;
+    long long begin;
+    int count;
+    if (per_tile) {                                                      // `per_tile` CTAs share each tile's k-values evenly
+        const int t = blockIdx.x / per_tile, part = blockIdx.x % per_tile;
+        const int k_begin = static_cast<int>(static_cast<long long>(part) * nk / per_tile);
+        begin = static_cast<long long>(t) * nk + k_begin;
+        count = static_cast<int>(static_cast<long long>(part + 1) * nk / per_tile) - k_begin;
+    } else {                                                             // one run of all items, cut evenly
+        begin = blockIdx.x * total / ctas;
+        count = static_cast<int>((blockIdx.x + 1) * total / ctas - begin);
+    }
     constexpr int CPR = GS_BK / 8;                                       // 16-byte chunks per row of a stage
 
-    auto load_w = [&](int i) {                                           // weights of k-tile kt_begin + i into stage i % STAGES
-        const int k0 = (kt_begin + i) * GS_BK;
+    auto load_w = [&](int i) {                                           // weights of item begin + i into stage i % STAGES
+        const long long item = begin + i;
+        const int n0 = static_cast<int>(item / nk) * GS_ROWS, k0 = static_cast<int>(item % nk) * GS_BK;
         bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
 #pragma unroll
         for (int j = 0; j < GS_ROWS * CPR / GS_THREADS; ++j) {
@@ -71,8 +89,8 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
             gs_cp_async16(gs_at(ws, row, ch), w + (valid ? static_cast<size_t>(n0 + row) * K + k0 + ch * 8 : 0), valid);
         }
     };
-    auto load_x = [&](int i) {                                           // the tokens' rows for the same k-tile
-        const int k0 = (kt_begin + i) * GS_BK;
+    auto load_x = [&](int i) {                                           // the tokens' rows for the same k-values
+        const int k0 = static_cast<int>((begin + i) % nk) * GS_BK;
         bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
 #pragma unroll
         for (int j = 0; j < MT * CPR / GS_THREADS; ++j) {
@@ -87,21 +105,22 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
     pdl_invite();
 #pragma unroll
     for (int s = 0; s < GS_STAGES - 1; ++s)
-        if (s < nk) load_w(s);
+        if (s < count) load_w(s);
     pdl_wait();
 #pragma unroll
     for (int s = 0; s < GS_STAGES - 1; ++s) {
-        if (s < nk) load_x(s);
+        if (s < count) load_x(s);
         gs_commit();                                                     // group 0 also holds every weight copy above
     }
     float acc[MT / 8][4];
 #pragma unroll
     for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
 
-    for (int i = 0; i < nk; ++i) {
+    int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk);
+    for (int i = 0; i < count; ++i) {
         gs_wait<GS_STAGES - 2>();
         __syncthreads();
-        if (i + GS_STAGES - 1 < nk) {
+        if (i + GS_STAGES - 1 < count) {
             load_w(i + GS_STAGES - 1);
             load_x(i + GS_STAGES - 1);
         }
@@ -121,21 +140,33 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
                 gs_mma(acc[j], a1, b[2], b[3]);
             }
         }
-    }
-    gs_wait<0>();
-    // acc[j]: features warp*16 + lane/4 (+8), tokens j*8 + (lane%4)*2 (+1)
-    const int f0 = n0 + warp * 16 + (lane >> 2), t0 = (lane & 3) * 2;
+        const bool tile_done = kt == nk - 1;
+        if (tile_done || i == count - 1) {
+            // acc[j]: features warp*16 + lane/4 (+8), tokens j*8 + (lane%4)*2 (+1)
+            const int f0 = tile * GS_ROWS + warp * 16 + (lane >> 2), t0 = (lane & 3) * 2;
+            const int slice = per_tile ? static_cast<int>(blockIdx.x % per_tile)
+                                       : static_cast<int>(blockIdx.x - gs_cta_of(static_cast<long long>(tile) * nk, total, ctas));
 #pragma unroll
-    for (int j = 0; j < MT / 8; ++j) {
+            for (int j = 0; j < MT / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int f = f0 + (e >> 1) * 8, tok = j * 8 + t0 + (e & 1);
-            if (f < N && tok < M) {
-                if (splits == 1) y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[j][e]);
-                else partial[(static_cast<size_t>(blockIdx.y) * M + tok) * N + f] = acc[j][e];
+                for (int e = 0; e < 4; ++e) {
+                    const int f = f0 + (e >> 1) * 8, tok = j * 8 + t0 + (e & 1);
+                    if (f < N && tok < M) {
+                        if (slices == 1) {
+                            y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[j][e]);
+                        } else {
+                            partial[(static_cast<size_t>(slice) * M + tok) * N + f] = acc[j][e];
+                            if (tile_done && !per_tile)                  // nobody else comes after: clear the unused slices
+                                for (int z = slice + 1; z < slices; ++z) partial[(static_cast<size_t>(z) * M + tok) * N + f] = 0.0f;
+                        }
+                    }
+                    acc[j][e] = 0.0f;
+                }
             }
         }
+        if (tile_done) { kt = 0; ++tile; } else ++kt;
     }
+    gs_wait<0>();
 }
 
 // y[tok, f] = sum over splits of partial[split, tok, f], in split order.
@@ -155,64 +186,86 @@ extern "C" int llm_linear_skinny_supported(int M, int N, int K) {
 
 static int g_skinny_slots = 0;     // CTAs the current device holds at once (two per SM), found at the first call
 
-// How many k-splits a call uses: the grid should fill the GPU's CTA slots once or twice exactly.
-static int skinny_splits(int N, int K) {
-    const int tiles = (N + GS_ROWS - 1) / GS_ROWS, nk = (K + GS_BK - 1) / GS_BK;
-    if (tiles >= g_skinny_slots) return 1;
-    int best = 1;
-    for (int s = 1; s <= GS_MAX_SPLITS && s <= nk / 4; ++s)             // at least 4 stages per split
+static bool skinny_device() {
+    if (g_skinny_slots) return true;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return false;
+    g_skinny_slots = sms * 2;
+    return true;
+}
+
+// The grid for a product and the number of partial-sum slices it leaves (1 = none).  When whole
+// CTAs per feature tile fill at least 85 % of the GPU's CTA slots, each tile's k-values are shared
+// evenly by `per_tile` CTAs (fewest slices); otherwise (more tiles than slots, or a poor fit) the
+// items are cut into one even run per slot (per_tile = 0).
+static void skinny_plan(int N, int K, int* ctas, int* slices, int* per_tile) {
+    const long long tiles = (N + GS_ROWS - 1) / GS_ROWS, nk = (K + GS_BK - 1) / GS_BK, total = tiles * nk;
+    long long best = 0;
+    for (long long s = 1; s <= 16 && s <= (nk >= 4 ? nk / 4 : 1); ++s)   // at least four items per CTA
         if (tiles * s <= g_skinny_slots) best = s;
-    return best;
+    if (best && tiles * best * 100 >= 85LL * g_skinny_slots) {
+        *ctas = static_cast<int>(tiles * best);
+        *slices = *per_tile = static_cast<int>(best);
+        return;
+    }
+    long long g = total / 4;                                             // at least four items per CTA
+    if (g < 1) g = 1;
+    if (g > g_skinny_slots) g = g_skinny_slots;
+    int s = 1;
+    if (!(total % g == 0 && (total / g) % nk == 0)) {                    // some tile is cut
+        s = 0;
+        for (long long t = 0; t < tiles; ++t) {                          // the most CTAs that meet in one tile
+            const int n = static_cast<int>(gs_cta_of((t + 1) * nk - 1, total, g) - gs_cta_of(t * nk, total, g)) + 1;
+            if (n > s) s = n;
+        }
+    }
+    *ctas = static_cast<int>(g);
+    *slices = s;
+    *per_tile = 0;
 }
 
 // Floats of scratch a call needs for its partial sums.
 extern "C" long long llm_linear_skinny_scratch_floats(int M, int N, int K) {
-    if (g_skinny_slots == 0) return static_cast<long long>(GS_MAX_SPLITS) * M * N;
-    const int s = skinny_splits(N, K);
-    return s > 1 ? static_cast<long long>(s) * M * N : 0;
+    if (!skinny_device()) return 0;
+    int ctas, slices, per_tile;
+    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    return slices > 1 ? static_cast<long long>(slices) * M * N : 0;
 }
 
-// The number of k-splits a product of these sizes is cut into on the current device.
+// The number of partial-sum slices a product of these sizes leaves on the current device.
 extern "C" int llm_linear_skinny_splits(int M, int N, int K) {
-    if (g_skinny_slots == 0) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            return 1;
-        g_skinny_slots = sms * 2;
-    }
+    if (!skinny_device()) return 1;
     (void)M;
-    return skinny_splits(N, K);
+    int ctas, slices, per_tile;
+    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    return slices;
 }
 
 template <int MT, typename TO>
 static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, long long scratch_floats, int M, int N,
                          int K, int keep_partials, cudaStream_t s) {
-    if (g_skinny_slots == 0) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            return LLM_REFUSED_SIZE;
-        g_skinny_slots = sms * 2;
-    }
+    if (!skinny_device()) return LLM_REFUSED_SIZE;
     const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK * sizeof(bf16);
     auto kern = linear_skinny_kernel<MT, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    int splits = skinny_splits(N, K);
-    if (splits > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(splits) * M * N)) splits = 1;
-    dim3 grid((N + GS_ROWS - 1) / GS_ROWS, splits);
-    launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K);
+    int ctas, slices, per_tile;
+    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * M * N))
+        return LLM_REFUSED_SIZE;                                         // the caller sizes scratch with llm_linear_skinny_scratch_floats
+    launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile);
     int rc = launch_status();
-    if (rc != LLM_OK || splits == 1 || keep_partials) return rc;     // the caller's next kernel adds the splits itself
+    if (rc != LLM_OK || slices == 1 || keep_partials) return rc;     // the caller's next kernel adds the slices itself
     const long long mn = static_cast<long long>(M) * N;
-    launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, splits);
+    launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, slices);
     return launch_status();
 }
 
 // x: bfloat16 [M, K]; w: bfloat16 [N, K]; y: [M, N] float32 (out_dtype 0) or bfloat16 (1);
-// scratch: float32 of scratch_floats elements (without enough scratch K is not split).
-// keep_partials: with more than one split, leave the splits' sums in scratch as [splits, M, N]
+// scratch: float32 of scratch_floats elements (llm_linear_skinny_scratch_floats tells how many).
+// keep_partials: with more than one slice, leave the partial sums in scratch as [slices, M, N]
 // and write nothing to y (llm_linear_skinny_splits tells the count beforehand).
 extern "C" int llm_linear_skinny(const void* x, const void* w, void* y, int out_dtype, float* scratch,
                                  long long scratch_floats, int M, int N, int K, int keep_partials, uintptr_t stream) {

@@ -102,6 +102,9 @@ def main():
     ap.add_argument("--out-dtype", default="bfloat16")
     ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
+    ap.add_argument("--chain", type=int, default=0,
+                    help="linear: time CHAIN launches back to back, each over weights of its own (together larger "
+                         "than L2), as one CUDA graph; the figure is the time per launch inside a stream of kernels")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -172,11 +175,29 @@ def main():
             fn = lambda: ops.linear_skinny(x, w, od)
         else:
             fn = lambda: ops.linear(x, w, out_dtype=od)
+        if args.chain:
+            ws = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(args.chain)]
+            one = {"library": lambda wi: torch.mm(x, wi.t(), out_dtype=od) if od != x.dtype else torch.mm(x, wi.t()),
+                   "own": lambda wi: ops.linear_skinny(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for wi in ws:
+                    one(wi)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for wi in ws:
+                        one(wi)
+            chain_fn = graph.replay
+            fn = lambda: chain_fn()
+            res["chain"] = args.chain
         res["impl"] = args.impl
         res.update(m=args.tokens, n=args.n, k=args.k, bytes=args.n * args.k * 2 + args.tokens * (args.k * 2 + args.n * od.itemsize),
                    flops=2 * args.tokens * args.n * args.k)
 
     sec = timed(fn, args.iters, args.warmup, flush)
+    if args.kernel == "linear" and args.chain:
+        sec /= args.chain
     res["us"] = round(sec * 1e6, 2)
     if "bytes" in res:
         res["GB/s"] = round(res["bytes"] / sec / 1e9, 1)

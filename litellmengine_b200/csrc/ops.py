@@ -54,8 +54,9 @@ class PartialSum:
     is the result.  The engine's norm and q/k kernels add the splits while they read, which
     saves a kernel per product in decode steps; `as_tensor` adds them for anyone else."""
 
-    def __init__(self, parts: torch.Tensor):
+    def __init__(self, parts: torch.Tensor, rounds_to: Optional[torch.dtype] = None):
         self.parts = parts
+        self.rounds_to = rounds_to      # the product's own dtype when it is not float32: the sum is rounded to it
 
     @property
     def shape(self):
@@ -67,7 +68,10 @@ class PartialSum:
 
 
 def as_tensor(x):
-    return x.parts.sum(dim=0) if isinstance(x, PartialSum) else x
+    if not isinstance(x, PartialSum):
+        return x
+    total = x.parts.sum(dim=0)
+    return total.to(x.rounds_to) if x.rounds_to is not None else total
 
 
 launch_count = 0          # launches of the engine's own kernels since import (library products are not counted)
@@ -168,8 +172,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def silu_and_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """[T, 2I] -> [T, I]: silu(first half) * second half."""
+def silu_and_mul(gate_up, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, 2I] -> [T, I]: silu(first half) * second half.  A `PartialSum` is added up on the way."""
+    if isinstance(gate_up, PartialSum):
+        parts = gate_up.parts
+        _dev(parts, out)
+        S, T, two_i = parts.shape
+        if out is None:
+            out = torch.empty((T, two_i // 2), dtype=gate_up.rounds_to or torch.float32, device=parts.device)
+        f = _fn("activation", "llm_silu_and_mul_parts", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(f(_ptr(parts), S, _ptr(out), _dt(out), T, two_i // 2, _stream()), "silu_and_mul")
+        return out
     _dev(gate_up, out)
     T, two_i = gate_up.shape
     inter = two_i // 2
@@ -437,10 +450,10 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     f = _fn("gemm_skinny", "llm_linear_skinny",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
     splits = _fn("gemm_skinny", "llm_linear_skinny_splits", [c_int, c_int, c_int])(M, N, K)
-    if partials_ok and splits > 1 and out is None and out_dtype == torch.float32:
+    if partials_ok and splits > 1 and out is None:
         parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
         _check(f(_ptr(x), _ptr(weight), None, 0, _ptr(parts), parts.numel(), M, N, K, 1, _stream()), "linear_skinny")
-        return PartialSum(parts)
+        return PartialSum(parts, None if out_dtype == torch.float32 else out_dtype)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     scratch = skinny_scratch(x.device, splits * M * N if splits > 1 else 0)

@@ -39,6 +39,6 @@ class SwiGLU:
     supports_partials = True   # forward(x, partials_ok=True) may return an ops.PartialSum
 
     def forward(self, x: torch.Tensor, partials_ok: bool = False):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype)
+        gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype, partials_ok=True)     # silu_and_mul adds the slices
         return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=torch.float32,
                           partials_ok=partials_ok)                                    # joins the residual
