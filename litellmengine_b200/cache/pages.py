@@ -290,6 +290,18 @@ class CacheManager:
                     need[i] += m
         return new_slots <= self.free_slots and all(n <= g.pool.free_count for n, g in zip(need, self.groups))
 
+    def reserve(self, need: Sequence[int], slot: Optional[int], new_len: int) -> Optional[List[int]]:
+        """`need` (pages per group already promised in this step) plus what (slot or None, new
+        length) wants, or None if that does not fit the free pages.  `can_hold` one request at a
+        time, for callers that build a step up."""
+        if new_len > self.max_request_tokens:
+            return None
+        if slot is None:
+            total = [n + g.pages_for(new_len) for n, g in zip(need, self.groups)]
+        else:
+            total = [n + m for n, m in zip(need, self.pages_missing(slot, new_len))]
+        return total if all(t <= g.pool.free_count for t, g in zip(total, self.groups)) else None
+
     def ensure(self, slot: int, new_len: int) -> None:
         """Make room for positions [0, new_len) of the request, in every group, or take nothing."""
         self._check_live(slot)

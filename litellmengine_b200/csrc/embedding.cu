@@ -2,6 +2,8 @@
 // held in 32-bit).  An id outside [0, vocab) writes a zero row and records the first such
 // token in `status` ({code, token index}); nothing traps.  The reference does the same gather
 // with one element per thread and a blocking read of its error flag (src/layers/embedding.cu:91-158).
+// A negative id -1-j stands for feedback[j]: the token that the previous step sampled into a
+// device buffer, which the host has not read yet when it launches this step.
 //
 // Also here: the small scatter that applies a step's block-table changes on the device.
 #include "common.cuh"
@@ -9,10 +11,12 @@
 template <typename T>
 __global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
-                                        int32_t* __restrict__ status) {
+                                        int32_t* __restrict__ status, const int32_t* __restrict__ feedback,
+                                        int feedback_len) {
     pdl_begin();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (id < 0 && feedback != nullptr && -1 - id < feedback_len) id = feedback[-1 - id];
     float* o = out + static_cast<size_t>(t) * hidden;
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0 && atomicCAS(status, 0, 1) == 0) status[1] = t;
@@ -33,7 +37,7 @@ __global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const T
 
 extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int table_dtype, float* out,
                                     int num_tokens, int hidden, int vocab, int32_t* status,
-                                    uintptr_t stream) {
+                                    const int32_t* feedback, int feedback_len, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (hidden <= 0 || vocab <= 0) return LLM_REFUSED_SIZE;
     if ((hidden & 7) == 0 && (!aligned16(table) || !aligned16(out))) return LLM_REFUSED_ALIGN;
@@ -41,10 +45,10 @@ extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int t
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (table_dtype == LLM_DT_F32)
         launch_pdl((embedding_gather_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, 
-            ids, static_cast<const float*>(table), out, hidden, vocab, status);
+            ids, static_cast<const float*>(table), out, hidden, vocab, status, feedback, feedback_len);
     else if (table_dtype == LLM_DT_BF16)
         launch_pdl((embedding_gather_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, 
-            ids, static_cast<const bf16*>(table), out, hidden, vocab, status);
+            ids, static_cast<const bf16*>(table), out, hidden, vocab, status, feedback, feedback_len);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -120,16 +120,19 @@ def _i32(t: Optional[torch.Tensor], what: str) -> None:
 
 # ------------------------------------------------------------------------------------------
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 [T, H] = table[ids]."""
-    _dev(ids, table, status, out)
+              out: Optional[torch.Tensor] = None, feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [T, H] = table[ids]; an id -1-j takes its token from feedback[j] (int32, on the device)."""
+    _dev(ids, table, status, out, feedback)
     _i32(ids, "ids")
+    if feedback is not None:
+        _i32(feedback, "feedback")
     T, (V, H) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     f = _fn("embedding", "llm_embedding_gather",
-            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(status), _stream()), "embedding")
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(status), _ptr(feedback),
+             feedback.numel() if feedback is not None else 0, _stream()), "embedding")
     return out
 
 

@@ -26,6 +26,8 @@ class StepEntry:
     tokens: Sequence[int]
     want: Sequence[int] = ()
     past: int = 0                     # filled in by the step function: tokens already cached
+    feedback: int = -1                # >= 0: the LAST token is not known to the host yet; it is entry
+                                      # `feedback` of the tokens the previous step sampled on the device
 
 
 class StepBuffers:
@@ -99,9 +101,11 @@ class StepBatch:
     num_decode: int = 0
     num_prefill_tiles: int = 0
     entries: List[StepEntry] = field(default_factory=list)
+    feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
 
 
-def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBatch:
+def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
+              feedback: Optional[torch.Tensor] = None) -> StepBatch:
     """Fill the pinned buffer from `entries` (whose `past` is set) and the cache manager's
     pending table `updates`, start the copy, and return the device views."""
     T = sum(len(e.tokens) for e in entries)
@@ -121,6 +125,8 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
     for i, e in enumerate(entries):
         n = len(e.tokens)
         tok[row:row + n] = np.asarray(e.tokens, dtype=np.int32)
+        if e.feedback >= 0:
+            tok[row + n - 1] = -1 - e.feedback
         pos[row:row + n] = np.arange(e.past, e.past + n, dtype=np.int32)
         ent[row:row + n] = i
         slot[i], qs[i], ql[i], kl[i] = e.slot, row, n, e.past + n
@@ -159,4 +165,4 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates) -> StepBa
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
         decode_rows=dv("decode_rows", n_dec), prefill_tiles=dv("prefill_tiles", 2 * n_tiles).view(n_tiles, 2),
         num_decode=n_dec, num_prefill_tiles=n_tiles, status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
-        entries=entries)
+        entries=entries, feedback=feedback)

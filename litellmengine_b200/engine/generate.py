@@ -4,6 +4,13 @@ class of that name (include/engine/paged_generate_engine.hpp:14-87): `add_reques
 has `prefill`, `decode_one_step` and `decode_batch`, this has one `step()` that runs
 whatever the scheduler picked — prompt portions and decode tokens in the same batch — and
 `run()` that steps until every request is finished.
+
+Steps are pipelined by default: `step()` launches the next batch before it reads the tokens
+of the one before, so the device never waits for the host's scheduling and packing.  A
+request's next token then reaches the following step's embedding straight from the device
+buffer it was sampled into (`StepEntry.feedback`); the host reads it one step late, which
+is when finished requests are noticed.  `pipelined=False` reads every step's tokens before
+the next is planned, as the reference does.
 """
 from __future__ import annotations
 
@@ -21,7 +28,7 @@ from .scheduler import ScheduledPortion, Scheduler
 class PagedGenerateEngine:
     def __init__(self, model, dtype: str = "bfloat16", device: str = "cuda:0", page_size: int = 16,
                  max_total_tokens: int = 8192, max_requests: int = 64, max_tokens_per_step: int = 8192,
-                 chunk: Optional[int] = None, verbose: bool = False, seed: int = 0):
+                 chunk: Optional[int] = None, verbose: bool = False, seed: int = 0, pipelined: bool = True):
         """`model`: a model folder (config.json + *.safetensors), a typed configuration (random
         weights from `seed`, drawn on the device), or a ready `ModelRunner`."""
         if isinstance(model, ModelRunner):
@@ -36,7 +43,12 @@ class PagedGenerateEngine:
         self.scheduler = Scheduler(self.runner.cache, self.runner.buffers.max_tokens, chunk)
         self.sampler = Sampler(self.runner.cache.state["sampler"])
         self.verbose = verbose
-        self._tokens_pinned = torch.empty(self.runner.buffers.max_entries, dtype=torch.int32, pin_memory=True)
+        self.pipelined = pipelined
+        n = self.runner.buffers.max_entries
+        self._tokens_pinned = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._read_done = [torch.cuda.Event() for _ in range(2)]
+        self._launched = 0
+        self._in_flight = None            # (plan, requests that sample, which pinned buffer) of the launched step
 
     # ---- the reference's surface -------------------------------------------------------------
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int, eos_token_id: int = -1,
@@ -62,7 +74,8 @@ class PagedGenerateEngine:
 
     def release_request(self, request_id: int) -> None:
         """Forget a request.  A finished request holds no pages (they went back when it
-        finished); an unfinished one is taken out of the queues and its pages freed."""
+        finished); an unfinished one is taken out of the queues and its pages freed (a token of
+        it that a launched step is still sampling is dropped when it arrives)."""
         req = self.request(request_id)
         if not req.finished:
             if req in self.scheduler.running:
@@ -74,39 +87,67 @@ class PagedGenerateEngine:
         del self.scheduler.requests[request_id]
 
     # ---- stepping --------------------------------------------------------------------------
-    def step(self) -> List[tuple]:
-        """Run one scheduled batch.  Returns [(request id, sampled token)] of this step."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            return []
+    def _launch(self, plan: List[ScheduledPortion]):
+        """Everything of a step that needs no answer from the device: pages, metadata, kernels,
+        sampling into `runner.sampled`, and the start of the copy of the sampled tokens."""
         entries, samplers = [], []
         for p in plan:
             req = p.request
             if req.cached_len == 0:           # first portion since admission: bind its random stream
-                self.sampler.admit(req.slot, req.seed, len(req.generated_ids), req.temperature)
-            toks = req.input_ids[req.cached_len:req.cached_len + p.num_tokens]
-            entries.append(StepEntry(req.slot, toks, [p.num_tokens - 1] if p.samples else []))
+                self.sampler.admit(req.slot, req.seed, len(req.generated_ids) + req.pending, req.temperature)
+            end = req.cached_len + p.num_tokens
+            toks = req.input_ids[req.cached_len:end]
+            feedback = -1
+            if end > len(req.input_ids):      # the portion ends with the token that is still on the device
+                toks = toks + [0]
+                feedback = req.feedback_index
+            entries.append(StepEntry(req.slot, toks, [p.num_tokens - 1] if p.samples else [], feedback=feedback))
             if p.samples:
                 samplers.append(req)
         batch = self.runner.prepare(entries)
         logits = self.runner.forward(batch)
         self.runner.finish(batch)
+        which = self._launched & 1
+        self._launched += 1
+        if samplers:
+            dev = self.sampler.sample(logits, batch.want_slot, any(r.temperature > 0 for r in samplers),
+                                      out=self.runner.sampled[:len(samplers)])
+            self._tokens_pinned[which][:len(samplers)].copy_(dev, non_blocking=True)
+            self._read_done[which].record()
+        if self.verbose:
+            print(f"[step {self.runner.steps_run}] tokens={batch.num_tokens} entries={batch.num_entries}")
+        return plan, samplers, which
+
+    def _deliver(self, launched) -> List[tuple]:
+        plan, samplers, which = launched
         tokens: List[int] = []
         if samplers:
-            dev = self.sampler.sample(logits, batch.want_slot, any(r.temperature > 0 for r in samplers))
-            host = self._tokens_pinned[:len(samplers)]
-            host.copy_(dev, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            tokens = host.tolist()
-        out = [(r.request_id, t) for r, t in zip(samplers, tokens)]
-        self.scheduler.update(plan, tokens)
-        if self.verbose:
-            print(f"[step {self.runner.steps_run}] tokens={batch.num_tokens} entries={batch.num_entries} "
-                  f"sampled={out}")
+            self._read_done[which].synchronize()
+            tokens = self._tokens_pinned[which][:len(samplers)].tolist()
+        out = [(r.request_id, t) for r, t in self.scheduler.deliver(plan, tokens)]
+        if self.verbose and out:
+            print(f"[tokens] {out}")
         return out
 
+    def step(self) -> List[tuple]:
+        """Launch one scheduled batch and return [(request id, token)] of the tokens that
+        became known to the host in this call: this batch's own when not pipelined, the
+        previous batch's when pipelined (an empty list at the very first step)."""
+        plan = self.scheduler.schedule()
+        launched = None
+        if plan:
+            launched = self._launch(plan)
+            self.scheduler.advance(plan)
+        if not self.pipelined:
+            return self._deliver(launched) if launched else []
+        before, self._in_flight = self._in_flight, launched
+        return self._deliver(before) if before else []
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._in_flight is not None
+
     def run(self) -> None:
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         self.runner.check_status()
 

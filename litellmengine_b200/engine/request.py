@@ -6,7 +6,9 @@ prompt plus generated tokens; `cached_len` counts tokens whose keys and values a
 cache; a sampled token equal to `eos_token_id` (when >= 0) finishes the request and is kept;
 so does reaching `max_new_tokens`; `max_new_tokens == 0` is finished at once.  Added: the
 `Waiting` state covers both a request never run and one preempted (its pages were taken
-away, its tokens kept), and a request may be prefilled in portions.
+away, its tokens kept), and a request may be prefilled in portions.  `pending` counts a
+token that a launched step has sampled on the device and the host has not read yet: it is
+part of the request's length (the next step may already run it) but not of `input_ids`.
 """
 from __future__ import annotations
 
@@ -36,19 +38,22 @@ class GenerationRequest:
     status: RequestStatus = RequestStatus.WAITING
     preemptions: int = 0
     finish_reason: Optional[str] = None
+    pending: int = 0             # sampled tokens of this request that are still on the device (1 when a step is planned)
+    feedback_index: int = -1     # where among the last launched step's sampled tokens its token is
 
     @property
     def device_len(self) -> int:
         """Tokens that have to be in the cache before the next token can be sampled."""
-        return len(self.input_ids)
+        return len(self.input_ids) + self.pending
 
     @property
     def extend_len(self) -> int:
-        return len(self.input_ids) - self.cached_len
+        return len(self.input_ids) + self.pending - self.cached_len
 
     @property
     def remain_len(self) -> int:
-        return self.max_new_tokens - len(self.generated_ids)
+        """Tokens still to be sampled by steps not yet launched."""
+        return self.max_new_tokens - len(self.generated_ids) - self.pending
 
     @property
     def finished(self) -> bool:
@@ -56,8 +61,8 @@ class GenerationRequest:
 
     def append_token(self, token: int) -> None:
         """src/engine/request_manager.cpp:122-159"""
-        if self.status is not RequestStatus.RUNNING:
-            raise RuntimeError("append_token expects a running request")
+        if self.status is RequestStatus.FINISHED:
+            raise RuntimeError("append_token on a finished request")
         self.input_ids.append(int(token))
         self.generated_ids.append(int(token))
         if self.eos_token_id >= 0 and token == self.eos_token_id:

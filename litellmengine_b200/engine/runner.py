@@ -46,6 +46,9 @@ class ModelRunner:
             dtype=model.dtype, device=self.device,
             extra_state={"sampler": StateNeed((4,), "int32")})
         self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device)
+        # Tokens sampled by the step before, for entries whose last token the host has not read yet
+        # (`StepEntry.feedback`); whoever samples writes them here.
+        self.sampled = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         # CUDA graphs for steps made only of single decoded tokens: one graph per batch size,
         # captured the second time that size is seen.  Only for models whose parts all say
@@ -101,9 +104,12 @@ class ModelRunner:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise ValueError("an entry needs at least one token")
-            for t in e.tokens:
+            known = e.tokens if e.feedback < 0 else e.tokens[:-1]     # the last one may still be on the device
+            for t in known:
                 if not 0 <= int(t) < V:
                     raise ValueError(f"token id {t} is outside the vocabulary [0, {V})")
+            if e.feedback >= self.sampled.numel():
+                raise ValueError(f"feedback index {e.feedback} is outside the {self.sampled.numel()} sampled tokens")
             e.past = self.cache.length(e.slot)
             if e.past + len(e.tokens) > self.plan.max_position:
                 raise ValueError(f"position {e.past + len(e.tokens) - 1} exceeds max_position_embeddings "
@@ -112,7 +118,7 @@ class ModelRunner:
             raise OutOfPages("the step's tokens do not fit the free pages")
         for e in entries:
             self.cache.ensure(e.slot, e.past + len(e.tokens))
-        batch = pack_step(self.buffers, entries, self.cache.drain_updates())
+        batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled)
         counts = self.buffers.dev_view("counts")
         for g, group in enumerate(self.cache.groups):
             n = int(self.buffers.host_view("counts")[8 + g])

@@ -18,6 +18,12 @@ Rules, in this order, every step:
   to the FRONT of the waiting queue to be recomputed from its first token.  This repeats
   until the older request fits; a request alone always fits because `add` refuses requests
   longer than the pool.  All choices depend only on the order of `add` calls.
+
+A step's result may be read one step late: `advance(plan)` books a launched step (lengths move
+on, each sampled token is `pending`), `deliver(plan, tokens)` books its tokens when the host has
+them; `update` is both at once.  Between the two, `schedule` already plans the next step: a
+request whose pending token is its last (by `max_new_tokens`) is left out, one that turns out
+to have ended with its end-of-sequence token has run one token too many, which `deliver` drops.
 """
 from __future__ import annotations
 
@@ -93,10 +99,7 @@ class Scheduler:
     def schedule(self) -> List[ScheduledPortion]:
         budget = self.max_tokens_per_step
         plan: List[ScheduledPortion] = []
-        reserved: List[tuple] = []         # (slot, new_len) already promised pages in this step
-
-        def fits(slot, new_len) -> bool:
-            return self.cache.can_hold(reserved + [(slot, new_len)])
+        need = [0] * len(self.cache.groups)               # pages per group already promised in this step
 
         preempted = False
         i = 0
@@ -104,59 +107,93 @@ class Scheduler:
         queue = [self.running[k] for k in order]          # decoders first, each kind oldest first
         while i < len(queue):
             req = queue[i]
-            if req not in self.running:                   # preempted below
+            if req not in self.running or req.remain_len <= 0:   # preempted below, or only awaiting its last token
                 i += 1
                 continue
             if budget <= 0:
                 break
             n = min(req.extend_len, self.chunk, budget)
-            while not fits(req.slot, req.cached_len + n):
+            while True:
+                got = self.cache.reserve(need, req.slot, req.cached_len + n)
+                if got is not None:
+                    break
                 victim = self._preempt_latest()
                 preempted = True
                 plan = [p for p in plan if p.request is not victim]
-                reserved = [(p.request.slot, p.request.cached_len + p.num_tokens) for p in plan]
                 budget = self.max_tokens_per_step - sum(p.num_tokens for p in plan)
+                need = [0] * len(self.cache.groups)
+                for p in plan:                            # the pool changed: count the promises again
+                    need = self.cache.reserve(need, p.request.slot, p.request.cached_len + p.num_tokens)
                 if victim is req:
                     break
             if req not in self.running:
                 i += 1
                 continue
+            need = got
             plan.append(ScheduledPortion(req, n, n == req.extend_len))
-            reserved.append((req.slot, req.cached_len + n))
             budget -= n
             i += 1
 
         # no admission in a step that had to preempt: the victim would come straight back
         while not preempted and self.waiting and budget > 0 and self.cache.free_slots > 0:
             req = self.waiting[0]
-            n = min(req.extend_len, self.chunk, budget)
-            if not self.cache.can_hold(reserved + [(None, n)]):
+            if req.remain_len <= 0:                       # preempted with its last token on its way
                 break
+            n = min(req.extend_len, self.chunk, budget)
+            got = self.cache.reserve(need, None, n)
+            if got is None:
+                break
+            need = got
             self.waiting.popleft()
             req.slot = self.cache.admit()
             req.status = RequestStatus.RUNNING
             self.running.append(req)
             plan.append(ScheduledPortion(req, n, n == req.extend_len))
-            reserved.append((req.slot, n))
             budget -= n
-        if not plan and self.has_work():
+        if not plan and self.has_work() and not any(r.pending for r in list(self.running) + list(self.waiting)):
             raise OutOfPages("nothing can be scheduled: the cache is too small for the oldest request")
         return plan
 
-    def update(self, plan: List[ScheduledPortion], sampled: List[int]) -> List[GenerationRequest]:
-        """After the step ran: advance cached lengths, append the sampled tokens (one per
-        portion with `samples`, in plan order), free finished requests' pages and slots.
-        Returns the requests that finished."""
-        it = iter(sampled)
-        done = []
+    def advance(self, plan: List[ScheduledPortion]) -> None:
+        """The step of `plan` has been launched: its tokens count as cached, and each portion
+        that samples leaves a pending token (`feedback_index` = its place among the step's
+        sampled tokens, in plan order)."""
+        k = 0
         for p in plan:
             req = p.request
             req.cached_len += p.num_tokens
             if p.samples:
-                req.append_token(next(it))
-                if req.finished:
+                req.pending += 1                          # two for a moment: the step before is read after this
+                req.feedback_index = k
+                k += 1
+
+    def deliver(self, plan: List[ScheduledPortion], sampled: List[int]) -> List[tuple]:
+        """The host has read the tokens of the step of `plan` (one per portion with `samples`, in
+        plan order): append them, free finished requests' pages and slots.  Returns
+        [(request, token)] of the tokens that count; a token sampled for a request that had
+        already finished (end of sequence found one step late, or released) is dropped."""
+        it = iter(sampled)
+        out = []
+        for p in plan:
+            if not p.samples:
+                continue
+            req, token = p.request, next(it)
+            req.pending -= 1
+            if req.finished:
+                continue
+            req.append_token(token)
+            out.append((req, token))
+            if req.finished:
+                if req in self.running:
                     self.running.remove(req)
                     self.cache.release(req.slot)
                     req.slot = -1
-                    done.append(req)
-        return done
+                elif req in self.waiting:                 # preempted while its last token was on its way
+                    self.waiting.remove(req)
+        return out
+
+    def update(self, plan: List[ScheduledPortion], sampled: List[int]) -> List[GenerationRequest]:
+        """After a step ran and its tokens were read: `advance` and `deliver` in one.  Returns the
+        requests that finished."""
+        self.advance(plan)
+        return [r for r, _ in self.deliver(plan, sampled) if r.finished]

@@ -97,7 +97,7 @@ class Model:
     def forward(self, batch, cache) -> torch.Tensor:
         """batch: StepBatch already on the device; cache: CacheManager.  Returns float32
         [batch.num_want, vocab] (an empty tensor when nothing is wanted)."""
-        h = ops.embedding(batch.token_ids, self.embedding, batch.status)
+        h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
         delta = None
         for s, st in enumerate(self.plan.order):
             block = self.blocks[st.block]

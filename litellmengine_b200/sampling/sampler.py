@@ -38,8 +38,9 @@ class Sampler:
         row = torch.tensor(slot_state_row(seed, counter, temperature), dtype=torch.int32)
         self.state[slot].copy_(row, non_blocking=False)
 
-    def sample(self, logits: torch.Tensor, want_slot: torch.Tensor, any_sampling: bool) -> torch.Tensor:
-        """int32 [rows] on the device."""
+    def sample(self, logits: torch.Tensor, want_slot: torch.Tensor, any_sampling: bool,
+               out: torch.Tensor = None) -> torch.Tensor:
+        """int32 [rows] on the device (written into `out` when given)."""
         if not any_sampling:
-            return ops.argmax_rows(logits)
-        return ops.sample_rows(logits, want_slot, self.state)
+            return ops.argmax_rows(logits, out=out)
+        return ops.sample_rows(logits, want_slot, self.state, out=out)

@@ -88,6 +88,37 @@ def test_page_pressure_preempts_and_results_do_not_change():
     tight.runner.cache.check_invariants()
 
 
+def test_pipelined_and_unpipelined_stepping_give_the_same_tokens():
+    """Launching a step before the tokens of the one before are read changes nothing but the
+    timing: greedy and sampling requests, an end-of-sequence token found one step late, so few
+    pages that requests are preempted with a token still on the device."""
+    cfg, w = tm.TINY_A, tm.make_weights(tm.TINY_A, tm.TINY_A_SEED)
+    prompts = [tm.random_tokens(cfg, n, 300 + n) for n in (10, 3, 12, 7, 9)]
+    free = [pq.greedy_generate(p, w, cfg, 14) for p in prompts]
+    eos = free[1][4]
+
+    def run(pipelined, pool):
+        eng = engine_for(cfg, w, "float32", 4, pool=pool, pipelined=pipelined, chunk=5, max_tokens_per_step=12)
+        ids = [eng.add_request(p, 14, eos_token_id=eos if i == 1 else -1, temperature=0.7 if i == 3 else 0.0,
+                               seed=50 + i) for i, p in enumerate(prompts)]
+        steps = 0
+        while eng.has_work():
+            eng.step()
+            steps += 1
+            assert steps < 2000
+        eng.runner.check_status()
+        eng.runner.cache.check_invariants()
+        assert all(g.pool.free_count == g.pool.num_pages for g in eng.runner.cache.groups)
+        return [eng.request(i).generated_ids for i in ids], [eng.request(i).finish_reason for i in ids], eng
+
+    want, why, _ = run(False, 256)
+    assert why[1] == "eos" and want[1] == free[1][:free[1].index(eos) + 1] and want[0] == free[0]
+    for pool in (256, 48):
+        got, why2, eng = run(True, pool)
+        assert got == want and why2 == why
+        assert (eng.scheduler.num_preemptions > 0) == (pool == 48)
+
+
 def test_temperature_sampling_is_reproducible_and_batch_independent():
     """BASELINE config B: 12 sampling steps at temperature 0.8 with a fixed seed."""
     from litellmengine_b200.csrc import ops

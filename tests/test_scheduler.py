@@ -147,3 +147,89 @@ def test_window_group_lets_long_requests_share_few_pages():
     cache, s = make(pages=6, page=4, budget=8, chunk=4, window=None, longest=64)
     with pytest.raises(OutOfPages, match="at most 24"):
         s.add(list(range(1, 30)), 20)         # without a window the pool is the limit
+
+
+# ---- tokens read one step late --------------------------------------------------------------
+def run_pipelined(cache, sched, limit=2000):
+    """The engine's pipelined loop, minus the GPU: a step is launched (`advance`) before the
+    tokens of the step before it are read (`deliver`).  The fake device knows every token, so
+    a portion that ends with a pending token is checked to be exactly the next one."""
+    in_flight, steps = None, 0
+    device_ids = {}                                       # request id -> ids as the device has seen them
+    while sched.has_work() or in_flight:
+        plan = sched.schedule()
+        launched = None
+        if plan:
+            sampled = []
+            for p in plan:
+                r = p.request
+                assert cache.length(r.slot) == r.cached_len
+                cache.ensure(r.slot, r.cached_len + p.num_tokens)
+                cache.commit(r.slot, r.cached_len + p.num_tokens)
+                end = r.cached_len + p.num_tokens
+                assert end <= len(r.input_ids) + r.pending
+                if end > len(r.input_ids):                # the last token comes from the step before
+                    assert r.pending == 1 and in_flight is not None
+                    prev_plan, prev_sampled = in_flight
+                    owners = [q.request for q in prev_plan if q.samples]
+                    assert owners[r.feedback_index] is r
+                if p.samples:                             # the device holds every token sampled so far
+                    ids = device_ids.setdefault(r.request_id, list(r.input_ids[:r.prompt_len]))
+                    assert ids[:len(r.input_ids)] == r.input_ids and len(ids) == end
+                    ids.append(fake_next(ids))
+                    sampled.append(ids[-1])
+            sched.advance(plan)
+            launched = (plan, sampled)
+        if in_flight:
+            sched.deliver(*in_flight)
+        in_flight = launched
+        cache.check_invariants()
+        steps += 1
+        assert steps < limit
+    return steps
+
+
+@pytest.mark.parametrize("pages,budget,chunk", [(64, 16, None), (12, 8, 5), (9, 16, 3)])
+def test_reading_tokens_one_step_late_gives_the_same_tokens(pages, budget, chunk):
+    cache, s = make(pages=pages, budget=budget, chunk=chunk, slots=3)
+    prompts = [[3, 1, 4, 1, 5, 9, 2], [6, 5], [3, 5, 8, 9, 7, 9, 3, 2, 3, 8, 4], [1], [2, 7, 1, 8]]
+    news = [6, 9, 4, 1, 7]
+    reqs = [s.add(p, n) for p, n in zip(prompts, news)]
+    run_pipelined(cache, s)
+    for r, p, n in zip(reqs, prompts, news):
+        assert r.finished and r.generated_ids == expected(p, n) and r.pending == 0, (r.generated_ids, expected(p, n))
+    assert cache.groups[0].pool.free_count == pages and cache.free_slots == 3
+
+
+def test_a_request_awaiting_its_last_token_is_not_scheduled_again():
+    cache, s = make(pages=16)
+    a = s.add([5, 6, 7], 2)
+    plan = s.schedule()
+    s.advance(plan)                                        # prompt launched: first token pending
+    assert a.pending == 1 and a.remain_len == 1 and a.extend_len == 1
+    plan2 = s.schedule()
+    assert [(p.request, p.num_tokens, p.samples) for p in plan2] == [(a, 1, True)]
+    s.advance(plan2)
+    s.deliver(plan, [11])
+    assert a.pending == 1 and a.remain_len == 0           # its second and last token is on its way
+    assert s.schedule() == []                              # nothing to launch, and no OutOfPages either
+    s.deliver(plan2, [12])
+    assert a.finished and a.generated_ids == [11, 12] and not s.has_work()
+
+
+def test_end_of_sequence_found_one_step_late_drops_the_extra_token():
+    cache, s = make(pages=16)
+    a = s.add([5, 6, 7], 10, eos_token_id=42)
+    b = s.add([1, 2], 10)
+    p1 = s.schedule(); s.advance(p1)
+    p2 = s.schedule(); s.advance(p2)                       # both decode on, their first tokens unread
+    got = s.deliver(p1, [42, 9])                           # a's first token was its end of sequence
+    assert [(r.request_id, t) for r, t in got] == [(a.request_id, 42), (b.request_id, 9)]
+    assert a.finished and a.finish_reason == "eos" and a.slot == -1
+    p3 = s.schedule()                                      # a is gone from the plan
+    assert [p.request for p in p3] == [b]
+    s.advance(p3)
+    got = s.deliver(p2, [77, 10])                          # 77 was sampled for a after its end: dropped
+    assert [(r.request_id, t) for r, t in got] == [(b.request_id, 10)]
+    assert a.generated_ids == [42] and b.generated_ids == [9, 10]
+    cache.check_invariants()
