@@ -89,6 +89,143 @@ __global__ void qk_norm_rope_kv_write_kernel(
     for (int i = lane; i < d; i += 32) dst[i] = from_f32<TC>(x[i]);
 }
 
+// ---- head sizes 64 and 128, whole-head rotation: everything in registers -----------------------
+// A lane holds D/32 consecutive elements of a head, so a head is one 8- or 16-byte access per
+// lane, and element i's rotation partner i + D/2 sits in lane + 16 (one shuffle).  A warp takes
+// HPW heads of one token at once: their loads are in flight together, and the token's sines and
+// cosines are computed once for all of them.
+template <int N> __device__ __forceinline__ void rc_load(const float* p, float (&v)[N]) {
+    if constexpr (N == 4) { const float4 a = *reinterpret_cast<const float4*>(p); v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; }
+    else { const float2 a = *reinterpret_cast<const float2*>(p); v[0] = a.x; v[1] = a.y; }
+}
+template <int N> __device__ __forceinline__ void rc_load(const bf16* p, float (&v)[N]) {
+    if constexpr (N == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+        v[0] = a.x; v[1] = a.y;
+    }
+}
+template <int N> __device__ __forceinline__ void rc_store(float* p, const float (&v)[N]) {
+    if constexpr (N == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+}
+template <int N> __device__ __forceinline__ void rc_store(bf16* p, const float (&v)[N]) {
+    if constexpr (N == 4) {
+        uint2 raw;
+        *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = raw;
+    } else {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+}
+
+template <int D, int HPW, typename TI, typename T, typename TC>
+__global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kernel(
+    const TI* __restrict__ qkv, T* __restrict__ q_out, TC* __restrict__ cache,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ inv_freq, int num_tokens, int nq, int nkv, int page_size, int has_kv,
+    int num_pages, int32_t* __restrict__ status, int qkv_parts, long long qkv_part_stride) {
+    pdl_begin();
+    constexpr int N = D / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+    const int groups = (heads_total + HPW - 1) / HPW;
+    const long long item = static_cast<long long>(blockIdx.x) * RC_WARPS + warp;
+    if (item >= static_cast<long long>(num_tokens) * groups) return;
+    const int t = static_cast<int>(item / groups);
+    const int head0 = static_cast<int>(item - static_cast<long long>(t) * groups) * HPW;
+    const int e0 = lane * N;                                             // this lane's first element of a head
+    const TI* src = qkv + static_cast<size_t>(t) * heads_total * D + e0;
+
+    float x[HPW][N];
+#pragma unroll
+    for (int j = 0; j < HPW; ++j) {
+        if (head0 + j < heads_total) {
+            rc_load<N>(src + static_cast<size_t>(head0 + j) * D, x[j]);
+            for (int part = 1; part < qkv_parts; ++part) {                // k-splits of the product
+                float y[N];
+                rc_load<N>(src + part * qkv_part_stride + static_cast<size_t>(head0 + j) * D, y);
+#pragma unroll
+                for (int i = 0; i < N; ++i) x[j][i] += y[i];
+            }
+        }
+    }
+    const int pos = positions[t];
+    float sn[N], cs[N];
+    if (inv_freq) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) sincosf(static_cast<float>(pos) * inv_freq[(e0 + i) & (D / 2 - 1)], &sn[i], &cs[i]);
+    }
+    int page = -2;                                                        // looked up at the first key or value head
+#pragma unroll
+    for (int j = 0; j < HPW; ++j) {
+        const int head = head0 + j;
+        if (head >= heads_total) break;
+        const bool is_q = head < nq;
+        const bool is_k = !is_q && head < nq + nkv;
+        const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+        if (nw) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < N; ++i) ss += x[j][i] * x[j][i];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+            float w[N];
+            rc_load<N>(nw + e0, w);
+#pragma unroll
+            for (int i = 0; i < N; ++i) x[j][i] = x[j][i] * inv * w[i];
+        }
+        if ((is_q || is_k) && inv_freq) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[j][i], 16);
+                // first half: x1 cos - x2 sin; second half: x2 cos + x1 sin
+                x[j][i] = lane < 16 ? x[j][i] * cs[i] - other * sn[i] : x[j][i] * cs[i] + other * sn[i];
+            }
+        }
+        if (is_q) {
+            rc_store<N>(q_out + static_cast<size_t>(t) * nq * D + static_cast<size_t>(head) * D + e0, x[j]);
+            continue;
+        }
+        if (page == -2) {
+            const int slot = entry_slot[token_entry[t]];
+            const int logical = pos / page_size;
+            page = (pos >= 0 && logical < table_stride) ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
+                page = -1;
+            }
+        }
+        if (page < 0) continue;
+        const int kv_head = is_k ? head - nq : head - nq - nkv;
+        TC* dst = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * nkv + kv_head) * page_size * D +
+                  static_cast<size_t>(pos % page_size) * D + e0;
+        rc_store<N>(dst, x[j]);
+    }
+}
+
+template <int D, int HPW, typename TI, typename T, typename TC>
+static void launch_rope_vec(const void* qkv, void* q_out, void* cache, const int32_t* positions,
+                            const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
+                            int table_stride, const float* q_norm_w, const float* k_norm_w, float eps,
+                            const float* inv_freq, int num_tokens, int nq, int nkv, int page_size, int has_kv,
+                            int num_pages, int32_t* status, int qkv_parts, long long qkv_part_stride, cudaStream_t s) {
+    const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+    const long long items = static_cast<long long>(num_tokens) * ((heads_total + HPW - 1) / HPW);
+    const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
+    launch_pdl((qk_norm_rope_kv_write_vec_kernel<D, HPW, TI, T, TC>), dim3(blocks), dim3(RC_WARPS * 32), 0, s,
+               static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions, token_entry,
+               entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv,
+               page_size, has_kv, num_pages, status, qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride);
+}
+
 // qkv: [T, heads_total * d] (qkv_dtype); q_out: [T, nq * d] (q_dtype); cache (cache_dtype).
 extern "C" int llm_qk_norm_rope_kv_write(
     const void* qkv, int qkv_dtype, void* q_out, int q_dtype, void* cache, int cache_dtype,
@@ -114,6 +251,21 @@ extern "C" int llm_qk_norm_rope_kv_write(
         rotary_dim, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status,                    \
         qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride)
     const int key = qkv_dtype * 4 + q_dtype * 2 + cache_dtype;
+    // the register kernel: head size 64 or 128 rotated whole, 16-byte aligned rows, float32 projection
+    const bool whole = inv_freq == nullptr || rotary_dim == d;
+    if ((d == 64 || d == 128) && whole && (key == 0 || key == 3) && aligned16(qkv) && aligned16(q_out) &&
+        aligned16(cache) && (qkv_part_stride % 4) == 0 && aligned16(q_norm_w) && aligned16(k_norm_w)) {
+#define VEC(D, HPW)                                                                                           \
+    do {                                                                                                      \
+        if (key == 0) launch_rope_vec<D, HPW, float, float, float>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, s); \
+        else launch_rope_vec<D, HPW, float, bf16, bf16>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, s); \
+    } while (0)
+        const bool many = num_tokens >= 64;                              // few tokens: one head per warp keeps more warps busy
+        if (d == 128) { if (many) VEC(128, 4); else VEC(128, 1); }
+        else { if (many) VEC(64, 4); else VEC(64, 1); }
+#undef VEC
+        return launch_status();
+    }
     if (key == 0) LAUNCH(float, float, float);
     else if (key == 3) LAUNCH(float, bf16, bf16);
     else if (key == 7) LAUNCH(bf16, bf16, bf16);

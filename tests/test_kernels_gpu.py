@@ -109,20 +109,24 @@ def build_cache(k, v, page, table, num_pages, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 4, 16, 4, 16), (6, 2, 48, 16, 48), (8, 1, 128, 8, 64),
-                                               (3, 3, 256, 32, 256), (2, 1, 80, 16, 40)])
-def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, rot):
+@pytest.mark.parametrize("nq,nkv,d,page,rot,T", [(4, 4, 16, 4, 16, 29), (6, 2, 48, 16, 48, 29), (8, 1, 128, 8, 64, 29),
+                                                 (3, 3, 256, 32, 256, 29), (2, 1, 80, 16, 40, 29),
+                                                 # head sizes 64 and 128 rotated whole: the register kernel, with
+                                                 # one head per warp (few tokens) and four (11 heads: a ragged group)
+                                                 (5, 3, 128, 16, 128, 29), (5, 3, 128, 16, 128, 93),
+                                                 (7, 2, 64, 8, 64, 29), (7, 2, 64, 8, 64, 93)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, rot, T):
     torch.manual_seed(3)
-    T, theta, eps = 29, 50000.0, 1e-5
+    theta, eps = 50000.0, 1e-5
     heads = nq + 2 * nkv
     qkv = torch.randn(T, heads * d)
     qw, kw = 1 + 0.2 * torch.randn(d), 1 + 0.2 * torch.randn(d)
     # two requests: slot 2 holds positions 5.., slot 0 holds positions 40..
-    lens = [17, 12]
-    pos = torch.cat([torch.arange(5, 5 + 17), torch.arange(40, 40 + 12)]).to(torch.int32)
-    entry = torch.cat([torch.zeros(17), torch.ones(12)]).to(torch.int32)
+    first = T - 12
+    pos = torch.cat([torch.arange(5, 5 + first), torch.arange(40, 40 + 12)]).to(torch.int32)
+    entry = torch.cat([torch.zeros(first), torch.ones(12)]).to(torch.int32)
     slots = torch.tensor([2, 0], dtype=torch.int32)
-    width = (52 + page - 1) // page + 1
+    width = (max(52, 5 + first) + page - 1) // page + 1
     num_pages = 2 * width + 5
     table = torch.full((3, width), -1, dtype=torch.int32)
     perm = torch.randperm(num_pages)[:2 * width].to(torch.int32)
