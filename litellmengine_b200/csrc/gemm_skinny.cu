@@ -4,11 +4,11 @@
 // bytes of w each SM keeps in flight and whether every SM is busy until the end.  The library's
 // kernels for these shapes reach 40-60 % of the memory bandwidth when N is small (N = 4096 or 6144
 // gives fewer thread blocks than the GPU has SMs).  Here the work is cut into items of 64 output
-// features (one 16-row tensor-core tile per warp) by 128 k-values, numbered feature tile by
-// feature tile, and the grid is persistent: two CTAs per SM, each taking one contiguous run of
-// items of (nearly) the same length, whatever N and K are.  A CTA streams its items through six
-// (five for 16 tokens) shared-memory stages with cp.async (16 KB of w and up to 4 KB of x per
-// stage) without draining the pipeline between feature tiles.  A feature tile whose items lie in
+// features (one 16-row tensor-core tile per warp) by 256 k-values (128 for 16 tokens), numbered
+// feature tile by feature tile, and the grid is persistent: two CTAs per SM, each taking one
+// contiguous run of items of (nearly) the same length, whatever N and K are.  A CTA streams its
+// items through three stages of shared memory (five for 16 tokens) with cp.async (32 KB of w and
+// 4 KB of x per stage) without draining the pipeline between feature tiles.  A feature tile whose items lie in
 // several CTAs gets one float32 partial sum from each, in a slice numbered by the CTA's place
 // among them (the CTA that finishes the tile zeroes the slices nobody uses); a second small
 // kernel, or the consumer, adds the slices in order (no atomics: the result does not depend on
@@ -20,8 +20,11 @@
 #include "common.cuh"
 
 #define GS_ROWS 64          // output features per CTA (16 per warp)
-#define GS_BK 128           // k-values per stage
-#define GS_STAGES_FOR(MT) ((MT) <= 8 ? 6 : 5)   // two CTAs per SM must fit: (64 + MT) rows * 256 B per stage
+// k-values per stage and stages, by token tile: two CTAs per SM must fit.  Up to 8 tokens: three
+// stages of 256 k-values (512 contiguous bytes of each weight row per request, which the memory
+// system serves better than 256: 6.2 against 5.9 TB/s on the output head); 16 tokens: five of 128.
+#define GS_BK_FOR(MT) ((MT) <= 8 ? 256 : 128)
+#define GS_STAGES_FOR(MT) ((MT) <= 8 ? 3 : 5)
 #define GS_THREADS 128
 
 __device__ __forceinline__ void gs_cp_async16(void* smem, const void* gmem, bool valid) {
@@ -41,9 +44,9 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], un
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// 16-byte chunk `chunk` of row `row` in a [rows][GS_BK] bfloat16 stage, XOR-swizzled.
-__device__ __forceinline__ bf16* gs_at(bf16* base, int row, int chunk) {
-    return base + row * GS_BK + ((chunk ^ (row & 7)) << 3);
+// 16-byte chunk `chunk` of row `row` in a [rows][BK] bfloat16 stage, XOR-swizzled.
+template <int BK> __device__ __forceinline__ bf16* gs_at(bf16* base, int row, int chunk) {
+    return base + row * BK + ((chunk ^ (row & 7)) << 3);
 }
 
 // Which CTA of `ctas` holds item `item` when CTA c takes items [c*total/ctas, (c+1)*total/ctas).
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
                                                                    const bf16* __restrict__ w, TO* __restrict__ y,
                                                                    float* __restrict__ partial, int M, int N, int K,
                                                                    int slices, int per_tile) {
-    constexpr int GS_STAGES = GS_STAGES_FOR(MT);
+    constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT);
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK]
     bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
         for (int j = 0; j < GS_ROWS * CPR / GS_THREADS; ++j) {
             const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
             const bool valid = (n0 + row < N) && (k0 + ch * 8 < K);
-            gs_cp_async16(gs_at(ws, row, ch), w + (valid ? static_cast<size_t>(n0 + row) * K + k0 + ch * 8 : 0), valid);
+            gs_cp_async16(gs_at<GS_BK>(ws, row, ch), w + (valid ? static_cast<size_t>(n0 + row) * K + k0 + ch * 8 : 0), valid);
         }
     };
     auto load_x = [&](int i) {                                           // the tokens' rows for the same k-values
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
         for (int j = 0; j < MT * CPR / GS_THREADS; ++j) {
             const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
             const bool valid = (row < M) && (k0 + ch * 8 < K);
-            gs_cp_async16(gs_at(xs, row, ch), x + (valid ? static_cast<size_t>(row) * K + k0 + ch * 8 : 0), valid);
+            gs_cp_async16(gs_at<GS_BK>(xs, row, ch), x + (valid ? static_cast<size_t>(row) * K + k0 + ch * 8 : 0), valid);
         }
     };
 
@@ -130,12 +133,12 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
 #pragma unroll
         for (int kp = 0; kp < GS_BK / 32; ++kp) {                        // pairs of k-steps
             unsigned a0[4], a1[4];
-            gs_ldmatrix_x4(a0, gs_at(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
-            gs_ldmatrix_x4(a1, gs_at(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
+            gs_ldmatrix_x4(a0, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
+            gs_ldmatrix_x4(a1, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
 #pragma unroll
             for (int j = 0; j < MT / 8; ++j) {
                 unsigned b[4];                                           // tokens 8j..8j+7, two k-steps
-                gs_ldmatrix_x4(b, gs_at(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
+                gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
                 gs_mma(acc[j], a0, b[0], b[1]);
                 gs_mma(acc[j], a1, b[2], b[3]);
             }
@@ -200,8 +203,8 @@ static bool skinny_device() {
 // CTAs per feature tile fill at least 85 % of the GPU's CTA slots, each tile's k-values are shared
 // evenly by `per_tile` CTAs (fewest slices); otherwise (more tiles than slots, or a poor fit) the
 // items are cut into one even run per slot (per_tile = 0).
-static void skinny_plan(int N, int K, int* ctas, int* slices, int* per_tile) {
-    const long long tiles = (N + GS_ROWS - 1) / GS_ROWS, nk = (K + GS_BK - 1) / GS_BK, total = tiles * nk;
+static void skinny_plan(int N, int K, int bk, int* ctas, int* slices, int* per_tile) {
+    const long long tiles = (N + GS_ROWS - 1) / GS_ROWS, nk = (K + bk - 1) / bk, total = tiles * nk;
     long long best = 0;
     for (long long s = 1; s <= 16 && s <= (nk >= 4 ? nk / 4 : 1); ++s)   // at least four items per CTA
         if (tiles * s <= g_skinny_slots) best = s;
@@ -230,16 +233,15 @@ static void skinny_plan(int N, int K, int* ctas, int* slices, int* per_tile) {
 extern "C" long long llm_linear_skinny_scratch_floats(int M, int N, int K) {
     if (!skinny_device()) return 0;
     int ctas, slices, per_tile;
-    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    skinny_plan(N, K, GS_BK_FOR(M <= 8 ? 8 : 16), &ctas, &slices, &per_tile);
     return slices > 1 ? static_cast<long long>(slices) * M * N : 0;
 }
 
 // The number of partial-sum slices a product of these sizes leaves on the current device.
 extern "C" int llm_linear_skinny_splits(int M, int N, int K) {
     if (!skinny_device()) return 1;
-    (void)M;
     int ctas, slices, per_tile;
-    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    skinny_plan(N, K, GS_BK_FOR(M <= 8 ? 8 : 16), &ctas, &slices, &per_tile);
     return slices;
 }
 
@@ -247,12 +249,12 @@ template <int MT, typename TO>
 static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, long long scratch_floats, int M, int N,
                          int K, int keep_partials, cudaStream_t s) {
     if (!skinny_device()) return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK * sizeof(bf16);
+    const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK_FOR(MT) * sizeof(bf16);
     auto kern = linear_skinny_kernel<MT, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     int ctas, slices, per_tile;
-    skinny_plan(N, K, &ctas, &slices, &per_tile);
+    skinny_plan(N, K, GS_BK_FOR(MT), &ctas, &slices, &per_tile);
     if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * M * N))
         return LLM_REFUSED_SIZE;                                         // the caller sizes scratch with llm_linear_skinny_scratch_floats
     launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile);
