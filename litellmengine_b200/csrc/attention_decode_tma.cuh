@@ -71,7 +71,10 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
     int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
-    pdl_begin();
+    // The wait for the kernel before this one (which writes q and this step's key and value row)
+    // comes late: keys and values of earlier steps, the block table and the step's metadata are
+    // read first, so the first tiles are already on their way when q arrives.
+    pdl_invite();
     constexpr int CH = D / 8, KB = D / 16;
     constexpr int TILE = AD_BN * D;                                  // elements of one K (or V) tile
     extern __shared__ unsigned char smem_dyn[];
@@ -107,19 +110,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (n_tiles > 0 && tid < 16 * 2) {                               // the group's query heads, zero rows after them
-        const int row = tid >> 1, half = tid & 1;
-        const bool valid = row < G;
-        const bf16* src = q + (static_cast<size_t>(t) * nq + h0 + (valid ? row : 0)) * D;
-#pragma unroll
-        for (int i = 0; i < CH / 2; ++i) {
-            const int c = 2 * i + half;
-            cp_async16(tile_at<D>(q_s, row, c), src + c * 8, valid);
-        }
-    }
-    cp_async_commit();
-    cp_async_wait_all();
-    __syncthreads();
+    __syncthreads();                                                 // the barriers exist
 
     if (warp == 4) {
         // ---- producer: one lane feeds the copy engine ----
@@ -128,8 +119,13 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
             const int last_logical = (k_end - 1) / page_size;
             const unsigned tile_bytes = 2u * TILE * sizeof(bf16);
             int issued = 0;
+            bool waited = false;
             for (int it = 0; it < n_tiles; ++it) {
                 const int st = it % STAGES;
+                if (!waited && (it >= STAGES || k_origin + (it + 1) * AD_BN > pos)) {
+                    pdl_wait();                                       // the tile with this step's own row, or a stage to be reused
+                    waited = true;
+                }
                 if (it >= STAGES && !mbar_wait(&empty_bar[st], ((it / STAGES) - 1) & 1, &abort_flag, status, t)) break;
                 mbar_expect_tx(&full_bar[st], tile_bytes);
                 const int first_logical = (k_origin + it * AD_BN) / page_size;
@@ -161,6 +157,20 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     }
 
     // ---- consumers: warps 0..3, 16 keys of every tile each ----
+    pdl_wait();
+    if (n_tiles > 0 && tid < 16 * 2) {                               // the group's query heads, zero rows after them
+        const int row = tid >> 1, half = tid & 1;
+        const bool valid = row < G;
+        const bf16* src = q + (static_cast<size_t>(t) * nq + h0 + (valid ? row : 0)) * D;
+#pragma unroll
+        for (int i = 0; i < CH / 2; ++i) {
+            const int c = 2 * i + half;
+            cp_async16(tile_at<D>(q_s, row, c), src + c * 8, valid);
+        }
+    }
+    cp_async_commit();
+    cp_async_wait_all();
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // the four consumer warps
     unsigned qf[KB][4];
 #pragma unroll
     for (int kb = 0; kb < KB; ++kb)

@@ -96,6 +96,10 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 // not depend on its predecessor (the streaming product fetches weights) does that work between
 // the two halves.  Big grids do not invite their successor early: its blocks would only take
 // room from blocks of this grid that have not started yet.
+// What a kernel may read BEFORE its wait: weights, the step's metadata (copied to the device
+// before the step's first kernel) and the block tables (their scatter kernel invites nobody
+// early), keys and values of earlier steps.  Never anything a kernel of this step writes: a
+// chain of early invitations can keep several of them in flight at once.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_invite() {

@@ -61,7 +61,10 @@ __global__ void scatter_int32_kernel(int32_t* __restrict__ dst, long long dst_le
                                      const int32_t* __restrict__ index, const int32_t* __restrict__ value,
                                      const int32_t* __restrict__ count, int max_count,
                                      int32_t* __restrict__ status) {
-    pdl_begin();
+    // No early invitation here: kernels later in the step read the tables before their own
+    // griddepcontrol.wait (they only wait for the kernel just before them), which is safe
+    // because nothing after this kernel starts until it has finished.
+    pdl_wait();
     const int n = min(*count, max_count);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const long long at = index[i];

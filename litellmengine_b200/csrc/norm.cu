@@ -15,6 +15,10 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
                                const float* __restrict__ w, TO* __restrict__ out,
                                const int32_t* __restrict__ rows, int hidden, float eps,
                                int write_sum, int vec, int delta_parts, long long delta_part_stride) {
+    // The norm weights are read before the wait for the kernel that produces x / delta.
+    float g0[8];
+    const bool one_trip = vec && hidden <= static_cast<int>(blockDim.x) * 8;
+    if (one_trip && static_cast<int>(threadIdx.x) * 8 < hidden) load8(w + threadIdx.x * 8, g0);
     pdl_begin();
     extern __shared__ __align__(16) float smem[];   // hidden floats (padded to 8) + 33 for the reduction
     float* v = smem;
@@ -53,7 +57,16 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TD* __restrict__ delta,
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
-    if (vec) {
+    if (one_trip) {
+        const int h = threadIdx.x * 8;
+        if (h < hidden) {
+            float a[8];
+            load8(v + h, a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = a[i] * inv * g0[i];
+            store8(orow + h, a);
+        }
+    } else if (vec) {
         for (int h = threadIdx.x * 8; h < hidden; h += blockDim.x * 8) {
             float a[8], g[8];
             load8(v + h, a);

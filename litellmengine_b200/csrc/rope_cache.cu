@@ -132,7 +132,6 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int num_tokens, int nq, int nkv, int page_size, int has_kv,
     int num_pages, int32_t* __restrict__ status, int qkv_parts, long long qkv_part_stride) {
-    pdl_begin();
     constexpr int N = D / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
@@ -143,6 +142,30 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
     const int head0 = static_cast<int>(item - static_cast<long long>(t) * groups) * HPW;
     const int e0 = lane * N;                                             // this lane's first element of a head
     const TI* src = qkv + static_cast<size_t>(t) * heads_total * D + e0;
+
+    // Before the wait for the projection: everything that comes from the step's metadata, the
+    // block table and the weights (position, sines and cosines, norm weights, the page).
+    const int pos = positions[t];
+    float sn[N], cs[N], wq[N], wk[N];
+    if (inv_freq) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) sincosf(static_cast<float>(pos) * inv_freq[(e0 + i) & (D / 2 - 1)], &sn[i], &cs[i]);
+    }
+    if (q_norm_w) rc_load<N>(q_norm_w + e0, wq);
+    if (k_norm_w) rc_load<N>(k_norm_w + e0, wk);
+    int page = -1;
+    bool bad_page = false;
+    if (head0 + HPW > nq && has_kv) {                                     // this warp holds a key or value head
+        const int slot = entry_slot[token_entry[t]];
+        const int logical = pos / page_size;
+        page = (pos >= 0 && logical < table_stride) ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
+        bad_page = page < 0 || page >= num_pages;
+    }
+    pdl_begin();
+    if (bad_page) {
+        if (lane == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
+        page = -1;
+    }
 
     float x[HPW][N];
 #pragma unroll
@@ -157,13 +180,6 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
             }
         }
     }
-    const int pos = positions[t];
-    float sn[N], cs[N];
-    if (inv_freq) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) sincosf(static_cast<float>(pos) * inv_freq[(e0 + i) & (D / 2 - 1)], &sn[i], &cs[i]);
-    }
-    int page = -2;                                                        // looked up at the first key or value head
 #pragma unroll
     for (int j = 0; j < HPW; ++j) {
         const int head = head0 + j;
@@ -177,10 +193,8 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
             for (int i = 0; i < N; ++i) ss += x[j][i] * x[j][i];
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
-            float w[N];
-            rc_load<N>(nw + e0, w);
 #pragma unroll
-            for (int i = 0; i < N; ++i) x[j][i] = x[j][i] * inv * w[i];
+            for (int i = 0; i < N; ++i) x[j][i] = x[j][i] * inv * (is_q ? wq[i] : wk[i]);
         }
         if ((is_q || is_k) && inv_freq) {
 #pragma unroll
@@ -193,15 +207,6 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
         if (is_q) {
             rc_store<N>(q_out + static_cast<size_t>(t) * nq * D + static_cast<size_t>(head) * D + e0, x[j]);
             continue;
-        }
-        if (page == -2) {
-            const int slot = entry_slot[token_entry[t]];
-            const int logical = pos / page_size;
-            page = (pos >= 0 && logical < table_stride) ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
-            if (page < 0 || page >= num_pages) {
-                if (lane == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
-                page = -1;
-            }
         }
         if (page < 0) continue;
         const int kv_head = is_k ? head - nq : head - nq - nkv;
