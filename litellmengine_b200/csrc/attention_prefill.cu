@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     bf16* k_s = q_s + AP_BM * D;                                      // [2][64][D]
     bf16* v_s = k_s + 2 * AP_BN * D;                                  // [2][64][D]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    const int tile = blockIdx.y, h = blockIdx.x;      // heads vary fastest: the tile list's expensive tiles start first
     const int kvh = h / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
@@ -278,7 +278,7 @@ extern "C" int llm_paged_attention_prefill(
     if (!aligned16(q) || !aligned16(out) || !aligned16(cache)) return LLM_REFUSED_ALIGN;
     const size_t smem = static_cast<size_t>(AP_BM + 4 * AP_BN) * d * sizeof(bf16);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    dim3 grid(n_tiles, nq);
+    dim3 grid(nq, n_tiles);
     const float scale_log2e = scale * 1.4426950408889634f;
 #define LAUNCH(DD)                                                                                             \
     {                                                                                                          \

@@ -54,6 +54,26 @@ __device__ __forceinline__ bool t5_try_wait(unsigned long long* bar, unsigned pa
                  : "=r"(ok) : "r"(t5_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Built with -DT5_TRACE, CTA 0 records (event, tile, SM clock) triples of its issuing thread
+// and of its first softmax thread; llm_t5_trace_read copies them out.  A debugging aid only.
+#ifdef T5_TRACE
+#define T5_TRACE_LEN 8192
+__device__ long long g_t5_trace[2][T5_TRACE_LEN];
+#define T5_EVENT(role, n, code, u)                                                      \
+    do {                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (n) + 2 < T5_TRACE_LEN) {                                \
+            g_t5_trace[role][(n)++] = (static_cast<long long>(code) << 32) | (u);       \
+            g_t5_trace[role][(n)++] = clock64();                                        \
+        }                                                                               \
+    } while (0)
+extern "C" int llm_t5_trace_read(long long* host, int role) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_t5_trace, sizeof(long long) * T5_TRACE_LEN,
+                                                 sizeof(long long) * T5_TRACE_LEN * role));
+}
+#else
+#define T5_EVENT(role, n, code, u) do { } while (0)
+#endif
+
 __device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                         int32_t* status, int where) {
     for (int i = 0; i < T5_WAIT_LIMIT; ++i) {
@@ -156,8 +176,10 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
 
-    const int tile = blockIdx.x;
-    const int h0 = blockIdx.y * HEADS;                            // first query head of this CTA
+    // Heads vary fastest: CTAs are handed to SMs in this order, and the tile list has the most
+    // expensive tiles first, so those start first whatever the number of heads.
+    const int tile = blockIdx.y;
+    const int h0 = blockIdx.x * HEADS;                            // first query head of this CTA
     const int kvh = h0 / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
@@ -242,9 +264,18 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
             constexpr unsigned IDESC_QK = t5_idesc(T5_BM, T5_BN, 0);
             constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
+            int tn = 0; (void)tn;
+            // Descriptors are built once: a tile further on in shared memory is the same descriptor
+            // plus its byte offset / 16 in the address field (one thread issues every product, so
+            // what it computes per instruction is what limits the rate of issue).
+            const unsigned long long qd0 = t5_desc(q_s, 16, 1024), kd0 = t5_desc(k_s, 16, 1024);
+            const unsigned long long vd0 = t5_desc(v_s, T5_HALF * sizeof(bf16), 1024);
+            constexpr unsigned long long STAGE_STEP = (T5_TILE * sizeof(bf16)) >> 4;
             auto issue_qk = [&](int u) -> bool {
                 const int st = u % STAGES, sb = u & 1;
+                T5_EVENT(0, tn, 1, u);
                 if (!t5_wait(&kv_full[st], (u / STAGES) & 1, &abort_flag, status, row_base)) return false;
+                T5_EVENT(0, tn, 2, u);
                 if (u >= 2) {                                     // the buffer's previous tile must be done with it
                     const int prev = u - 2;
                     const bool a = prev < n_tiles;
@@ -253,16 +284,18 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                         return false;
                 }
                 t5_fence_after();
+                T5_EVENT(0, tn, 3, u);
 #pragma unroll
                 for (int g = 0; g < HEADS; ++g)
 #pragma unroll
                     for (int k = 0; k < T5_D / 16; ++k) {
-                        const bf16* qa = q_s + g * 2 * T5_QHALF + (k >> 2) * T5_QHALF + (k & 3) * 16;
-                        const bf16* kb = k_s + st * T5_TILE + (k >> 2) * T5_HALF + (k & 3) * 16;
-                        t5_mma_ss(tmem + s_col(g, sb), t5_desc(qa, 16, 1024), t5_desc(kb, 16, 1024), IDESC_QK, k > 0);
+                        const unsigned long long qoff = ((g * 2 + (k >> 2)) * T5_QHALF + (k & 3) * 16) * sizeof(bf16) >> 4;
+                        const unsigned long long koff = ((k >> 2) * T5_HALF + (k & 3) * 16) * sizeof(bf16) >> 4;
+                        t5_mma_ss(tmem + s_col(g, sb), qd0 + qoff, kd0 + st * STAGE_STEP + koff, IDESC_QK, k > 0);
                     }
                 t5_commit(&s_full[sb]);
                 if (u < n_tiles) t5_commit(&kv_empty[st]);        // pass A: the keys are all this stage held
+                T5_EVENT(0, tn, 4, u);
                 return true;
             };
             if (ok && total > 0) ok = issue_qk(0);
@@ -270,19 +303,22 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                 if (u + 1 < total) ok = issue_qk(u + 1);          // the next S while this tile's softmax runs
                 if (!ok || u < n_tiles) continue;
                 const int st = u % STAGES, sb = u & 1, v = u - n_tiles;
+                T5_EVENT(0, tn, 5, u);
                 if (!t5_wait(&p_full[sb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
                 t5_fence_after();
+                T5_EVENT(0, tn, 6, u);
 #pragma unroll
                 for (int g = 0; g < HEADS; ++g)
 #pragma unroll
                     for (int k = 0; k < T5_BN / 16; ++k) {
-                        const bf16* vb = v_s + st * T5_TILE + k * 16 * 64;      // 16 keys further, both 64-column halves
-                        t5_mma_ts(tmem + o_col(g), tmem + s_col(g, sb) + k * 8, t5_desc(vb, T5_HALF * sizeof(bf16), 1024),
+                        const unsigned long long voff = (k * 16 * 64) * sizeof(bf16) >> 4;   // 16 keys further, both 64-column halves
+                        t5_mma_ts(tmem + o_col(g), tmem + s_col(g, sb) + k * 8, vd0 + st * STAGE_STEP + voff,
                                   IDESC_PV, (v > 0 || k > 0) ? 1u : 0u);
                     }
                 t5_commit(&kv_empty[st]);
                 t5_commit(&s_used[sb]);
                 if (u == total - 1) t5_commit(&o_done);
+                T5_EVENT(0, tn, 7, u);
             }
         }
     } else {
@@ -296,15 +332,20 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
+        int tn = 0; (void)tn;
+        const bool tracer = (warp == 2 && lane == 0); (void)tracer;
         for (int u = 0; ok && u < n_tiles; ++u) {                 // pass A: maxima
             const int sb = u & 1, kt = k_lo + u * T5_BN;
+            if (tracer) T5_EVENT(1, tn, 11, u);
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
+            if (tracer) T5_EVENT(1, tn, 12, u);
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned r[2][32];                                    // both halves of the row are requested at once
             t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
             t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
             t5_wait_ld();
+            if (tracer) T5_EVENT(1, tn, 13, u);
             t5_fence_before();
             t5_arrive(&s_read[sb]);                               // S is in registers: the buffer may be overwritten
 #pragma unroll
@@ -324,13 +365,16 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
         const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
         for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
             const int sb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
+            if (tracer) T5_EVENT(1, tn, 21, u);
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
+            if (tracer) T5_EVENT(1, tn, 22, u);
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned pk[32], r[2][32];
             t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
             t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
             t5_wait_ld();
+            if (tracer) T5_EVENT(1, tn, 23, u);
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 if (full_tile) {
@@ -358,9 +402,11 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { a[i] = pk[i]; b[i] = pk[16 + i]; }
                 t5_st16(tmem + lane_addr + s_col(g, sb), a);
+                if (tracer) T5_EVENT(1, tn, 24, u);
                 t5_st16(tmem + lane_addr + s_col(g, sb) + 16, b);
             }
             t5_wait_st();
+            if (tracer) T5_EVENT(1, tn, 25, u);
             t5_fence_before();
             t5_arrive(&p_full[sb]);
         }
@@ -438,7 +484,8 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
     const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
     int num_pages, int32_t* status, uintptr_t stream) {
     if (n_tiles <= 0) return LLM_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !llm_paged_prefill_tcgen05_supported(d, page_size) || nq > 65535)
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !llm_paged_prefill_tcgen05_supported(d, page_size) || nq > 65535 ||
+        n_tiles > 65535)
         return LLM_REFUSED_SIZE;
     if (!aligned16(q) || !aligned16(out) || !aligned16(cache)) return LLM_REFUSED_ALIGN;
     CUtensorMap q_map, kv_map;
@@ -455,7 +502,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
                                                    static_cast<int>(smem));                                          \
         if (e != cudaSuccess) return static_cast<int>(e);                                                            \
-        launch_pdl(kern, dim3(n_tiles, nq / HEADS), dim3(64 + 128 * HEADS), smem, s, q_map, kv_map,                  \
+        launch_pdl(kern, dim3(nq / HEADS, n_tiles), dim3(64 + 128 * HEADS), smem, s, q_map, kv_map,                  \
                    static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,             \
                    block_table, table_stride, nq, nkv, page_size, window, sl2, num_pages, status);                   \
     }
