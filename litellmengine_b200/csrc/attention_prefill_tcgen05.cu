@@ -441,6 +441,296 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
     }
 }
 
+// ---- one pass with a running reference maximum, two heads in turns -------------------------------
+// The same work in ONE pass over the keys, for the two query heads of a group that share a key/value
+// tile: 128 keys a tile, S = Q K^T for head 0 while the softmax threads of head 1 work and the
+// other way round, so the tensor pipe always has a product of one head to run while the other
+// head's weights are being made.  Per head TMEM holds S (128 columns of float32, the bfloat16 P
+// over its first 64) and O (128 columns).
+// The weights are P = exp2(S*scale*log2e - m) with a reference m per row that trails the running
+// maximum: m moves up only when the maximum has passed it by more than 8 (a factor 256, far
+// inside what bfloat16 and the float32 sums hold), and only then O and the row sum l are
+// multiplied by exp2(m_old - m_new) (the running-maximum form of src/ops/attention.cu:204-249 with
+// the correction made rare).  The result sum(P V) / sum(P) does not depend on which m was used.
+#define T5O_BN 128
+#define T5O_HALF (T5O_BN * 64)                // elements of one 64-column half of a 128-key tile
+#define T5O_TILE (2 * T5O_HALF)
+#define T5O_STAGES 2
+#define T5O_JUMP 8.0f
+
+__device__ __forceinline__ void t5_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::
+            "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+
+__global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online_kernel(
+    const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
+    const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
+    const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
+    const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
+    float scale_log2e, int num_pages, int32_t* __restrict__ status) {
+    pdl_begin();
+    constexpr int STAGES = T5O_STAGES;
+    constexpr unsigned TMEM_COLS = 512;                           // S0 S1 O0 O1, 128 columns each
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [2 heads][2 halves][128][64]
+    bf16* k_s = q_s + 2 * 2 * T5_QHALF;                           // [STAGES][2][128][64]
+    bf16* v_s = k_s + STAGES * T5O_TILE;                          // [STAGES][2][128][64]
+    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], pv_done[2];
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_flag;
+
+    const int tile = blockIdx.y;
+    const int h0 = blockIdx.x * 2;                                // first of this CTA's two query heads
+    const int kvh = h0 / (nq / nkv);
+    const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
+    const int past = kv_len - q_len;
+    const int row_base = entry_q_start[e] + q0;
+    const int rows_here = min(T5_BM, q_len - q0);
+    const int32_t* table = block_table + static_cast<size_t>(entry_slot[e]) * table_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
+    const int k_lo = (window > 0 && pos_first - window + 1 > 0) ? ((pos_first - window + 1) / T5O_BN) * T5O_BN : 0;
+    const int n_tiles = (pos_last - k_lo) / T5O_BN + 1;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        t5_mbar_init(&q_full, 1);
+        for (int s = 0; s < STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
+        for (int g = 0; g < 2; ++g) {
+            t5_mbar_init(&s_full[g], 1);                 // the head's S of a tile is in TMEM
+            t5_mbar_init(&p_full[g], 128);               // every softmax thread of the head has put its row of P over S
+            t5_mbar_init(&pv_done[g], 1);                // the head's O holds the tile's P V
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_smem(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    t5_fence_before();
+    __syncthreads();
+    t5_fence_after();
+    const unsigned tmem = tmem_base_s;
+    auto s_col = [](int g) { return static_cast<unsigned>(g * 128); };
+    auto o_col = [](int g) { return static_cast<unsigned>(256 + g * 128); };
+
+    if (warp == 0) {
+        // ---- producer ----
+        if (lane == 0) {
+            t5_expect_tx(&q_full, 2 * 2 * T5_QHALF * sizeof(bf16));
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                t5_tma_2d(q_s + g * 2 * T5_QHALF, &q_map, (h0 + g) * T5_D, row_base, &q_full);
+                t5_tma_2d(q_s + g * 2 * T5_QHALF + T5_QHALF, &q_map, (h0 + g) * T5_D + 64, row_base, &q_full);
+            }
+            const int boxes = T5O_BN / page_size;
+            const int last_logical = pos_last / page_size;
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % STAGES;
+                if (j >= STAGES && !t5_wait(&kv_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base)) break;
+                t5_expect_tx(&kv_full[st], 2u * T5O_TILE * sizeof(bf16));
+                const int first_logical = (k_lo + j * T5O_BN) / page_size;
+                for (int b = 0; b < boxes; ++b) {
+                    const int logical = min(first_logical + b, last_logical);
+                    int page = logical < table_stride ? __ldg(table + logical) : -1;
+                    if (page < 0 || page >= num_pages) {
+                        if (atomicCAS(status, 0, 4) == 0) status[1] = row_base;
+                        page = 0;
+                    }
+                    const int k_row = ((page * 2) * nkv + kvh) * page_size;
+                    const int v_row = ((page * 2 + 1) * nkv + kvh) * page_size;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        t5_tma_2d(k_s + st * T5O_TILE + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, k_row, &kv_full[st]);
+                        t5_tma_2d(v_s + st * T5O_TILE + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, v_row, &kv_full[st]);
+                    }
+                }
+                issued = j + 1;
+            }
+            if (abort_flag)
+                for (int j = max(0, issued - STAGES); j < issued; ++j)
+                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&kv_full[j % STAGES], (j / STAGES) & 1); ++i) {}
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: S0(j), O1 += P1 V(j-1), S1(j), O0 += P0 V(j), ... ----
+        if (lane == 0) {
+            constexpr unsigned IDESC_QK = t5_idesc(T5_BM, T5O_BN, 0);
+            constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
+            const unsigned long long qd0 = t5_desc(q_s, 16, 1024), kd0 = t5_desc(k_s, 16, 1024);
+            const unsigned long long vd0 = t5_desc(v_s, T5O_HALF * sizeof(bf16), 1024);
+            constexpr unsigned long long STAGE_STEP = (T5O_TILE * sizeof(bf16)) >> 4;
+            auto qk = [&](int g, int st) {
+#pragma unroll
+                for (int k = 0; k < T5_D / 16; ++k) {
+                    const unsigned long long qoff = ((g * 2 + (k >> 2)) * T5_QHALF + (k & 3) * 16) * sizeof(bf16) >> 4;
+                    const unsigned long long koff = ((k >> 2) * T5O_HALF + (k & 3) * 16) * sizeof(bf16) >> 4;
+                    t5_mma_ss(tmem + s_col(g), qd0 + qoff, kd0 + st * STAGE_STEP + koff, IDESC_QK, k > 0);
+                }
+                t5_commit(&s_full[g]);
+            };
+            auto pv = [&](int g, int st, bool first) {
+#pragma unroll
+                for (int k = 0; k < T5O_BN / 16; ++k) {
+                    const unsigned long long voff = (k * 16 * 64) * sizeof(bf16) >> 4;       // 16 keys further, both 64-column halves
+                    t5_mma_ts(tmem + o_col(g), tmem + s_col(g) + k * 8, vd0 + st * STAGE_STEP + voff, IDESC_PV,
+                              (!first || k > 0) ? 1u : 0u);
+                }
+                t5_commit(&pv_done[g]);
+            };
+            bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int st = j % STAGES;
+                if (!t5_wait(&kv_full[st], (j / STAGES) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                t5_fence_after();
+                qk(0, st);
+                if (j > 0) {
+                    if (!t5_wait(&p_full[1], (j - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                    t5_fence_after();
+                    pv(1, (j - 1) % STAGES, j == 1);
+                    t5_commit(&kv_empty[(j - 1) % STAGES]);            // the last reader of tile j-1
+                }
+                qk(1, st);
+                if (!t5_wait(&p_full[0], j & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                t5_fence_after();
+                pv(0, st, j == 0);
+            }
+            if (ok && t5_wait(&p_full[1], (n_tiles - 1) & 1, &abort_flag, status, row_base)) {
+                t5_fence_after();
+                pv(1, (n_tiles - 1) % STAGES, n_tiles == 1);
+                t5_commit(&kv_empty[(n_tiles - 1) % STAGES]);
+            }
+        }
+    } else {
+        // ---- softmax: a thread owns one query row of one head = one TMEM lane ----
+        const int g = (warp - 2) >> 2;                            // warps 2..5: head h0, warps 6..9: head h0 + 1
+        const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
+        const int pos = (row < rows_here) ? past + q0 + row : -1;
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        float m = -CUDART_INF_F, l = 0.0f;                        // m: the reference maximum, in units of log2
+        bool ok = true;
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int kt = k_lo + j * T5O_BN;
+            if (!t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            t5_fence_after();
+            const bool full_tile = (kt + T5O_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
+            // the tile's maximum over the keys this row sees
+            float mx = -CUDART_INF_F;
+#pragma unroll 1
+            for (int c = 0; c < T5O_BN; c += 64) {
+                unsigned r[2][32];
+                t5_ld32(tmem + lane_addr + s_col(g) + c, r[0]);
+                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, r[1]);
+                t5_wait_ld();
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    if (full_tile) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[cc][i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = kt + c + cc * 32 + i;
+                            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(r[cc][i]));
+                        }
+                    }
+                }
+            }
+            mx *= scale_log2e;                                    // scale > 0; -inf stays -inf
+            // move the reference up only when the maximum has run away from it
+            const bool adopt = (m == -CUDART_INF_F) && (mx > m);  // nothing accumulated under the old reference
+            const bool jump = (m != -CUDART_INF_F) && (mx > m + T5O_JUMP);
+            if (__any_sync(0xffffffffu, jump)) {
+                // O still receives the previous tile's product: wait for it, then scale this warp's rows
+                if (!t5_wait(&pv_done[g], (j - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                t5_fence_after();
+                const float alpha = jump ? t5_ex2(m - mx) : 1.0f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < T5_D; c += 32) {
+                    unsigned r[32];
+                    t5_ld32(tmem + lane_addr + o_col(g) + c, r);
+                    t5_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    t5_st32(tmem + lane_addr + o_col(g) + c, r);
+                }
+                t5_wait_st();
+            }
+            if (adopt || jump) m = mx;
+            const float msub = (m == -CUDART_INF_F) ? 0.0f : m;
+            // the weights, rounded to bfloat16, over the first half of S
+#pragma unroll 1
+            for (int c = 0; c < T5O_BN; c += 32) {
+                unsigned r[32], pk[16];
+                t5_ld32(tmem + lane_addr + s_col(g) + c, r);
+                t5_wait_ld();
+                if (full_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
+                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
+                        l += p0 + p1;
+                        pk[i >> 1] = t5_pack(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = kt + c + i;
+                        const float p0 = (key <= pos && key >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub)) : 0.0f;
+                        const float p1 = (key + 1 <= pos && key + 1 >= lo) ? t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub)) : 0.0f;
+                        l += p0 + p1;
+                        pk[i >> 1] = t5_pack(p0, p1);
+                    }
+                }
+                // columns c/2 .. c/2+15 of P lie over columns of S already read (c/2 + 15 < c + 32)
+                t5_st16(tmem + lane_addr + s_col(g) + (c >> 1), pk);
+            }
+            t5_wait_st();
+            t5_fence_before();
+            t5_arrive(&p_full[g]);
+        }
+        if (ok && t5_wait(&pv_done[g], (n_tiles - 1) & 1, &abort_flag, status, row_base)) {
+            t5_fence_after();
+            const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h0 + g) * T5_D;
+#pragma unroll 1
+            for (int c = 0; c < T5_D; c += 32) {
+                unsigned r[32];
+                t5_ld32(tmem + lane_addr + o_col(g) + c, r);
+                t5_wait_ld();
+                if (row < rows_here) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = t5_pack(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        w.y = t5_pack(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        w.z = t5_pack(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        w.w = t5_pack(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    t5_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        t5_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------
 typedef CUresult (*T5EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -505,6 +795,21 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
         launch_pdl(kern, dim3(nq / HEADS, n_tiles), dim3(64 + 128 * HEADS), smem, s, q_map, kv_map,                  \
                    static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,             \
                    block_table, table_stride, nq, nkv, page_size, window, sl2, num_pages, status);                   \
+    }
+    static int two_pass = -1;                                       // LLM_PREFILL_T5=twopass keeps the two-pass kernel
+    if (two_pass < 0) {
+        const char* ev = getenv("LLM_PREFILL_T5");
+        two_pass = (ev && ev[0] == 't') ? 1 : 0;
+    }
+    if (group % 2 == 0 && !two_pass) {
+        const size_t smem = static_cast<size_t>(2 * 2 * T5_QHALF + 2 * T5O_STAGES * T5O_TILE) * sizeof(bf16) + 1024;
+        auto kern = paged_prefill_attention_tcgen05_online_kernel;
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        launch_pdl(kern, dim3(nq / 2, n_tiles), dim3(320), smem, s, q_map, kv_map, static_cast<bf16*>(out), tiles,
+                   entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv, page_size,
+                   window, sl2, num_pages, status);
+        return launch_status();
     }
     if (group % 2 == 0) T5_GO(2, 4) else T5_GO(1, 4)
 #undef T5_GO
