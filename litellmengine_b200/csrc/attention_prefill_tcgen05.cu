@@ -58,7 +58,7 @@ __device__ __forceinline__ bool t5_try_wait(unsigned long long* bar, unsigned pa
 // and of its first softmax thread; llm_t5_trace_read copies them out.  A debugging aid only.
 #ifdef T5_TRACE
 #define T5_TRACE_LEN 8192
-__device__ long long g_t5_trace[2][T5_TRACE_LEN];
+__device__ long long g_t5_trace[3][T5_TRACE_LEN];
 #define T5_EVENT(role, n, code, u)                                                      \
     do {                                                                                \
         if (blockIdx.x == 0 && blockIdx.y == 0 && (n) + 2 < T5_TRACE_LEN) {                                \
@@ -468,6 +468,26 @@ __device__ __forceinline__ void t5_st32(unsigned taddr, const unsigned (&r)[32])
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
 
+// exp2 on the FMA pipe for a share of the weights (the special-function unit makes 16 a clock per
+// SM, which 2 x 128 x 128 exponentials per tile would saturate): x = n + f with n = round(x),
+// 2^f on [-0.5, 0.5] by a cubic (relative error 1e-4, far below bfloat16's 4e-3), n added to the
+// exponent field.  x is clamped at -125 (the result is then 2^-125, which rounds away in the sums).
+__device__ __forceinline__ float t5_ex2_poly(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;                       // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.05550357f, 0.24022652f);
+    p = fmaf(p, f, 0.69314720f);
+    p = fmaf(p, f, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+#ifndef T5O_POLY_EVERY
+#define T5O_POLY_EVERY 0                                   // one weight in this many takes the polynomial (0: none)
+#endif
+__device__ __forceinline__ constexpr bool t5_use_poly(int i) {
+    return T5O_POLY_EVERY > 0 && (i % (T5O_POLY_EVERY > 0 ? T5O_POLY_EVERY : 1)) == T5O_POLY_EVERY - 1;
+}
+
 __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
     const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
@@ -482,7 +502,10 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
     bf16* q_s = reinterpret_cast<bf16*>(smem_al);                 // [2 heads][2 halves][128][64]
     bf16* k_s = q_s + 2 * 2 * T5_QHALF;                           // [STAGES][2][128][64]
     bf16* v_s = k_s + STAGES * T5O_TILE;                          // [STAGES][2][128][64]
-    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], pv_done[2];
+    // keys and values have rings of their own: a key tile is free once both heads' S are made, a
+    // value tile only after both heads' P V, half a tile's work later
+    __shared__ __align__(8) unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES],
+        s_full[2], p_full[2], pv_done[2];
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
 
@@ -503,7 +526,10 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
     if (tid == 0) {
         abort_flag = 0;
         t5_mbar_init(&q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { t5_mbar_init(&kv_full[s], 1); t5_mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) {
+            t5_mbar_init(&k_full[s], 1); t5_mbar_init(&k_empty[s], 1);
+            t5_mbar_init(&v_full[s], 1); t5_mbar_init(&v_empty[s], 1);
+        }
         for (int g = 0; g < 2; ++g) {
             t5_mbar_init(&s_full[g], 1);                 // the head's S of a tile is in TMEM
             t5_mbar_init(&p_full[g], 128);               // every softmax thread of the head has put its row of P over S
@@ -533,11 +559,14 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
             }
             const int boxes = T5O_BN / page_size;
             const int last_logical = pos_last / page_size;
-            int issued = 0;
-            for (int j = 0; j < n_tiles; ++j) {
+            int issued_k = 0, issued_v = 0;
+            auto load = [&](int j, bool values) -> bool {
                 const int st = j % STAGES;
-                if (j >= STAGES && !t5_wait(&kv_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base)) break;
-                t5_expect_tx(&kv_full[st], 2u * T5O_TILE * sizeof(bf16));
+                unsigned long long* full = values ? &v_full[st] : &k_full[st];
+                if (j >= STAGES && !t5_wait(values ? &v_empty[st] : &k_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base))
+                    return false;
+                t5_expect_tx(full, T5O_TILE * sizeof(bf16));
+                bf16* dst = (values ? v_s : k_s) + st * T5O_TILE;
                 const int first_logical = (k_lo + j * T5O_BN) / page_size;
                 for (int b = 0; b < boxes; ++b) {
                     const int logical = min(first_logical + b, last_logical);
@@ -546,67 +575,96 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
                         if (atomicCAS(status, 0, 4) == 0) status[1] = row_base;
                         page = 0;
                     }
-                    const int k_row = ((page * 2) * nkv + kvh) * page_size;
-                    const int v_row = ((page * 2 + 1) * nkv + kvh) * page_size;
+                    const int row0 = ((page * 2 + (values ? 1 : 0)) * nkv + kvh) * page_size;
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        t5_tma_2d(k_s + st * T5O_TILE + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, k_row, &kv_full[st]);
-                        t5_tma_2d(v_s + st * T5O_TILE + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, v_row, &kv_full[st]);
-                    }
+                    for (int half = 0; half < 2; ++half)
+                        t5_tma_2d(dst + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, row0, full);
                 }
-                issued = j + 1;
+                return true;
+            };
+            for (int j = 0; j < n_tiles; ++j) {
+                if (!load(j, false)) break;
+                issued_k = j + 1;
+                if (!load(j, true)) break;
+                issued_v = j + 1;
             }
-            if (abort_flag)
-                for (int j = max(0, issued - STAGES); j < issued; ++j)
-                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&kv_full[j % STAGES], (j / STAGES) & 1); ++i) {}
+            if (abort_flag) {                                     // let what is in flight land before the CTA goes away
+                for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
+                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&k_full[j % STAGES], (j / STAGES) & 1); ++i) {}
+                for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
+                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&v_full[j % STAGES], (j / STAGES) & 1); ++i) {}
+            }
         }
     } else if (warp == 1) {
         // ---- MMA issuer: S0(j), O1 += P1 V(j-1), S1(j), O0 += P0 V(j), ... ----
         if (lane == 0) {
             constexpr unsigned IDESC_QK = t5_idesc(T5_BM, T5O_BN, 0);
             constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
-            const unsigned long long qd0 = t5_desc(q_s, 16, 1024), kd0 = t5_desc(k_s, 16, 1024);
-            const unsigned long long vd0 = t5_desc(v_s, T5O_HALF * sizeof(bf16), 1024);
-            constexpr unsigned long long STAGE_STEP = (T5O_TILE * sizeof(bf16)) >> 4;
-            auto qk = [&](int g, int st) {
+            // One thread issues every product, and what it computes per instruction is what limits the
+            // rate of issue: every operand descriptor is made once, here, and the loop over tiles is
+            // unrolled by the two stages so that each product names its descriptors by constant index.
+            unsigned long long qd[2][8], kd[2][8], vd[2][8];
+            {
+                const unsigned long long qd0 = t5_desc(q_s, 16, 1024), kd0 = t5_desc(k_s, 16, 1024);
+                const unsigned long long vd0 = t5_desc(v_s, T5O_HALF * sizeof(bf16), 1024);
+                constexpr unsigned long long STAGE_STEP = (T5O_TILE * sizeof(bf16)) >> 4;
 #pragma unroll
-                for (int k = 0; k < T5_D / 16; ++k) {
-                    const unsigned long long qoff = ((g * 2 + (k >> 2)) * T5_QHALF + (k & 3) * 16) * sizeof(bf16) >> 4;
-                    const unsigned long long koff = ((k >> 2) * T5O_HALF + (k & 3) * 16) * sizeof(bf16) >> 4;
-                    t5_mma_ss(tmem + s_col(g), qd0 + qoff, kd0 + st * STAGE_STEP + koff, IDESC_QK, k > 0);
-                }
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        qd[a][k] = qd0 + (((a * 2 + (k >> 2)) * T5_QHALF + (k & 3) * 16) * sizeof(bf16) >> 4);
+                        kd[a][k] = kd0 + a * STAGE_STEP + (((k >> 2) * T5O_HALF + (k & 3) * 16) * sizeof(bf16) >> 4);
+                        vd[a][k] = vd0 + a * STAGE_STEP + ((k * 16 * 64) * sizeof(bf16) >> 4);   // 16 keys further, both 64-column halves
+                    }
+            }
+            auto qk = [&](int g, int st) {                        // g, st: constants where this is inlined
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t5_mma_ss(tmem + s_col(g), qd[g][k], kd[st][k], IDESC_QK, k > 0);
                 t5_commit(&s_full[g]);
             };
             auto pv = [&](int g, int st, bool first) {
 #pragma unroll
-                for (int k = 0; k < T5O_BN / 16; ++k) {
-                    const unsigned long long voff = (k * 16 * 64) * sizeof(bf16) >> 4;       // 16 keys further, both 64-column halves
-                    t5_mma_ts(tmem + o_col(g), tmem + s_col(g) + k * 8, vd0 + st * STAGE_STEP + voff, IDESC_PV,
-                              (!first || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < 8; ++k)
+                    t5_mma_ts(tmem + o_col(g), tmem + s_col(g) + k * 8, vd[st][k], IDESC_PV, (!first || k > 0) ? 1u : 0u);
                 t5_commit(&pv_done[g]);
             };
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
-            for (int j = 0; ok && j < n_tiles; ++j) {
-                const int st = j % STAGES;
-                if (!t5_wait(&kv_full[st], (j / STAGES) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            int tn = 0; (void)tn;
+            auto one_tile = [&](int j, int st) -> bool {          // st = j % 2, a constant where this is inlined
+                T5_EVENT(0, tn, 0, j);
+                if (!t5_wait(&k_full[st], (j >> 1) & 1, &abort_flag, status, row_base)) return false;
                 t5_fence_after();
+                T5_EVENT(0, tn, 1, j);
                 qk(0, st);
+                T5_EVENT(0, tn, 2, j);
                 if (j > 0) {
-                    if (!t5_wait(&p_full[1], (j - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                    if (!t5_wait(&p_full[1], (j - 1) & 1, &abort_flag, status, row_base)) return false;
                     t5_fence_after();
-                    pv(1, (j - 1) % STAGES, j == 1);
-                    t5_commit(&kv_empty[(j - 1) % STAGES]);            // the last reader of tile j-1
+                    T5_EVENT(0, tn, 3, j);
+                    pv(1, 1 - st, j == 1);
+                    t5_commit(&v_empty[1 - st]);                       // the last reader of the values of tile j-1
+                    T5_EVENT(0, tn, 4, j);
                 }
                 qk(1, st);
-                if (!t5_wait(&p_full[0], j & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                t5_commit(&k_empty[st]);                               // the last reader of the keys of tile j
+                T5_EVENT(0, tn, 5, j);
+                if (!t5_wait(&p_full[0], j & 1, &abort_flag, status, row_base)) return false;
+                if (!t5_wait(&v_full[st], (j >> 1) & 1, &abort_flag, status, row_base)) return false;
                 t5_fence_after();
+                T5_EVENT(0, tn, 6, j);
                 pv(0, st, j == 0);
+                T5_EVENT(0, tn, 7, j);
+                return true;
+            };
+            static_assert(T5O_STAGES == 2, "the issue loop is unrolled by the number of stages");
+            for (int j = 0; ok && j < n_tiles; j += 2) {
+                ok = one_tile(j, 0);
+                if (ok && j + 1 < n_tiles) ok = one_tile(j + 1, 1);
             }
             if (ok && t5_wait(&p_full[1], (n_tiles - 1) & 1, &abort_flag, status, row_base)) {
                 t5_fence_after();
-                pv(1, (n_tiles - 1) % STAGES, n_tiles == 1);
-                t5_commit(&kv_empty[(n_tiles - 1) % STAGES]);
+                if ((n_tiles - 1) & 1) { pv(1, 1, n_tiles == 1); t5_commit(&v_empty[1]); }
+                else { pv(1, 0, n_tiles == 1); t5_commit(&v_empty[0]); }
             }
         }
     } else {
@@ -619,34 +677,46 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;                        // m: the reference maximum, in units of log2
         bool ok = true;
+        int tn = 0; (void)tn;
+        const bool tracer = (quarter == 2 && lane == 0); (void)tracer;    // warps 2 and 6
         for (int j = 0; ok && j < n_tiles; ++j) {
             const int kt = k_lo + j * T5O_BN;
+            if (tracer) T5_EVENT(1 + g, tn, 10, j);
             if (!t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
+            if (tracer) T5_EVENT(1 + g, tn, 11, j);
             const bool full_tile = (kt + T5O_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-            // the tile's maximum over the keys this row sees
+            // The tile's maximum over the keys this row sees.  S is read from TMEM twice (here and for
+            // the weights below) in loops that are not unrolled: holding the row in 128 registers with
+            // everything unrolled made code too long for so few warps to fetch (measured 1.4x slower).
+            // (Loads run one chunk ahead of the arithmetic: with one softmax warp of a head per
+            // scheduler there is no other warp to hide a TMEM load behind.)
             float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < T5O_BN; c += 64) {
-                unsigned r[2][32];
-                t5_ld32(tmem + lane_addr + s_col(g) + c, r[0]);
-                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, r[1]);
-                t5_wait_ld();
+            unsigned ra[32], rb[32];
+            auto tile_max = [&](const unsigned (&r)[32], int c) {
+                if (full_tile) {
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    if (full_tile) {
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[cc][i]));
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int key = kt + c + cc * 32 + i;
-                            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(r[cc][i]));
-                        }
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kt + c + i;
+                        if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(r[i]));
                     }
                 }
+            };
+            t5_ld32(tmem + lane_addr + s_col(g), ra);
+#pragma unroll 1
+            for (int c = 0; c < T5O_BN; c += 64) {
+                t5_wait_ld();
+                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, rb);
+                tile_max(ra, c);
+                t5_wait_ld();
+                if (c + 64 < T5O_BN) t5_ld32(tmem + lane_addr + s_col(g) + c + 64, ra);
+                tile_max(rb, c + 32);
             }
             mx *= scale_log2e;                                    // scale > 0; -inf stays -inf
+            if (tracer) T5_EVENT(1 + g, tn, 12, j);
             // move the reference up only when the maximum has run away from it
             const bool adopt = (m == -CUDART_INF_F) && (mx > m);  // nothing accumulated under the old reference
             const bool jump = (m != -CUDART_INF_F) && (mx > m + T5O_JUMP);
@@ -666,20 +736,20 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
                     t5_st32(tmem + lane_addr + o_col(g) + c, r);
                 }
                 t5_wait_st();
+                if (tracer) T5_EVENT(1 + g, tn, 13, j);
             }
             if (adopt || jump) m = mx;
             const float msub = (m == -CUDART_INF_F) ? 0.0f : m;
             // the weights, rounded to bfloat16, over the first half of S
-#pragma unroll 1
-            for (int c = 0; c < T5O_BN; c += 32) {
-                unsigned r[32], pk[16];
-                t5_ld32(tmem + lane_addr + s_col(g) + c, r);
-                t5_wait_ld();
+            auto weights = [&](const unsigned (&r)[32], int c) {
+                unsigned pk[16];
                 if (full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = t5_ex2(fmaf(__uint_as_float(r[i]), scale_log2e, -msub));
-                        const float p1 = t5_ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub));
+                        const float x0 = fmaf(__uint_as_float(r[i]), scale_log2e, -msub);
+                        const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub);
+                        const float p0 = t5_use_poly(i) ? t5_ex2_poly(x0) : t5_ex2(x0);
+                        const float p1 = t5_use_poly(i + 1) ? t5_ex2_poly(x1) : t5_ex2(x1);
                         l += p0 + p1;
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
@@ -693,10 +763,22 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
                 }
-                // columns c/2 .. c/2+15 of P lie over columns of S already read (c/2 + 15 < c + 32)
+                // columns c/2 .. c/2+15 of P lie over columns of S that are in registers by now:
+                // the load that runs ahead covers columns up to c + 63, and c/2 + 15 < c + 32
                 t5_st16(tmem + lane_addr + s_col(g) + (c >> 1), pk);
+            };
+            t5_ld32(tmem + lane_addr + s_col(g), ra);
+#pragma unroll 1
+            for (int c = 0; c < T5O_BN; c += 64) {
+                t5_wait_ld();
+                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, rb);
+                weights(ra, c);
+                t5_wait_ld();
+                if (c + 64 < T5O_BN) t5_ld32(tmem + lane_addr + s_col(g) + c + 64, ra);
+                weights(rb, c + 32);
             }
             t5_wait_st();
+            if (tracer) T5_EVENT(1 + g, tn, 14, j);
             t5_fence_before();
             t5_arrive(&p_full[g]);
         }

@@ -320,7 +320,7 @@ def test_sample_rows_follow_their_own_streams(vocab):
 
 
 # ---- the tuned bfloat16 attention kernels ------------------------------------------------------
-def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1, seed=0):
+def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1, seed=0, ramp=None):
     """reqs: [(keys in the cache after the step, queries at the end)].  Runs `kernel` ('decode' or
     'prefill') over all queries and returns (out, reference) for the query rows."""
     g = torch.Generator().manual_seed(seed)
@@ -343,6 +343,9 @@ def fast_case(kernel, nq, nkv, d, page, reqs, window=None, spike=None, splits=1,
             k[j, :, 0] = 6.0
             q[:, :, 0] = 3.0 * math.sqrt(d)
             v[j] = torch.arange(d, dtype=torch.float32)[None, :] + 100.0
+        if ramp is not None and ramp[0] == b:                # scores that climb with the key index, by ramp[1] in all
+            k[:, :, 0] = torch.linspace(0.0, ramp[1], n)[:, None]
+            q[:, :, 0] = math.sqrt(d)
         q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
         for t in range(n):
             cache[table[b, t // page], 0, :, t % page] = k[t]
@@ -478,6 +481,15 @@ def test_prefill_tcgen05_finds_a_far_key(key):
     means = out[30:].float().mean(dim=(1, 2))
     for i in range(nqr):
         assert (float(means[i]) > 90.0) == (first_q + i >= key)
+
+
+@pytest.mark.parametrize("climb", [3.0, 12.0, 40.0, 150.0])
+def test_prefill_tcgen05_scores_that_keep_climbing(climb):
+    """The one-pass kernel keeps a reference maximum that trails the running one and rescales its
+    accumulator only when the maximum has run away: scores that rise with the key index by
+    `climb` over 1,500 keys (12 tiles) make that happen never, sometimes, or at every tile."""
+    out, ref = fast_case("prefill_tcgen05", 4, 2, 128, 16, [(40, 40), (1500, 300)], ramp=(1, climb), seed=3)
+    close(out, ref, 1e-2)
 
 
 @pytest.mark.parametrize("window", [1, 5, 128, 129, 200])
