@@ -58,7 +58,7 @@ __device__ __forceinline__ bool t5_try_wait(unsigned long long* bar, unsigned pa
 // and of its first softmax thread; llm_t5_trace_read copies them out.  A debugging aid only.
 #ifdef T5_TRACE
 #define T5_TRACE_LEN 8192
-__device__ long long g_t5_trace[3][T5_TRACE_LEN];
+__device__ long long g_t5_trace[4][T5_TRACE_LEN];
 #define T5_EVENT(role, n, code, u)                                                      \
     do {                                                                                \
         if (blockIdx.x == 0 && blockIdx.y == 0 && (n) + 2 < T5_TRACE_LEN) {                                \
@@ -457,6 +457,7 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
 #define T5O_TILE (2 * T5O_HALF)
 #define T5O_STAGES 2
 #define T5O_JUMP 8.0f
+#define T5O_THREADS (64 + 2 * 256)             // producer warp, issuing warp, then 8 softmax warps per head
 
 __device__ __forceinline__ void t5_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile(
@@ -488,7 +489,7 @@ __device__ __forceinline__ constexpr bool t5_use_poly(int i) {
     return T5O_POLY_EVERY > 0 && (i % (T5O_POLY_EVERY > 0 ? T5O_POLY_EVERY : 1)) == T5O_POLY_EVERY - 1;
 }
 
-__global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online_kernel(
+__global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen05_online_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, bf16* __restrict__ out,
     const int32_t* __restrict__ tiles, const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
@@ -508,6 +509,8 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
         s_full[2], p_full[2], pv_done[2];
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
+    __shared__ float x_max[2][2][2][128];                         // [tile parity][head][column half][row]: the halves' maxima
+    __shared__ float x_sum[2][2][128];                            // [head][column half][row]: the halves' row sums, at the end
 
     const int tile = blockIdx.y;
     const int h0 = blockIdx.x * 2;                                // first of this CTA's two query heads
@@ -532,7 +535,7 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
         }
         for (int g = 0; g < 2; ++g) {
             t5_mbar_init(&s_full[g], 1);                 // the head's S of a tile is in TMEM
-            t5_mbar_init(&p_full[g], 128);               // every softmax thread of the head has put its row of P over S
+            t5_mbar_init(&p_full[g], 256);               // every softmax thread of the head has put its part of P over S
             t5_mbar_init(&pv_done[g], 1);                // the head's O holds the tile's P V
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -549,7 +552,10 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
     auto o_col = [](int g) { return static_cast<unsigned>(256 + g * 128); };
 
     if (warp == 0) {
-        // ---- producer ----
+        // ---- producer: lane b looks up the page of box b of a tile, one tile ahead, and asks the copy
+        // engine for it ----
+        // (One thread doing this box by box spent 140 clocks a copy, 4,500 a tile: longer than the
+        // tile's products take.  A warp-wide copy instruction makes all boxes' requests at once.)
         if (lane == 0) {
             t5_expect_tx(&q_full, 2 * 2 * T5_QHALF * sizeof(bf16));
 #pragma unroll
@@ -557,43 +563,55 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
                 t5_tma_2d(q_s + g * 2 * T5_QHALF, &q_map, (h0 + g) * T5_D, row_base, &q_full);
                 t5_tma_2d(q_s + g * 2 * T5_QHALF + T5_QHALF, &q_map, (h0 + g) * T5_D + 64, row_base, &q_full);
             }
-            const int boxes = T5O_BN / page_size;
-            const int last_logical = pos_last / page_size;
-            int issued_k = 0, issued_v = 0;
-            auto load = [&](int j, bool values) -> bool {
-                const int st = j % STAGES;
+        }
+        const int boxes = T5O_BN / page_size;                     // at most 16
+        const int last_logical = pos_last / page_size;
+        auto page_of = [&](int j) {                               // lane b: the page of box b of tile j (checked)
+            if (j >= n_tiles || lane >= boxes) return 0;
+            const int logical = min((k_lo + j * T5O_BN) / page_size + lane, last_logical);
+            int page = logical < table_stride ? __ldg(table + logical) : -1;
+            if (page < 0 || page >= num_pages) {
+                if (atomicCAS(status, 0, 4) == 0) status[1] = row_base;
+                page = 0;
+            }
+            return page;
+        };
+        int issued_k = 0, issued_v = 0;
+        int tn = 0; (void)tn;
+        int next_page = page_of(0);
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j % STAGES;
+            const int my_page = next_page;
+            next_page = page_of(j + 1);
+#pragma unroll 1
+            for (int values = 0; values < 2; ++values) {
                 unsigned long long* full = values ? &v_full[st] : &k_full[st];
-                if (j >= STAGES && !t5_wait(values ? &v_empty[st] : &k_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base))
-                    return false;
-                t5_expect_tx(full, T5O_TILE * sizeof(bf16));
-                bf16* dst = (values ? v_s : k_s) + st * T5O_TILE;
-                const int first_logical = (k_lo + j * T5O_BN) / page_size;
-                for (int b = 0; b < boxes; ++b) {
-                    const int logical = min(first_logical + b, last_logical);
-                    int page = logical < table_stride ? __ldg(table + logical) : -1;
-                    if (page < 0 || page >= num_pages) {
-                        if (atomicCAS(status, 0, 4) == 0) status[1] = row_base;
-                        page = 0;
-                    }
-                    const int row0 = ((page * 2 + (values ? 1 : 0)) * nkv + kvh) * page_size;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        t5_tma_2d(dst + half * T5O_HALF + b * page_size * 64, &kv_map, half * 64, row0, full);
+                if (lane == 0) {
+                    T5_EVENT(3, tn, 30 + values, j);
+                    if (j >= STAGES && !t5_wait(values ? &v_empty[st] : &k_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base))
+                        ok = false;
+                    T5_EVENT(3, tn, 32 + values, j);
+                    if (ok) t5_expect_tx(full, T5O_TILE * sizeof(bf16));
                 }
-                return true;
-            };
-            for (int j = 0; j < n_tiles; ++j) {
-                if (!load(j, false)) break;
-                issued_k = j + 1;
-                if (!load(j, true)) break;
-                issued_v = j + 1;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                bf16* dst = (values ? v_s : k_s) + st * T5O_TILE;
+                if (lane < boxes) {                               // every lane asks for its own box: one instruction, `boxes` copies
+                    const int row0 = ((my_page * 2 + values) * nkv + kvh) * page_size;
+                    t5_tma_2d(dst + lane * page_size * 64, &kv_map, 0, row0, full);
+                    t5_tma_2d(dst + T5O_HALF + lane * page_size * 64, &kv_map, 64, row0, full);
+                }
+                if (lane == 0) T5_EVENT(3, tn, 34 + values, j);
+                if (values) issued_v = j + 1; else issued_k = j + 1;
             }
-            if (abort_flag) {                                     // let what is in flight land before the CTA goes away
-                for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
-                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&k_full[j % STAGES], (j / STAGES) & 1); ++i) {}
-                for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
-                    for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&v_full[j % STAGES], (j / STAGES) & 1); ++i) {}
-            }
+            if (!ok) break;
+        }
+        if (lane == 0 && abort_flag) {                            // let what is in flight land before the CTA goes away
+            for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
+                for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&k_full[j % STAGES], (j / STAGES) & 1); ++i) {}
+            for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
+                for (int i = 0; i < T5_WAIT_LIMIT && !t5_try_wait(&v_full[j % STAGES], (j / STAGES) & 1); ++i) {}
         }
     } else if (warp == 1) {
         // ---- MMA issuer: S0(j), O1 += P1 V(j-1), S1(j), O0 += P0 V(j), ... ----
@@ -625,7 +643,8 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
             auto pv = [&](int g, int st, bool first) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
-                    t5_mma_ts(tmem + o_col(g), tmem + s_col(g) + k * 8, vd[st][k], IDESC_PV, (!first || k > 0) ? 1u : 0u);
+                    t5_mma_ts(tmem + o_col(g), tmem + s_col(g) + (k >> 2) * 64 + (k & 3) * 8, vd[st][k], IDESC_PV,
+                              (!first || k > 0) ? 1u : 0u);      // P of keys 64..127 lies over S column 64
                 t5_commit(&pv_done[g]);
             };
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
@@ -668,79 +687,82 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
             }
         }
     } else {
-        // ---- softmax: a thread owns one query row of one head = one TMEM lane ----
-        const int g = (warp - 2) >> 2;                            // warps 2..5: head h0, warps 6..9: head h0 + 1
-        const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
+        // ---- softmax: two threads share a query row of a head (one TMEM lane), 64 columns of S each ----
+        // A warp reaches the 32 TMEM lanes of its quarter (warp index mod 4) only, so the two threads
+        // of a row sit in two warps of the same quarter.  Each keeps its 64 values of S in registers,
+        // the two exchange their maxima through shared memory, and each writes its 32 columns of P
+        // over the first half of ITS OWN columns of S (so neither ever touches the other's columns).
+        const int wl = warp - 2;
+        const int g = wl >> 3;                                    // warps 2..9: head h0, warps 10..17: head h0 + 1
+        const int half = (wl >> 2) & 1;                           // columns 64*half .. 64*half+63 of every tile
+        const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
+        const unsigned my_s = tmem + lane_addr + s_col(g) + half * 64;
+        const unsigned my_o = tmem + lane_addr + o_col(g) + half * 64;
         const int pos = (row < rows_here) ? past + q0 + row : -1;
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;                        // m: the reference maximum, in units of log2
         bool ok = true;
         int tn = 0; (void)tn;
-        const bool tracer = (quarter == 2 && lane == 0); (void)tracer;    // warps 2 and 6
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const int kt = k_lo + j * T5O_BN;
+        const bool tracer = (wl == 0 || wl == 8) && lane == 0; (void)tracer;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int kt = k_lo + j * T5O_BN + half * 64;         // this thread's first key of the tile
             if (tracer) T5_EVENT(1 + g, tn, 10, j);
-            if (!t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) { ok = false; break; }
+            // After a wait has run out (ok false) a thread still passes every barrier below, the same
+            // number of times as the others, and touches nothing else.
+            if (ok && !t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) ok = false;
             t5_fence_after();
             if (tracer) T5_EVENT(1 + g, tn, 11, j);
-            const bool full_tile = (kt + T5O_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
-            // The tile's maximum over the keys this row sees.  S is read from TMEM twice (here and for
-            // the weights below) in loops that are not unrolled: holding the row in 128 registers with
-            // everything unrolled made code too long for so few warps to fetch (measured 1.4x slower).
-            // (Loads run one chunk ahead of the arithmetic: with one softmax warp of a head per
-            // scheduler there is no other warp to hide a TMEM load behind.)
-            float mx = -CUDART_INF_F;
+            const bool full_tile = (kt + 63 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned ra[32], rb[32];
-            auto tile_max = [&](const unsigned (&r)[32], int c) {
+            float mx = -CUDART_INF_F;
+            if (ok) {
+                t5_ld32(my_s, ra);
+                t5_ld32(my_s + 32, rb);
+                t5_wait_ld();
                 if (full_tile) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(ra[i]), __uint_as_float(rb[i])));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = kt + c + i;
-                        if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(r[i]));
+                        if (kt + i <= pos && kt + i >= lo) mx = fmaxf(mx, __uint_as_float(ra[i]));
+                        if (kt + 32 + i <= pos && kt + 32 + i >= lo) mx = fmaxf(mx, __uint_as_float(rb[i]));
                     }
                 }
-            };
-            t5_ld32(tmem + lane_addr + s_col(g), ra);
-#pragma unroll 1
-            for (int c = 0; c < T5O_BN; c += 64) {
-                t5_wait_ld();
-                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, rb);
-                tile_max(ra, c);
-                t5_wait_ld();
-                if (c + 64 < T5O_BN) t5_ld32(tmem + lane_addr + s_col(g) + c + 64, ra);
-                tile_max(rb, c + 32);
+                x_max[j & 1][g][half][row] = mx;
             }
-            mx *= scale_log2e;                                    // scale > 0; -inf stays -inf
+            asm volatile("bar.sync %0, 256;\n" ::"r"(1 + g) : "memory");      // the 8 softmax warps of this head
+            if (!ok) continue;
+            mx = fmaxf(mx, x_max[j & 1][g][half ^ 1][row]) * scale_log2e;     // scale > 0; -inf stays -inf
             if (tracer) T5_EVENT(1 + g, tn, 12, j);
-            // move the reference up only when the maximum has run away from it
+            // move the reference up only when the maximum has run away from it (both threads of a row
+            // see the same numbers and decide alike)
             const bool adopt = (m == -CUDART_INF_F) && (mx > m);  // nothing accumulated under the old reference
             const bool jump = (m != -CUDART_INF_F) && (mx > m + T5O_JUMP);
             if (__any_sync(0xffffffffu, jump)) {
-                // O still receives the previous tile's product: wait for it, then scale this warp's rows
-                if (!t5_wait(&pv_done[g], (j - 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
+                // O still receives the previous tile's product: wait for it, then scale this thread's half of its row
+                if (!t5_wait(&pv_done[g], (j - 1) & 1, &abort_flag, status, row_base)) { ok = false; continue; }
                 t5_fence_after();
                 const float alpha = jump ? t5_ex2(m - mx) : 1.0f;
                 l *= alpha;
 #pragma unroll 1
-                for (int c = 0; c < T5_D; c += 32) {
-                    unsigned r[32];
-                    t5_ld32(tmem + lane_addr + o_col(g) + c, r);
+                for (int c = 0; c < 64; c += 32) {                // through ra, which is read again below
+                    t5_ld32(my_o + c, ra);
                     t5_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    t5_st32(tmem + lane_addr + o_col(g) + c, r);
+                    for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+                    t5_st32(my_o + c, ra);
                 }
                 t5_wait_st();
+                t5_ld32(my_s, ra);
+                t5_wait_ld();
                 if (tracer) T5_EVENT(1 + g, tn, 13, j);
             }
             if (adopt || jump) m = mx;
             const float msub = (m == -CUDART_INF_F) ? 0.0f : m;
-            // the weights, rounded to bfloat16, over the first half of S
+            // the weights, rounded to bfloat16: 32 columns of P over the first half of this thread's 64 of S
             auto weights = [&](const unsigned (&r)[32], int c) {
                 unsigned pk[16];
                 if (full_tile) {
@@ -763,33 +785,27 @@ __global__ void __launch_bounds__(320, 1) paged_prefill_attention_tcgen05_online
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
                 }
-                // columns c/2 .. c/2+15 of P lie over columns of S that are in registers by now:
-                // the load that runs ahead covers columns up to c + 63, and c/2 + 15 < c + 32
-                t5_st16(tmem + lane_addr + s_col(g) + (c >> 1), pk);
+                t5_st16(my_s + (c >> 1), pk);
             };
-            t5_ld32(tmem + lane_addr + s_col(g), ra);
-#pragma unroll 1
-            for (int c = 0; c < T5O_BN; c += 64) {
-                t5_wait_ld();
-                t5_ld32(tmem + lane_addr + s_col(g) + c + 32, rb);
-                weights(ra, c);
-                t5_wait_ld();
-                if (c + 64 < T5O_BN) t5_ld32(tmem + lane_addr + s_col(g) + c + 64, ra);
-                weights(rb, c + 32);
-            }
+            weights(ra, 0);
+            weights(rb, 32);
             t5_wait_st();
             if (tracer) T5_EVENT(1 + g, tn, 14, j);
             t5_fence_before();
             t5_arrive(&p_full[g]);
         }
+        // the row sum is the two halves' sums
+        x_sum[g][half][row] = l;
+        asm volatile("bar.sync %0, 256;\n" ::"r"(1 + g) : "memory");
+        l += x_sum[g][half ^ 1][row];
         if (ok && t5_wait(&pv_done[g], (n_tiles - 1) & 1, &abort_flag, status, row_base)) {
             t5_fence_after();
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h0 + g) * T5_D;
+            bf16* orow = out + (static_cast<size_t>(row_base + row) * nq + h0 + g) * T5_D + half * 64;
 #pragma unroll 1
-            for (int c = 0; c < T5_D; c += 32) {
+            for (int c = 0; c < 64; c += 32) {
                 unsigned r[32];
-                t5_ld32(tmem + lane_addr + o_col(g) + c, r);
+                t5_ld32(my_o + c, r);
                 t5_wait_ld();
                 if (row < rows_here) {
 #pragma unroll
@@ -888,7 +904,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
         auto kern = paged_prefill_attention_tcgen05_online_kernel;
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        launch_pdl(kern, dim3(nq / 2, n_tiles), dim3(320), smem, s, q_map, kv_map, static_cast<bf16*>(out), tiles,
+        launch_pdl(kern, dim3(nq / 2, n_tiles), dim3(T5O_THREADS), smem, s, q_map, kv_map, static_cast<bf16*>(out), tiles,
                    entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv, page_size,
                    window, sl2, num_pages, status);
         return launch_status();
