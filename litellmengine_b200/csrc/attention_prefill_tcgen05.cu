@@ -443,15 +443,23 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
 
 // ---- one pass with a running reference maximum, two heads in turns -------------------------------
 // The same work in ONE pass over the keys, for the two query heads of a group that share a key/value
-// tile: 128 keys a tile, S = Q K^T for head 0 while the softmax threads of head 1 work and the
-// other way round, so the tensor pipe always has a product of one head to run while the other
-// head's weights are being made.  Per head TMEM holds S (128 columns of float32, the bfloat16 P
-// over its first 64) and O (128 columns).
+// tile (the kernel above stays for groups of odd size): 128 keys a tile, S = Q K^T of head 0 while
+// the softmax threads of head 1 work and the other way round, so the tensor pipe has a product of
+// one head to run while the other head's weights are being made.  Per head TMEM holds S (128
+// columns of float32) and O (128 columns); P (bfloat16) lies over S, 32 columns at column 0 and 32
+// at column 64, each over the columns of the thread that makes it.
 // The weights are P = exp2(S*scale*log2e - m) with a reference m per row that trails the running
 // maximum: m moves up only when the maximum has passed it by more than 8 (a factor 256, far
 // inside what bfloat16 and the float32 sums hold), and only then O and the row sum l are
 // multiplied by exp2(m_old - m_new) (the running-maximum form of src/ops/attention.cu:204-249 with
 // the correction made rare).  The result sum(P V) / sum(P) does not depend on which m was used.
+// Roles: warp 0 looks up pages and asks the copy engine for keys and values (rings of two tiles
+// each); one lane of warp 1 issues every product; then eight softmax warps per head, two threads
+// to a query row with 64 columns of S each.  What limited earlier forms, in the order found by
+// reading the SM clock inside the kernel (-DT5_TRACE): the order of CTAs (long tiles must start
+// first), one thread requesting the copies box by box (140 clocks a request), one thread per row in
+// the softmax; what is left is the chain S -> weights -> P V of one head, about 4,000 clocks a
+// tile against 2,050 of tensor work for both heads.
 #define T5O_BN 128
 #define T5O_HALF (T5O_BN * 64)                // elements of one 64-column half of a 128-key tile
 #define T5O_TILE (2 * T5O_HALF)
@@ -467,26 +475,6 @@ __device__ __forceinline__ void t5_st32(unsigned taddr, const unsigned (&r)[32])
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
-}
-
-// exp2 on the FMA pipe for a share of the weights (the special-function unit makes 16 a clock per
-// SM, which 2 x 128 x 128 exponentials per tile would saturate): x = n + f with n = round(x),
-// 2^f on [-0.5, 0.5] by a cubic (relative error 1e-4, far below bfloat16's 4e-3), n added to the
-// exponent field.  x is clamped at -125 (the result is then 2^-125, which rounds away in the sums).
-__device__ __forceinline__ float t5_ex2_poly(float x) {
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;                       // 1.5 * 2^23: the integer part lands in the low mantissa bits
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.05550357f, 0.24022652f);
-    p = fmaf(p, f, 0.69314720f);
-    p = fmaf(p, f, 1.0f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-#ifndef T5O_POLY_EVERY
-#define T5O_POLY_EVERY 0                                   // one weight in this many takes the polynomial (0: none)
-#endif
-__device__ __forceinline__ constexpr bool t5_use_poly(int i) {
-    return T5O_POLY_EVERY > 0 && (i % (T5O_POLY_EVERY > 0 ? T5O_POLY_EVERY : 1)) == T5O_POLY_EVERY - 1;
 }
 
 __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen05_online_kernel(
@@ -770,8 +758,7 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                     for (int i = 0; i < 32; i += 2) {
                         const float x0 = fmaf(__uint_as_float(r[i]), scale_log2e, -msub);
                         const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2e, -msub);
-                        const float p0 = t5_use_poly(i) ? t5_ex2_poly(x0) : t5_ex2(x0);
-                        const float p1 = t5_use_poly(i + 1) ? t5_ex2_poly(x1) : t5_ex2(x1);
+                        const float p0 = t5_ex2(x0), p1 = t5_ex2(x1);     // (a cubic on the FMA pipe for a share of them: measured slower)
                         l += p0 + p1;
                         pk[i >> 1] = t5_pack(p0, p1);
                     }
