@@ -278,6 +278,8 @@ def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, positions, tok
 
 def fast_attention_supported(d: int, group: int) -> bool:
     """Whether the tuned bfloat16 kernels (tensor-core prefill, split-key decode) take this shape."""
+    if d % 64 != 0:          # they are written for head sizes 64 and 128: do not compile them just to hear "no"
+        return False
     a = _fn("attention_decode", "llm_paged_decode_supported", [c_int, c_int])
     b = _fn("attention_prefill", "llm_paged_prefill_supported", [c_int])
     return bool(a(d, group)) and bool(b(d))
