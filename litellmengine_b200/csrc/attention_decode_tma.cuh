@@ -2,10 +2,10 @@
 // paged_decode_attention_kernel (attention_decode.cu) for page sizes 8, 16, 32 and 64.
 //
 // What changes is who moves the data.  There, every thread issues sixteen 16-byte cp.async per
-// tile and the memory-input queue is what the warps wait on.  Here one lane of a fifth warp issues
-// a handful of bulk tensor copies per tile (one box of [page_size rows x 64 columns] per page and
-// 64-column half, 128-byte swizzled by the copy engine), arms an mbarrier with the byte count and
-// runs up to STAGES-1 tiles ahead; the four compute warps wait on the tile's "full" barrier, do
+// tile and the memory-input queue is what the warps wait on.  Here a fifth warp asks for a tile
+// with one warp-wide bulk tensor copy (a lane per box of [page_size rows x 64 columns]: one per
+// page, 64-column half and K or V, 128-byte swizzled by the copy engine), arms an mbarrier with
+// the byte count and runs up to STAGES-1 tiles ahead; the four compute warps wait on the tile's "full" barrier, do
 // exactly the arithmetic of the cp.async kernel, and release the stage through its "empty"
 // barrier.  A page is a box, so the copy engine does the address arithmetic that 128 threads did.
 //
@@ -113,45 +113,56 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     __syncthreads();                                                 // the barriers exist
 
     if (warp == 4) {
-        // ---- producer: one lane feeds the copy engine ----
-        if (lane == 0) {
-            const int boxes = AD_BN / page_size;                      // pages per tile
-            const int last_logical = (k_end - 1) / page_size;
-            const unsigned tile_bytes = 2u * TILE * sizeof(bf16);
-            int issued = 0;
-            bool waited = false;
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % STAGES;
-                if (!waited && (it >= STAGES || k_origin + (it + 1) * AD_BN > pos)) {
-                    pdl_wait();                                       // the tile with this step's own row, or a stage to be reused
-                    waited = true;
-                }
-                if (it >= STAGES && !mbar_wait(&empty_bar[st], ((it / STAGES) - 1) & 1, &abort_flag, status, t)) break;
-                mbar_expect_tx(&full_bar[st], tile_bytes);
-                const int first_logical = (k_origin + it * AD_BN) / page_size;
-                for (int j = 0; j < boxes; ++j) {
-                    const int logical = min(first_logical + j, last_logical);
-                    int page = logical < table_stride ? __ldg(table + logical) : -1;
-                    if (page < 0 || page >= num_pages) {
-                        if (atomicCAS(status, 0, 4) == 0) status[1] = t;
-                        page = 0;                                     // any page keeps the byte count; the result is flagged
-                    }
-                    const int k_row = ((page * 2) * nkv + kvh) * page_size;
-                    const int v_row = ((page * 2 + 1) * nkv + kvh) * page_size;
-#pragma unroll
-                    for (int half = 0; half < D / 64; ++half) {
-                        tma_load_2d(k_s + st * TILE + half * (AD_BN * 64) + j * page_size * 64, &kv_map, half * 64, k_row,
-                                    &full_bar[st]);
-                        tma_load_2d(v_s + st * TILE + half * (AD_BN * 64) + j * page_size * 64, &kv_map, half * 64, v_row,
-                                    &full_bar[st]);
-                    }
-                }
-                issued = it + 1;
+        // ---- producer: every lane asks the copy engine for one box of the tile ----
+        // A tile is (pages per tile) x (64-column halves) x (K, V) boxes, at most 32: lane l takes
+        // box l, looks its page up one tile ahead, and the whole tile is requested by one warp-wide
+        // instruction.  (One lane doing this box by box, each with its own table read, spent more
+        // time per tile than the compute warps need for it.)
+        const int boxes = AD_BN / page_size;                          // pages per tile
+        constexpr int HALVES = D / 64;
+        const int n_ops = boxes * HALVES * 2;
+        const bool active = lane < n_ops;
+        const int box = lane % boxes, half = (lane / boxes) % HALVES, kv = lane / (boxes * HALVES);
+        const int last_logical = (k_end - 1) / page_size;
+        const unsigned tile_bytes = 2u * TILE * sizeof(bf16);
+        auto page_of = [&](int it) {                                  // this lane's page of tile `it` (checked)
+            if (!active || it >= n_tiles) return 0;
+            const int logical = min((k_origin + it * AD_BN) / page_size + box, last_logical);
+            int page = logical < table_stride ? __ldg(table + logical) : -1;
+            if (page < 0 || page >= num_pages) {
+                if (atomicCAS(status, 0, 4) == 0) status[1] = t;
+                page = 0;                                             // any page keeps the byte count; the result is flagged
             }
-            if (abort_flag) {                                         // let what is in flight land before the CTA goes away
-                for (int it = max(0, issued - STAGES); it < issued; ++it)
-                    for (int i = 0; i < TMA_WAIT_LIMIT && !mbar_try_wait(&full_bar[it % STAGES], (it / STAGES) & 1); ++i) {}
+            return page;
+        };
+        int issued = 0;
+        bool waited = false;
+        int next_page = page_of(0);
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it % STAGES;
+            const int my_page = next_page;
+            next_page = page_of(it + 1);
+            if (!waited && (it >= STAGES || k_origin + (it + 1) * AD_BN > pos)) {
+                pdl_wait();                                           // the tile with this step's own row, or a stage to be reused
+                waited = true;
             }
+            int go = 1;
+            if (lane == 0) {
+                if (it >= STAGES && !mbar_wait(&empty_bar[st], ((it / STAGES) - 1) & 1, &abort_flag, status, t)) go = 0;
+                if (go) mbar_expect_tx(&full_bar[st], tile_bytes);
+            }
+            go = __shfl_sync(0xffffffffu, go, 0);
+            if (!go) break;
+            if (active) {
+                const int row0 = ((my_page * 2 + kv) * nkv + kvh) * page_size;
+                tma_load_2d((kv ? v_s : k_s) + st * TILE + half * (AD_BN * 64) + box * page_size * 64, &kv_map, half * 64, row0,
+                            &full_bar[st]);
+            }
+            issued = it + 1;
+        }
+        if (lane == 0 && abort_flag) {                                // let what is in flight land before the CTA goes away
+            for (int it = max(0, issued - STAGES); it < issued; ++it)
+                for (int i = 0; i < TMA_WAIT_LIMIT && !mbar_try_wait(&full_bar[it % STAGES], (it / STAGES) & 1); ++i) {}
         }
         return;
     }
