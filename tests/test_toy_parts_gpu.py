@@ -1,6 +1,7 @@
 """The framework's generality, shown with toy parts that exist only in this file: a mixer with
 a state of its own (no pages), a windowed attention layer (a cache group that gives pages
-back), a layer that runs twice, and a layer that reads another stage's cache.  They are
+back), a layer that runs twice, a layer that reads another stage's cache, a feed-forward that
+routes tokens to experts, and a position encoding with a frequency table of its own.  They are
 registered, built and stepped here without a change to the framework's files, in every way of
 cutting, against plain code.  None of this is a model of anyone's."""
 from dataclasses import dataclass
@@ -177,3 +178,166 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype, tmp_path):
         runner.release(s)
     finally:
         unregister_toys()
+
+
+# ---- a feed-forward with routing and another position encoding --------------------------------
+E_EXPERTS, E_INTER = 3, 32
+
+
+def register_routed_toys():
+    from litellmengine_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelPlan, NormSpec, PositionSpec,
+                                           StageSpec, register_architecture)
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.parts import register_feed_forward, register_position
+    from litellmengine_b200.weights import ParamSpec
+
+    @register_position("toy_linear_frequencies")
+    class LinearFrequencies:
+        """A rotation whose frequencies fall off linearly instead of geometrically:
+        inv_freq[i] = (1 - i / (rotary_dim / 2)) / theta.  The mixer's kernel only wants the table."""
+
+        def __init__(self, spec, head_dim, device):
+            self.rotary_dim = spec.rotary_dim or head_dim
+            half = self.rotary_dim // 2
+            self.inv_freq = ((1.0 - torch.arange(half, dtype=torch.float32) / half) / spec.theta).to(device)
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts:
+        """Each token goes to the expert with the largest router logit (logits in float32, ties to
+        the lowest index) and gets that expert's SwiGLU, scaled by the softmax weight of the choice."""
+
+        def __init__(self, spec, hidden_size, compute_dtype, device):
+            self.hidden, self.dtype = hidden_size, compute_dtype
+            self.inter = spec.intermediate_size
+            self.router = self.gate_up = self.down = None
+
+        def parameters(self) -> Dict[str, ParamSpec]:
+            out = {"router.weight": ParamSpec((E_EXPERTS, self.hidden))}
+            for e in range(E_EXPERTS):
+                out[f"experts.{e}.gate_proj.weight"] = ParamSpec((self.inter, self.hidden))
+                out[f"experts.{e}.up_proj.weight"] = ParamSpec((self.inter, self.hidden))
+                out[f"experts.{e}.down_proj.weight"] = ParamSpec((self.hidden, self.inter))
+            return out
+
+        def load(self, t):
+            self.router = t["router.weight"].float()
+            self.gate_up = [torch.cat([t[f"experts.{e}.gate_proj.weight"], t[f"experts.{e}.up_proj.weight"]]).contiguous()
+                            for e in range(E_EXPERTS)]
+            self.down = [t[f"experts.{e}.down_proj.weight"].contiguous() for e in range(E_EXPERTS)]
+
+        def forward(self, x, partials_ok=False):
+            logits = x.float() @ self.router.T                                   # router logits in 32-bit
+            prob = torch.softmax(logits, dim=-1)
+            choice = torch.argmax(logits, dim=-1)
+            out = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+            for e in range(E_EXPERTS):
+                idx = torch.nonzero(choice == e).flatten()
+                if idx.numel() == 0:
+                    continue
+                xe = x[idx].contiguous()
+                y = ops.linear(ops.silu_and_mul(ops.linear(xe, self.gate_up[e], out_dtype=self.dtype)), self.down[e],
+                               out_dtype=torch.float32)
+                out[idx] = y * prob[idx, e][:, None]
+            return out
+
+    @register_architecture("ToyRoutedForCausalLM")
+    @dataclass(frozen=True)
+    class ToyRouted:
+        @classmethod
+        def from_dict(cls, d):
+            return cls()
+
+        def to_dict(self):
+            return {"architectures": ["ToyRoutedForCausalLM"]}
+
+        def plan(self):
+            norm = NormSpec("rmsnorm", EPS)
+            pos = PositionSpec("toy_linear_frequencies", theta=40.0, rotary_dim=D)
+            attn = MixerSpec("attention", NQ, NKV, D, qk_norm=norm, position=pos)
+            routed = FeedForwardSpec("toy_top1_experts", intermediate_size=E_INTER)
+            dense = FeedForwardSpec("swiglu", intermediate_size=INTER)
+            blocks = (BlockSpec("pre_norm", attn, routed, norm, norm, weight_prefix="toy.0"),
+                      BlockSpec("pre_norm", attn, dense, norm, norm, weight_prefix="toy.1"))
+            return ModelPlan(H, VOCAB, blocks, (StageSpec(0), StageSpec(1), StageSpec(0)), norm, tie_word_embeddings=True,
+                             max_position=512, embedding_name="toy.embed", final_norm_name="toy.norm",
+                             output_name="toy.head")
+    return ToyRouted
+
+
+def plain_routed_logits(ids, w):
+    """Plain code for the routed toy, in double precision."""
+    w = {k: v.double() for k, v in w.items()}
+    T = len(ids)
+    pos = torch.arange(T, dtype=torch.float64)
+    half = D // 2
+    inv = ((1.0 - torch.arange(half, dtype=torch.float32) / half) / torch.tensor(40.0)).double()   # the table is float32
+    ang = (pos[:, None].float() * inv.float()[None, :]).double()                                    # and so is the angle
+
+    def rotate(x):                                                     # [T, heads, D]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+
+    def attention(x, p):
+        q = (x @ w[f"{p}.q_proj.weight"].T).view(T, NQ, D)
+        k = (x @ w[f"{p}.k_proj.weight"].T).view(T, NKV, D)
+        v = (x @ w[f"{p}.v_proj.weight"].T).view(T, NKV, D)
+        q = rotate(pq.rms_norm(q, w[f"{p}.q_norm.weight"], EPS))
+        k = rotate(pq.rms_norm(k, w[f"{p}.k_norm.weight"], EPS))
+        return pq.causal_attention(q, k, v).reshape(T, -1) @ w[f"{p}.o_proj.weight"].T
+
+    def routed(y, p):
+        logits = y @ w[f"{p}.router.weight"].T
+        prob = torch.softmax(logits, dim=-1)
+        choice = torch.argmax(logits, dim=-1)
+        out = torch.zeros_like(y)
+        for t in range(T):
+            e = int(choice[t])
+            out[t] = pq.swiglu(y[t:t + 1], w, f"{p}.experts.{e}")[0] * prob[t, e]
+        return out
+
+    h = pq.embedding(torch.as_tensor(ids), w["toy.embed"]).double()
+    for p, ffn in (("toy.0", "routed"), ("toy.1", "dense"), ("toy.0", "routed")):
+        h = h + attention(pq.rms_norm(h, w[f"{p}.input_layernorm.weight"], EPS), f"{p}.self_attn")
+        y = pq.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], EPS)
+        h = h + (routed(y, f"{p}.mlp") if ffn == "routed" else pq.swiglu(y, w, f"{p}.mlp"))
+    return (pq.rms_norm(h, w["toy.norm"], EPS) @ w["toy.embed"].T).float()
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward that routes each token to one of three experts and a position encoding with a
+    frequency table of its own, registered here, beside the framework's attention and dense
+    feed-forward, in a model whose first layer runs twice.  Float32 (a routing decision is a
+    discontinuity: under bfloat16 rounding a near-tie may fall the other way)."""
+    from litellmengine_b200.config import unregister_architecture
+    from litellmengine_b200.engine import ModelRunner
+    from litellmengine_b200.parts import unregister
+    from litellmengine_b200.weights import DictSource, SafetensorsSource, write_random_model
+    Toy = register_routed_toys()
+    try:
+        folder = write_random_model(Toy(), str(tmp_path / "routed"), seed=9, dtype=torch.float32)
+        src = SafetensorsSource(folder)
+        w = {n: src.get(n).float() for n in src.names()}
+        assert "toy.0.mlp.experts.2.down_proj.weight" in w and "toy.1.mlp.gate_proj.weight" in w
+        w = {k: (v * 4.0 if k.endswith("q_norm.weight") else v * 30.0 if k.endswith("router.weight") else v)
+             for k, v in w.items()}                                    # sharp attention, decided routing
+        rng = np.random.RandomState(1)
+        reqs = {f"r{i}": [int(t) for t in rng.randint(0, VOCAB, n)] for i, n in enumerate((2, 37, 64, 21))}
+        ref = {r: plain_routed_logits(t, w).numpy() for r, t in reqs.items()}
+        used = set()
+        for t in reqs.values():                                        # the test is about routing: all experts must get tokens
+            y = pq.rms_norm(pq.embedding(torch.as_tensor(t), w["toy.embed"]).float(), w["toy.0.post_attention_layernorm.weight"], EPS)
+            used |= set(torch.argmax(y @ w["toy.0.mlp.router.weight"].T, dim=-1).tolist())
+        assert used == {0, 1, 2}
+        for what, steps in (("whole", rh.trace_whole(reqs)), ("tail", rh.trace_tail_decode(reqs, 32)),
+                            ("portions", rh.trace_portions(reqs, 1)), ("mixed", rh.trace_mixed(reqs, 2, 4))):
+            runner = ModelRunner.from_config(Toy(), dtype="float32", device=DEV, page_size=4, max_requests=4,
+                                             max_tokens_per_step=128, max_total_tokens=rh.peak_tokens(steps, 4),
+                                             source=DictSource(dict(w)))
+            assert not runner.use_graphs                               # the routed part reads its choices on the host
+            got = rh.run_trace(runner, steps)
+            rh.assert_rows_match(got, ref, rh.FP32_TOL, f"routed toy {what}")
+    finally:
+        unregister("feed_forward", "toy_top1_experts")
+        unregister("position", "toy_linear_frequencies")
+        unregister_architecture("ToyRoutedForCausalLM")
