@@ -23,7 +23,7 @@ class RequestStatus(enum.Enum):
     FINISHED = "finished"
 
 
-@dataclass
+@dataclass(eq=False)            # a request is itself: lists of requests are searched by identity
 class GenerationRequest:
     request_id: int
     input_ids: List[int]

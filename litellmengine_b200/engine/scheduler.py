@@ -107,7 +107,7 @@ class Scheduler:
         queue = [self.running[k] for k in order]          # decoders first, each kind oldest first
         while i < len(queue):
             req = queue[i]
-            if req not in self.running or req.remain_len <= 0:   # preempted below, or only awaiting its last token
+            if req.status is not RequestStatus.RUNNING or req.remain_len <= 0:   # preempted below, or only awaiting its last token
                 i += 1
                 continue
             if budget <= 0:
@@ -126,7 +126,7 @@ class Scheduler:
                     need = self.cache.reserve(need, p.request.slot, p.request.cached_len + p.num_tokens)
                 if victim is req:
                     break
-            if req not in self.running:
+            if req.status is not RequestStatus.RUNNING:
                 i += 1
                 continue
             need = got
