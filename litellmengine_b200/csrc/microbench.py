@@ -100,7 +100,7 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--out-dtype", default="bfloat16")
-    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05"],
+    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "stream"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
     ap.add_argument("--chain", type=int, default=0,
                     help="linear: time CHAIN launches back to back, each over weights of its own (together larger "
@@ -173,12 +173,15 @@ def main():
             fn = lambda: torch.mm(x, w.t(), out_dtype=od) if od != x.dtype else torch.mm(x, w.t())
         elif args.impl == "own":
             fn = lambda: ops.linear_skinny(x, w, od)
+        elif args.impl == "stream":
+            fn = lambda: ops.linear_stream(x, w, od)
         else:
             fn = lambda: ops.linear(x, w, out_dtype=od)
         if args.chain:
             ws = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(args.chain)]
             one = {"library": lambda wi: torch.mm(x, wi.t(), out_dtype=od) if od != x.dtype else torch.mm(x, wi.t()),
-                   "own": lambda wi: ops.linear_skinny(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))
+                   "own": lambda wi: ops.linear_skinny(x, wi, od),
+                   "stream": lambda wi: ops.linear_stream(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
                 for wi in ws:

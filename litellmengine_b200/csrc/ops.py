@@ -468,6 +468,50 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
+STREAM_MAX_ROWS = 128    # rows up to which `linear` may take the tcgen05 weight-streaming kernel
+_STREAM_POLICY = os.environ.get("LLM_STREAM", "on")     # on | off
+_stream_status: Dict[str, torch.Tensor] = {}
+
+
+def stream_status(device) -> torch.Tensor:
+    """The status word of the tcgen05 streaming product (code 7: a bounded wait ran out)."""
+    key = str(device)
+    t = _stream_status.get(key)
+    if t is None:
+        t = _stream_status[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return t
+
+
+def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
+                  out: Optional[torch.Tensor] = None, partials_ok: bool = False):
+    """x [T <= 128, K] @ weight[N, K]^T with the tcgen05 weight-streaming kernel (bfloat16 operands
+    fetched by TMA, float32 accumulation in tensor memory, float32 or bfloat16 result).  With
+    `partials_ok` a product that is cut along K comes back as a `PartialSum`."""
+    _dev(x, weight, out)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError("the streaming product takes bfloat16 operands")
+    T, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError("x and weight disagree on K")
+    global launch_count
+    f = _fn("gemm_stream_tcgen05", "llm_linear_stream",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    slices = _fn("gemm_stream_tcgen05", "llm_linear_stream_slices", [c_int, c_int, c_int])(T, N, K)
+    status = stream_status(x.device)
+    if partials_ok and slices > 1 and out is None:
+        parts = torch.empty((slices, T, N), dtype=torch.float32, device=x.device)
+        _check(f(_ptr(x), _ptr(weight), None, 0, _ptr(parts), parts.numel(), T, N, K, 1, _ptr(status), _stream()), "linear_stream")
+        return PartialSum(parts, None if out_dtype == torch.float32 else out_dtype)
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    scratch = skinny_scratch(x.device, slices * T * N if slices > 1 else 0)
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
+             T, N, K, 0, _ptr(status), _stream()), "linear_stream")
+    launch_count += 1 if slices > 1 else 0        # the kernel that adds the slices
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            partials_ok: bool = False):
     """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's
@@ -483,6 +527,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
             and x.shape[1] % 8 == 0 and (_SKINNY_POLICY == "all" or (
                 _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
         return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
+            and x.shape[1] % 8 == 0 and _STREAM_POLICY != "off"):
+        return linear_stream(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
         want = out_dtype or x.dtype

@@ -464,6 +464,26 @@ def test_skinny_product(M, N, K, out_dtype):
     close(got, lib, 2e-5 if out_dtype == "float32" else 6e-3)      # and against the library product
 
 
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,N,K", [(17, 16, 512), (33, 100, 520), (64, 331, 80), (20, 48, 4096), (128, 1000, 1544),
+                                   (65, 17, 8), (64, 6144, 4096), (32, 4096, 12288), (100, 300, 64)])
+def test_stream_tcgen05_product(T, N, K, out_dtype):
+    """The tcgen05 weight-streaming product for 17..128 rows against float64, at sizes that are no
+    multiple of its tiles (N of 128, K of 64, T of 32/64/128), in both ways of cutting the work
+    (whole k-splits per tile; one even run of items per CTA) and with the partial sums left to
+    the caller."""
+    torch.manual_seed(T * 1000 + N)
+    x = torch.randn(T, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    got = ops().linear_stream(x.to(DEV), w.to(DEV), DT[out_dtype])
+    assert got.dtype == DT[out_dtype] and got.shape == (T, N)
+    close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    parts = ops().linear_stream(x.to(DEV), w.to(DEV), DT[out_dtype], partials_ok=True)
+    close(ops().as_tensor(parts), ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    assert ops().stream_status(DEV).tolist() == [0, 0]
+
+
 # ---- the tcgen05 / TMEM / TMA prompt-portion attention kernel ------------------------------------
 @pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 64), (3, 1, 8), (6, 2, 64), (4, 2, 32), (5, 5, 16)])
 def test_prefill_tcgen05_kernel(nq, nkv, page):
