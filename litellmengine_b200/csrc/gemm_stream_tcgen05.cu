@@ -17,6 +17,12 @@
 // feature tile; whole k-splits per tile when they fill the CTA slots well, otherwise one even run
 // of items per CTA, with float32 partial sums in slices added by a second kernel or the consumer.
 // Every mbarrier wait is bounded; a wait that runs out sets status code 7 and the CTA winds down.
+// Measured (B200, chain of launches over weights larger than L2): 24576 x 4096 weights take 54 / 67 /
+// 98 us for 32 / 64 / 128 rows against 37 / 40 / 40 us for the library's kernels: the time follows
+// the number of 128-byte rows the copy engine is asked for per stage (128 + NT), not the bytes, and
+// asking for the same rows in four boxes from four lanes changes nothing.  The engine therefore
+// keeps the library for these row counts unless LLM_STREAM=on; the next form of this kernel fills
+// the same swizzled tiles with cp.async in 512-byte runs, as the kernel for up to 16 rows does.
 // The reference calls cublasSgemm for every product (src/layers/linear.cu:169-215).
 #include "common.cuh"
 #include <cuda.h>

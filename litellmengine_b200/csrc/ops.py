@@ -469,7 +469,10 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 
 
 STREAM_MAX_ROWS = 128    # rows up to which `linear` may take the tcgen05 weight-streaming kernel
-_STREAM_POLICY = os.environ.get("LLM_STREAM", "on")     # on | off
+# off | on.  Off by default: fed by TMA in 128-byte rows (the widest a 128-byte-swizzled box can be)
+# the kernel reaches 3.1-4.0 TB/s where the library's kernels for these shapes reach 4.5-5.5 (its time
+# grows with the rows requested per stage, 128 of weights + the token tile, not with the bytes).
+_STREAM_POLICY = os.environ.get("LLM_STREAM", "off")
 _stream_status: Dict[str, torch.Tensor] = {}
 
 
@@ -528,7 +531,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
                 _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
         return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
-            and x.shape[1] % 8 == 0 and _STREAM_POLICY != "off"):
+            and x.shape[1] % 8 == 0 and _STREAM_POLICY == "on"):
         return linear_stream(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
