@@ -102,6 +102,7 @@ def main():
     ap.add_argument("--out-dtype", default="bfloat16")
     ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "stream"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
+    ap.add_argument("--tiled", action="store_true", help="linear --impl own: over a tile-by-tile copy of the weights")
     ap.add_argument("--chain", type=int, default=0,
                     help="linear: time CHAIN launches back to back, each over weights of its own (together larger "
                          "than L2), as one CUDA graph; the figure is the time per launch inside a stream of kernels")
@@ -169,6 +170,8 @@ def main():
         x = torch.randn(args.tokens, args.k, device=dev, dtype=torch.bfloat16)
         w = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02
         od = torch.float32 if args.out_dtype == "float32" else torch.bfloat16
+        if args.tiled:
+            ops.prepare_streaming(w)
         if args.impl == "library":
             fn = lambda: torch.mm(x, w.t(), out_dtype=od) if od != x.dtype else torch.mm(x, w.t())
         elif args.impl == "own":
@@ -179,6 +182,9 @@ def main():
             fn = lambda: ops.linear(x, w, out_dtype=od)
         if args.chain:
             ws = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(args.chain)]
+            if args.tiled:
+                for wi in ws:
+                    ops.prepare_streaming(wi)
             one = {"library": lambda wi: torch.mm(x, wi.t(), out_dtype=od) if od != x.dtype else torch.mm(x, wi.t()),
                    "own": lambda wi: ops.linear_skinny(x, wi, od),
                    "stream": lambda wi: ops.linear_stream(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from ctypes import c_float, c_int, c_int32, c_longlong, c_uint32, c_uint64, c_void_p
 from typing import Dict, Optional
 
@@ -439,6 +440,41 @@ SKINNY_MAX_ROWS = 16     # rows up to which `linear` may take the engine's own s
 _SKINNY_POLICY = os.environ.get("LLM_SKINNY", "all")     # all | auto | off: which products of few rows take it
 
 
+# ---- weights stored tile by tile for the streaming product ----------------------------------
+_TILED_POLICY = os.environ.get("LLM_TILED", "on")     # on | off: keep a tiled copy of decode weights
+_tiled: Dict[int, torch.Tensor] = {}                   # weight.data_ptr() -> its tiled copy
+TILE_ROWS, TILE_K = 64, 256
+
+
+def tile_weight(weight: torch.Tensor) -> torch.Tensor:
+    """bfloat16 [N, K] -> the same values as [N/64 tiles, K/256 steps] blocks of 64 x 256 in the
+    order the streaming kernel keeps a stage in shared memory (16-byte chunk c of row r at chunk
+    position c ^ (r % 8)), zero-padded at the edges: a stage is then one contiguous 32 KB."""
+    N, K = weight.shape
+    tn, nk = -(-N // TILE_ROWS), -(-K // TILE_K)
+    padded = torch.zeros((tn * TILE_ROWS, nk * TILE_K), dtype=weight.dtype, device=weight.device)
+    padded[:N, :K] = weight
+    v = padded.view(tn, TILE_ROWS, nk, TILE_K // 8, 8)
+    r = torch.arange(TILE_ROWS, device=weight.device)[:, None]
+    p = torch.arange(TILE_K // 8, device=weight.device)[None, :]
+    src = (p & ~7) | ((p & 7) ^ (r & 7))                                  # the chunk that lands at position p of row r
+    idx = src[None, :, None, :, None].expand(tn, TILE_ROWS, nk, TILE_K // 8, 8)
+    return torch.gather(v, 3, idx).permute(0, 2, 1, 3, 4).contiguous().view(tn, nk, TILE_ROWS * TILE_K)
+
+
+def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
+    """Keep a tiled copy of a bfloat16 weight for decode steps of up to 8 tokens (twice the
+    memory for that weight; `LLM_TILED=off` keeps one copy).  The copy lives as long as the weight."""
+    if (weight is None or _TILED_POLICY == "off" or not weight.is_cuda or weight.dtype != torch.bfloat16
+            or weight.dim() != 2 or weight.shape[1] % 8 != 0):
+        return
+    key = weight.data_ptr()
+    if key in _tiled:
+        return
+    _tiled[key] = tile_weight(weight)
+    weakref.finalize(weight, _tiled.pop, key, None)
+
+
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                   out: Optional[torch.Tensor] = None, partials_ok: bool = False):
     """x [M <= 16, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16
@@ -452,8 +488,15 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     if weight.shape[1] != K:
         raise KernelError("x and weight disagree on K")
     global launch_count
-    f = _fn("gemm_skinny", "llm_linear_skinny",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    tiled = _tiled.get(weight.data_ptr()) if M <= 8 else None
+    if tiled is not None:
+        g = _fn("gemm_skinny", "llm_linear_skinny_tiled",
+                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        st = stream_status(x.device)
+        f = lambda xp, wp, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, _ptr(tiled), yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
+    else:
+        f = _fn("gemm_skinny", "llm_linear_skinny",
+                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
     splits = _fn("gemm_skinny", "llm_linear_skinny_splits", [c_int, c_int, c_int])(M, N, K)
     if partials_ok and splits > 1 and out is None:
         parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)

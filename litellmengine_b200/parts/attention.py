@@ -67,6 +67,8 @@ class AttentionMixer:
         dt = torch.float32 if any(x.dtype == torch.float32 for x in parts) else parts[0].dtype
         self.w_qkv = torch.cat([x.to(dt) for x in parts], dim=0).contiguous()
         self.w_o = t["o_proj.weight"].contiguous()
+        ops.prepare_streaming(self.w_qkv)           # a tiled copy for decode steps (bfloat16 on a GPU only)
+        ops.prepare_streaming(self.w_o)
         if self.q_norm is not None:
             self.q_norm.load({"weight": t["q_norm.weight"]})
         if self.k_norm is not None:

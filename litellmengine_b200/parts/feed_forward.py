@@ -35,6 +35,8 @@ class SwiGLU:
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = t["down_proj.weight"].contiguous()
+        ops.prepare_streaming(self.w_gate_up)       # a tiled copy for decode steps (bfloat16 on a GPU only)
+        ops.prepare_streaming(self.w_down)
 
     supports_partials = True   # forward(x, partials_ok=True) may return an ops.PartialSum
 

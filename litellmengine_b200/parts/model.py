@@ -65,6 +65,7 @@ class Model:
             block.load({n: get(f"{spec.weight_prefix}.{n}") for n in block.parameters()})
         self.final_norm.load({"weight": get(p.final_norm_name)})
         self.output = self.embedding if p.output_name in aliased else get(p.output_name).contiguous()
+        ops.prepare_streaming(self.output)          # a tiled copy of the output head for decode steps
 
     def stage_needs(self) -> list:
         needs = []

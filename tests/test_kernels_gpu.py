@@ -465,6 +465,32 @@ def test_skinny_product(M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (7, 48, 4096), (8, 1000, 1544),
+                                   (5, 17, 8), (8, 6144, 4096), (2, 4096, 12288)])
+def test_skinny_product_over_tiled_weights(M, N, K, out_dtype):
+    """The same product reading a copy of the weights stored tile by tile (one bulk copy per
+    stage): same sums as over the plain layout, at sizes with ragged edge tiles."""
+    torch.manual_seed(M * 1000 + N + 1)
+    x = torch.randn(M, K).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().T
+    plain = ops().linear_skinny(x, w, DT[out_dtype])
+    ops().prepare_streaming(w)
+    assert w.data_ptr() in ops()._tiled
+    got = ops().linear_skinny(x, w, DT[out_dtype])
+    close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    assert torch.equal(got, plain)                          # same order of additions: bit for bit
+    parts = ops().linear_skinny(x, w, DT[out_dtype], partials_ok=True)
+    close(ops().as_tensor(parts), ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    assert ops().stream_status(DEV).tolist() == [0, 0]
+    key = w.data_ptr()
+    del w, got, plain, parts
+    import gc
+    gc.collect()
+    assert key not in ops()._tiled                          # the copy went with its weight
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,N,K", [(17, 16, 512), (33, 100, 520), (64, 331, 80), (20, 48, 4096), (128, 1000, 1544),
                                    (65, 17, 8), (64, 6144, 4096), (32, 4096, 12288), (100, 300, 64)])
 def test_stream_tcgen05_product(T, N, K, out_dtype):
