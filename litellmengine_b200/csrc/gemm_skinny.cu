@@ -174,8 +174,10 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
 
 // ---- the same for up to 8 tokens over weights stored tile by tile ---------------------------------
 // `w_tiled` holds the weights as the kernel wants them in shared memory: [feature tile][k-step]
-// blocks of 64 x 256 values (32 KB), each block already in the XOR-swizzled order of gs_at<256>,
-// zero-padded at the edges.  A stage of weights is then ONE contiguous 32 KB piece of memory,
+// blocks of 64 x 256 values (32 KB), each block four sub-tiles of [64 rows][64 k-values] with 128-byte
+// rows whose 16-byte chunks are XOR-swizzled by the row (chunk c of row r at position c ^ (r % 8):
+// the layout the copy engine's 128-byte swizzle writes and tcgen05 reads as a K-major operand, so
+// the same copy also serves gemm_stream_tcgen05.cu), zero-padded at the edges.  A stage of weights is then ONE contiguous 32 KB piece of memory,
 // fetched by one bulk copy (cp.async.bulk) of one thread instead of 2,048 sixteen-byte copies
 // of 128 threads, and DRAM sees whole pages instead of 512-byte runs 8 KB apart (measured with
 // the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for this kernel's strided
@@ -191,6 +193,11 @@ __device__ __forceinline__ bool gs_try_wait(unsigned long long* bar, unsigned pa
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(ok) : "r"(gs_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
+}
+
+// 16-byte chunk `chunk` (of 32) of row `row` in a [4 sub-tiles][64 rows][64 k-values] block.
+__device__ __forceinline__ bf16* gs_at_tiled(bf16* base, int row, int chunk) {
+    return base + (chunk >> 3) * (GS_ROWS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
 template <typename TO>
@@ -281,8 +288,8 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
 #pragma unroll
         for (int kp = 0; kp < GS_BK / 32; ++kp) {
             unsigned a0[4], a1[4], b[4];
-            gs_ldmatrix_x4(a0, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
-            gs_ldmatrix_x4(a1, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
+            gs_ldmatrix_x4(a0, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
+            gs_ldmatrix_x4(a1, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
             gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, (lane & 7), kp * 4 + (lane >> 3)));
             gs_mma(acc, a0, b[0], b[1]);
             gs_mma(acc, a1, b[2], b[3]);

@@ -447,19 +447,21 @@ TILE_ROWS, TILE_K = 64, 256
 
 
 def tile_weight(weight: torch.Tensor) -> torch.Tensor:
-    """bfloat16 [N, K] -> the same values as [N/64 tiles, K/256 steps] blocks of 64 x 256 in the
-    order the streaming kernel keeps a stage in shared memory (16-byte chunk c of row r at chunk
-    position c ^ (r % 8)), zero-padded at the edges: a stage is then one contiguous 32 KB."""
+    """bfloat16 [N, K] -> the same values as [N/64 tiles, K/256 steps] blocks of 32 KB, each four
+    sub-tiles of [64 rows][64 k-values] with 128-byte rows whose 16-byte chunks are XOR-swizzled by
+    the row (chunk c of row r at position c ^ (r % 8)), zero-padded at the edges.  A stage of the
+    streaming product for up to 8 tokens is one block; a K-major tcgen05 operand of 128 rows x 64
+    k-values is two sub-tiles."""
     N, K = weight.shape
     tn, nk = -(-N // TILE_ROWS), -(-K // TILE_K)
     padded = torch.zeros((tn * TILE_ROWS, nk * TILE_K), dtype=weight.dtype, device=weight.device)
     padded[:N, :K] = weight
-    v = padded.view(tn, TILE_ROWS, nk, TILE_K // 8, 8)
+    v = padded.view(tn, TILE_ROWS, nk, TILE_K // 64, 8, 8)               # [tile, row, step, sub, chunk, 8 values]
     r = torch.arange(TILE_ROWS, device=weight.device)[:, None]
-    p = torch.arange(TILE_K // 8, device=weight.device)[None, :]
-    src = (p & ~7) | ((p & 7) ^ (r & 7))                                  # the chunk that lands at position p of row r
-    idx = src[None, :, None, :, None].expand(tn, TILE_ROWS, nk, TILE_K // 8, 8)
-    return torch.gather(v, 3, idx).permute(0, 2, 1, 3, 4).contiguous().view(tn, nk, TILE_ROWS * TILE_K)
+    p = torch.arange(8, device=weight.device)[None, :]
+    src = p ^ (r & 7)                                                     # the chunk that lands at position p of row r
+    idx = src[None, :, None, None, :, None].expand(tn, TILE_ROWS, nk, TILE_K // 64, 8, 8)
+    return torch.gather(v, 4, idx).permute(0, 2, 3, 1, 4, 5).contiguous().view(tn, nk, TILE_ROWS * TILE_K)
 
 
 def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
