@@ -6,9 +6,13 @@
 // 16 rows (gemm_skinny.cu), with the roles swapped for tcgen05: a tile of 128 output features of
 // w is the M = 128 operand A, the tokens are the N operand B (padded to NT = 32, 64 or 128 by the
 // copy engine's zero fill), and the accumulator D[128 features, NT tokens] lives in tensor memory.
-//   * warp 0, one lane: TMA producer.  Per stage one box of w [128 features x 64 k-values] and one
-//     of x [NT tokens x 64 k-values], 128-byte swizzled; w does not depend on the kernel before this
-//     one, so its first stages are requested before griddepcontrol.wait, x after it.
+//   * warp 0, one lane: producer.  The weights come from the copy stored tile by tile (ops.tile_weight:
+//     [N/64][K/256] blocks of four [64 rows][64 k-values] sub-tiles in the 128-byte-swizzled K-major
+//     order): a stage's operand A, 128 features x 64 k-values, is two contiguous 8 KB sub-tiles, each
+//     one cp.async.bulk.  (Fetched by TMA boxes from the plain [N, K] layout the same kernel was bound
+//     by DRAM's dislike of 128-byte pieces 8 KB apart: 54-98 us where the library takes 37-40.)  The
+//     tokens x [NT x 64 k-values] come by one TMA box per stage.  w does not depend on the kernel
+//     before this one, so its first stages are requested before griddepcontrol.wait, x after it.
 //   * warp 1, one lane: issues tcgen05.mma (M 128 x N NT x K 16, four per stage) and owns the TMEM
 //     allocation (two accumulators of NT columns, so that the epilogue of one segment runs while
 //     the next segment's products are issued).
@@ -17,12 +21,15 @@
 // feature tile; whole k-splits per tile when they fill the CTA slots well, otherwise one even run
 // of items per CTA, with float32 partial sums in slices added by a second kernel or the consumer.
 // Every mbarrier wait is bounded; a wait that runs out sets status code 7 and the CTA winds down.
-// Measured (B200, chain of launches over weights larger than L2): 24576 x 4096 weights take 54 / 67 /
-// 98 us for 32 / 64 / 128 rows against 37 / 40 / 40 us for the library's kernels: the time follows
-// the number of 128-byte rows the copy engine is asked for per stage (128 + NT), not the bytes, and
-// asking for the same rows in four boxes from four lanes changes nothing.  The engine therefore
-// keeps the library for these row counts unless LLM_STREAM=on; the next form of this kernel fills
-// the same swizzled tiles with cp.async in 512-byte runs, as the kernel for up to 16 rows does.
+// Measured (B200, chain of launches over weights larger than L2): 24576 x 4096 weights take 52 / 68 /
+// 100 us for 32 / 64 / 128 rows against 37 / 40 / 40 us for the library's kernels, whichever way the
+// operands are fetched (TMA boxes from the plain layout, bulk copies of the tiled copy; tokens by TMA
+// or cp.async).  Taking the products out changes nothing; taking the epilogue's stores out gives 42 /
+// 58 us: a thread writes its feature's NT sums one 4-byte store at a time at the end of the CTA's
+// life, and the tokens' tile is read again from L2 for every 128 features (as many bytes as the
+// weights at 128 rows).  The engine therefore keeps the library for these row counts unless
+// LLM_STREAM=on; what this kernel needs next is 256 features per token tile and an epilogue that
+// goes through shared memory.
 // The reference calls cublasSgemm for every product (src/layers/linear.cu:169-215).
 #include "common.cuh"
 #include <cuda.h>
@@ -30,7 +37,7 @@
 #define GT_BM 128                 // output features per tile (rows of A)
 #define GT_BK 64                  // k-values per stage: one 128-byte swizzled row
 #define GT_WAIT_LIMIT 400000
-#define GT_THREADS 192
+#define GT_THREADS 320                // producer warp, issuing warp, 4 epilogue warps, 4 warps that fetch the tokens
 
 __device__ __forceinline__ unsigned gt_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void gt_mbar_init(unsigned long long* bar, int count) {
@@ -110,7 +117,7 @@ __host__ __device__ __forceinline__ long long gt_cta_of(long long item, long lon
 // (0: one even run of all items per CTA).
 template <int NT, int STAGES, typename TO>
 __global__ void __launch_bounds__(GT_THREADS) linear_stream_tcgen05_kernel(
-    const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, TO* __restrict__ y,
+    const bf16* __restrict__ w_tiled, const bf16* __restrict__ x, TO* __restrict__ y,
     float* __restrict__ partial, int T, int N, int K, int slices, int per_tile, int32_t* __restrict__ status) {
     pdl_invite();
     constexpr int A_ELEMS = GT_BM * GT_BK, B_ELEMS = NT * GT_BK;
@@ -139,7 +146,7 @@ __global__ void __launch_bounds__(GT_THREADS) linear_stream_tcgen05_kernel(
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) { gt_mbar_init(&full[s], 1); gt_mbar_init(&empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { gt_mbar_init(&full[s], 1 + 128); gt_mbar_init(&empty[s], 1); }   // weights + 128 token fetchers
         for (int s = 0; s < 2; ++s) { gt_mbar_init(&acc_full[s], 1); gt_mbar_init(&acc_empty[s], 128); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -155,32 +162,69 @@ __global__ void __launch_bounds__(GT_THREADS) linear_stream_tcgen05_kernel(
     if (warp == 0) {
         // ---- producer ----
         if (lane == 0) {
-            constexpr unsigned A_BYTES = A_ELEMS * sizeof(bf16), B_BYTES = B_ELEMS * sizeof(bf16);
-            auto load_w = [&](int i) {
+            constexpr unsigned A_BYTES = A_ELEMS * sizeof(bf16);
+            const int tiles64 = (N + 63) / 64;
+            const long long nk256 = (K + 255) / 256;
+            auto load_w = [&](int i) {                            // two sub-tiles: features 0..63 and 64..127 of the tile
                 const long long item = begin + i;
-                gt_expect_tx(&full[i % STAGES], A_BYTES);
-                gt_tma_2d(a_s + (i % STAGES) * A_ELEMS, &w_map, static_cast<int>(item % nk) * GT_BK,
-                          static_cast<int>(item / nk) * GT_BM, &full[i % STAGES]);
-            };
-            auto load_x = [&](int i) {
-                gt_arrive_expect_tx(&full[i % STAGES], B_BYTES);
-                gt_tma_2d(b_s + (i % STAGES) * B_ELEMS, &x_map, static_cast<int>((begin + i) % nk) * GT_BK, 0, &full[i % STAGES]);
+                const int tile = static_cast<int>(item / nk), kc = static_cast<int>(item % nk);
+                const bool two = 2 * tile + 1 < tiles64;          // the last tile may have one half only
+                gt_arrive_expect_tx(&full[i % STAGES], two ? A_BYTES : A_BYTES / 2);
+                for (int h = 0; h < (two ? 2 : 1); ++h) {
+                    const bf16* src = w_tiled + ((static_cast<size_t>(2 * tile + h) * nk256 + (kc >> 2)) * 4 + (kc & 3)) * (64 * 64);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+                                     "r"(gt_smem(a_s + (i % STAGES) * A_ELEMS + h * (64 * 64))), "l"(src), "r"(A_BYTES / 2),
+                                 "r"(gt_smem(&full[i % STAGES])) : "memory");
+                }
             };
             const int ahead = count < STAGES ? count : STAGES;
             for (int i = 0; i < ahead; ++i) load_w(i);            // weights: nobody in this step writes them
-            pdl_wait();                                           // x is the output of the kernel before this one
-            for (int i = 0; i < ahead; ++i) load_x(i);
             int issued = ahead;
             for (int i = STAGES; i < count; ++i) {
                 if (!gt_wait(&empty[i % STAGES], ((i / STAGES) - 1) & 1, &abort_flag, status)) break;
                 load_w(i);
-                load_x(i);
                 issued = i + 1;
             }
             if (abort_flag)                                       // let what is in flight land before the CTA goes away
                 for (int i = max(0, issued - STAGES); i < issued; ++i)
                     for (int n = 0; n < GT_WAIT_LIMIT && !gt_try_wait(&full[i % STAGES], (i / STAGES) & 1); ++n) {}
         }
+    } else if (warp >= 6) {
+        // ---- the tokens: warps 6..9 copy x[0..T) x 64 k-values of every stage with cp.async into the
+        // 128-byte-swizzled K-major tile (rows of x are K values apart: a TMA box of such rows costs the
+        // copy engine 21 clocks a row, which was this kernel's time) ----
+        const int lt = tid - 6 * 32;                              // 0..127
+        constexpr int LAG = 2;                                    // stages of x a thread keeps in flight
+        constexpr int PER = NT * 8 / 128;                         // 16-byte chunks per thread and stage
+        pdl_wait();                                               // x is the output of the kernel before this one
+        auto arrive_after_copies = [&](int i) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // the tensor core reads through the async proxy
+            gt_arrive(&full[i % STAGES]);
+        };
+        bool ok = true;
+        int done = 0;                                             // stages whose arrival has been made
+        for (int i = 0; i < count; ++i) {
+            const int st = i % STAGES;
+            if (i >= STAGES && !gt_wait(&empty[st], ((i / STAGES) - 1) & 1, &abort_flag, status)) { ok = false; break; }
+            const int k0 = static_cast<int>((begin + i) % nk) * GT_BK;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int c = lt + 128 * j, row = c >> 3, ch = c & 7;
+                const bool valid = row < T && k0 + ch * 8 < K;
+                const unsigned dst = gt_smem(b_s + st * B_ELEMS + row * 64 + ((ch ^ (row & 7)) << 3));
+                const bf16* src = x + (valid ? static_cast<size_t>(row) * K + k0 + ch * 8 : 0);
+                const int bytes = valid ? 16 : 0;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+            if (i >= LAG) {
+                asm volatile("cp.async.wait_group %0;\n" ::"n"(LAG));
+                arrive_after_copies(done++);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        if (ok)
+            while (done < count) arrive_after_copies(done++);
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
@@ -210,6 +254,7 @@ __global__ void __launch_bounds__(GT_THREADS) linear_stream_tcgen05_kernel(
         }
     } else {
         // ---- epilogue: warps 2..5, thread = one feature = one TMEM lane ----
+        // (warps 6..9 were taken by the branch above)
         const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk), seg = 0;
@@ -295,18 +340,6 @@ static bool gt_ready() {
     return g_gt_state > 0;
 }
 
-// [rows, cols] bfloat16 row-major as a 2-D tensor with boxes of [box_rows, 64 columns], 128-byte swizzle,
-// zeros outside.
-static bool gt_encode(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(bf16)};
-    const cuuint32_t box[2] = {GT_BK, static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t estr[2] = {1u, 1u};
-    return g_gt_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 extern "C" int llm_linear_stream_supported(int T, int N, int K) {
     return T >= 1 && T <= 128 && N >= 1 && K >= 8 && (K % 8) == 0;
 }
@@ -350,37 +383,38 @@ extern "C" int llm_linear_stream_slices(int T, int N, int K) {
 }
 
 template <int NT, typename TO>
-static int gt_launch(const CUtensorMap& w_map, const CUtensorMap& x_map, void* y, float* scratch, int T, int N, int K, int ctas,
+static int gt_launch(const bf16* w_tiled, const bf16* x, void* y, float* scratch, int T, int N, int K, int ctas,
                      int slices, int per_tile, int32_t* status, cudaStream_t s) {
     constexpr int STAGES = NT <= 64 ? 4 : 3;                      // two CTAs per SM must fit
     const size_t smem = static_cast<size_t>(STAGES) * (GT_BM + NT) * GT_BK * sizeof(bf16) + 1024;
     auto kern = linear_stream_tcgen05_kernel<NT, STAGES, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    launch_pdl(kern, dim3(ctas), dim3(GT_THREADS), smem, s, w_map, x_map, static_cast<TO*>(y), scratch, T, N, K, slices, per_tile,
+    launch_pdl(kern, dim3(ctas), dim3(GT_THREADS), smem, s, w_tiled, x, static_cast<TO*>(y), scratch, T, N, K, slices, per_tile,
                status);
     return launch_status();
 }
 
-// x: bfloat16 [T, K]; w: bfloat16 [N, K]; y: [T, N] float32 (out_dtype 0) or bfloat16 (1);
+// x: bfloat16 [T, K]; w_tiled: the weights [N, K] stored tile by tile (ops.tile_weight); y: [T, N] float32
+// (out_dtype 0) or bfloat16 (1);
 // scratch: float32, slices * T * N elements when llm_linear_stream_slices says more than one.
 // keep_partials: leave the partial sums in scratch as [slices, T, N] and write nothing to y.
-extern "C" int llm_linear_stream(const void* x, const void* w, void* y, int out_dtype, float* scratch, long long scratch_floats,
+extern "C" int llm_linear_stream(const void* x, const void* w_tiled, void* y, int out_dtype, float* scratch, long long scratch_floats,
                                  int T, int N, int K, int keep_partials, int32_t* status, uintptr_t stream) {
     if (!llm_linear_stream_supported(T, N, K)) return LLM_REFUSED_SIZE;
-    if (!aligned16(x) || !aligned16(w)) return LLM_REFUSED_ALIGN;
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(w_tiled) & 127u) != 0) return LLM_REFUSED_ALIGN;
     if (!gt_ready()) return LLM_REFUSED_SIZE;
     int ctas, slices, per_tile;
     gt_plan(N, K, &ctas, &slices, &per_tile);
     if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * T * N)) return LLM_REFUSED_SIZE;
     const int nt = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
-    CUtensorMap w_map, x_map;
-    if (!gt_encode(&w_map, w, N, K, GT_BM) || !gt_encode(&x_map, x, T, K, nt)) return LLM_REFUSED_SIZE;
+    const bf16* wt = static_cast<const bf16*>(w_tiled);
+    const bf16* xp = static_cast<const bf16*>(x);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     int rc;
 #define GO(NTV)                                                                                                         \
-    rc = out_dtype == LLM_DT_F32 ? gt_launch<NTV, float>(w_map, x_map, y, scratch, T, N, K, ctas, slices, per_tile, status, s) \
-                                 : gt_launch<NTV, bf16>(w_map, x_map, y, scratch, T, N, K, ctas, slices, per_tile, status, s)
+    rc = out_dtype == LLM_DT_F32 ? gt_launch<NTV, float>(wt, xp, y, scratch, T, N, K, ctas, slices, per_tile, status, s) \
+                                 : gt_launch<NTV, bf16>(wt, xp, y, scratch, T, N, K, ctas, slices, per_tile, status, s)
     if (out_dtype != LLM_DT_F32 && out_dtype != LLM_DT_BF16) return LLM_REFUSED_DTYPE;
     if (nt == 32) GO(32); else if (nt == 64) GO(64); else GO(128);
 #undef GO

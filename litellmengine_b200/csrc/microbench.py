@@ -170,7 +170,7 @@ def main():
         x = torch.randn(args.tokens, args.k, device=dev, dtype=torch.bfloat16)
         w = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02
         od = torch.float32 if args.out_dtype == "float32" else torch.bfloat16
-        if args.tiled:
+        if args.tiled or args.impl == "stream":
             ops.prepare_streaming(w)
         if args.impl == "library":
             fn = lambda: torch.mm(x, w.t(), out_dtype=od) if od != x.dtype else torch.mm(x, w.t())
@@ -182,7 +182,7 @@ def main():
             fn = lambda: ops.linear(x, w, out_dtype=od)
         if args.chain:
             ws = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(args.chain)]
-            if args.tiled:
+            if args.tiled or args.impl == "stream":
                 for wi in ws:
                     ops.prepare_streaming(wi)
             one = {"library": lambda wi: torch.mm(x, wi.t(), out_dtype=od) if od != x.dtype else torch.mm(x, wi.t()),

@@ -514,9 +514,8 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 
 
 STREAM_MAX_ROWS = 128    # rows up to which `linear` may take the tcgen05 weight-streaming kernel
-# off | on.  Off by default: fed by TMA in 128-byte rows (the widest a 128-byte-swizzled box can be)
-# the kernel reaches 3.1-4.0 TB/s where the library's kernels for these shapes reach 4.5-5.5 (its time
-# grows with the rows requested per stage, 128 of weights + the token tile, not with the bytes).
+# off | on.  Off by default: 52-100 us where the library's kernels for these shapes take 37-40 (see the
+# header of gemm_stream_tcgen05.cu for what was measured and what the kernel needs next).
 _STREAM_POLICY = os.environ.get("LLM_STREAM", "off")
 _stream_status: Dict[str, torch.Tensor] = {}
 
@@ -532,10 +531,14 @@ def stream_status(device) -> torch.Tensor:
 
 def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                   out: Optional[torch.Tensor] = None, partials_ok: bool = False):
-    """x [T <= 128, K] @ weight[N, K]^T with the tcgen05 weight-streaming kernel (bfloat16 operands
-    fetched by TMA, float32 accumulation in tensor memory, float32 or bfloat16 result).  With
-    `partials_ok` a product that is cut along K comes back as a `PartialSum`."""
+    """x [T <= 128, K] @ weight[N, K]^T with the tcgen05 weight-streaming kernel (the weights from
+    their tile-by-tile copy, see `prepare_streaming`; float32 accumulation in tensor memory, float32
+    or bfloat16 result).  With `partials_ok` a product that is cut along K comes back as a
+    `PartialSum`."""
     _dev(x, weight, out)
+    tiled = _tiled.get(weight.data_ptr())
+    if tiled is None:
+        raise KernelError("the streaming product wants a weight prepared with prepare_streaming")
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("the streaming product takes bfloat16 operands")
     T, K = x.shape
@@ -549,12 +552,12 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     status = stream_status(x.device)
     if partials_ok and slices > 1 and out is None:
         parts = torch.empty((slices, T, N), dtype=torch.float32, device=x.device)
-        _check(f(_ptr(x), _ptr(weight), None, 0, _ptr(parts), parts.numel(), T, N, K, 1, _ptr(status), _stream()), "linear_stream")
+        _check(f(_ptr(x), _ptr(tiled), None, 0, _ptr(parts), parts.numel(), T, N, K, 1, _ptr(status), _stream()), "linear_stream")
         return PartialSum(parts, None if out_dtype == torch.float32 else out_dtype)
     if out is None:
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     scratch = skinny_scratch(x.device, slices * T * N if slices > 1 else 0)
-    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
+    _check(f(_ptr(x), _ptr(tiled), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
              T, N, K, 0, _ptr(status), _stream()), "linear_stream")
     launch_count += 1 if slices > 1 else 0        # the kernel that adds the slices
     return out
@@ -576,7 +579,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
                 _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
         return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
-            and x.shape[1] % 8 == 0 and _STREAM_POLICY == "on"):
+            and x.shape[1] % 8 == 0 and _STREAM_POLICY == "on" and weight.data_ptr() in _tiled):
         return linear_stream(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())

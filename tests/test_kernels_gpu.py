@@ -502,10 +502,12 @@ def test_stream_tcgen05_product(T, N, K, out_dtype):
     x = torch.randn(T, K).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    got = ops().linear_stream(x.to(DEV), w.to(DEV), DT[out_dtype])
+    wd = w.to(DEV)
+    ops().prepare_streaming(wd)
+    got = ops().linear_stream(x.to(DEV), wd, DT[out_dtype])
     assert got.dtype == DT[out_dtype] and got.shape == (T, N)
     close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
-    parts = ops().linear_stream(x.to(DEV), w.to(DEV), DT[out_dtype], partials_ok=True)
+    parts = ops().linear_stream(x.to(DEV), wd, DT[out_dtype], partials_ok=True)
     close(ops().as_tensor(parts), ref, 2e-5 if out_dtype == "float32" else 6e-3)
     assert ops().stream_status(DEV).tolist() == [0, 0]
 
