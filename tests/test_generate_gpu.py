@@ -25,7 +25,7 @@ def engine_for(cfg, w, dtype, page, pool, **kw):
 
 
 def test_greedy_generation_config_a_float32():
-    """BASELINE config A: prompts of 5, 9 and 13 tokens, 8 greedy steps each, page size 4."""
+    """Tiny configuration A: prompts of 5, 9 and 13 tokens, 8 greedy steps each, page size 4."""
     cfg, w = tm.TINY_A, tm.make_weights(tm.TINY_A, tm.TINY_A_SEED)
     prompts = [tm.random_tokens(cfg, n, 40 + n) for n in (5, 9, 13)]
     eng = engine_for(cfg, w, "float32", tm.TINY_A_PAGE, pool=96)
@@ -37,7 +37,7 @@ def test_greedy_generation_config_a_float32():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_chunked_and_mixed(dtype):
-    """BASELINE config B's shape of work: prompts of 1, 7, 16 and 33 tokens, prefilled in
+    """Tiny configuration B: prompts of 1, 7, 16 and 33 tokens, prefilled in
     portions of 6 beside decoding requests.  A bfloat16 run may differ from the plain code only
     where the two best logits are closer than bfloat16 resolves."""
     cfg = tm.TINY_B
@@ -120,7 +120,7 @@ def test_pipelined_and_unpipelined_stepping_give_the_same_tokens():
 
 
 def test_temperature_sampling_is_reproducible_and_batch_independent():
-    """BASELINE config B: 12 sampling steps at temperature 0.8 with a fixed seed."""
+    """Tiny configuration B: 12 sampling steps at temperature 0.8 with a fixed seed."""
     from litellmengine_b200.csrc import ops
     cfg, w = tm.TINY_B, tm.make_weights(tm.TINY_B, tm.TINY_B_SEED)
     prompts = [tm.random_tokens(cfg, n, 80 + n) for n in (1, 7, 16, 33)]
