@@ -531,6 +531,18 @@ def test_prefill_tcgen05_finds_a_far_key(key):
         assert (float(means[i]) > 90.0) == (first_q + i >= key)
 
 
+def test_long_contexts_decode_and_prompt_kernels():
+    """Thousands of keys: block tables of hundreds of pages, sixteen key splits of twenty tiles each
+    in the decode kernel, twenty-four 128-key tiles and a ring that wraps twelve times in the
+    one-pass prompt kernel; a spiked key early in the context must still be found."""
+    out, ref = fast_case("decode", 4, 2, 128, 16, [(5000, 1), (4097, 1)], splits=16, spike=(0, 77), seed=5)
+    close(out, ref, 1e-2)
+    assert float(out[0].float().mean()) > 90.0
+    out, ref = fast_case("prefill_tcgen05", 4, 2, 128, 16, [(3000, 260)], spike=(0, 131), seed=6)
+    close(out, ref, 1e-2)
+    assert float(out[-1].float().mean()) > 90.0
+
+
 @pytest.mark.parametrize("climb", [3.0, 12.0, 40.0, 150.0])
 def test_prefill_tcgen05_scores_that_keep_climbing(climb):
     """The one-pass kernel keeps a reference maximum that trails the running one and rescales its
