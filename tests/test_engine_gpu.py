@@ -174,3 +174,17 @@ def test_decode_steps_replayed_as_graphs_match_kernel_by_kernel_launches(dtype):
         assert (runner.graph_replays > 20) == graphs
     worst = max(float(np.abs(got[True][k] - got[False][k]).max()) for k in got[True])
     assert worst <= rh.tol_for(dtype)
+
+
+def test_one_layer_at_real_widths():
+    """Hidden 4096, 32/8 heads of 128, intermediate 12288, one layer, bfloat16: the engine's products
+    (k-splits, partial sums, tiled weight copies), the TMA decode attention and the tcgen05 prompt
+    attention at the sizes they are tuned for, whole and mixed, against the plain code."""
+    cfg, seed, page = tm.WIDE_G, tm.WIDE_G_SEED, tm.WIDE_G_PAGE
+    w = tm.make_weights(cfg, seed, bf16_exact=True, matrix_std=0.02)
+    reqs = rh.requests_for(cfg, [3, 70, 150], seed)
+    ref = rh.plain_rows(cfg, w, reqs, "bfloat16")
+    for what, steps in (("whole", rh.trace_whole(reqs)), ("mixed", rh.trace_mixed(reqs, seed=2, max_live=3, prompt_frac=0.4))):
+        runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=rh.peak_tokens(steps, page), max_requests=4,
+                                max_tokens_per_step=256)
+        rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.BF16_TOL, f"wide {what}")

@@ -74,6 +74,18 @@ TINY_F = dict(
 TINY_F_PAGE, TINY_F_SEED = 32, 17
 
 
+# One layer at the widths of a real 8B model (a small vocabulary keeps it quick): the products'
+# k-splits, tiled weight copies and the attention kernels' grids at the sizes they are tuned for.
+WIDE_G = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, intermediate_size=12288, vocab_size=1031, rope_theta=1000000.0,
+    rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=False,
+    torch_dtype="bfloat16",
+)
+WIDE_G_PAGE, WIDE_G_SEED = 16, 19
+
+
 def tensor_shapes(cfg: dict) -> dict:
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
