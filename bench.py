@@ -236,7 +236,7 @@ def main() -> int:
     for i in ids:
         engine.release_request(i)
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": runner.buffers.size * 4, "d2h_bytes_per_step": args.batch * 4}
+           "h2d_bytes_per_step": runner.buffers.last.size * 4, "d2h_bytes_per_step": args.batch * 4}
 
     points = {}
     if not args.no_points:

@@ -30,13 +30,13 @@ class StepEntry:
                                       # `feedback` of the tokens the previous step sampled on the device
 
 
-class StepBuffers:
-    """Pinned staging and device arrays sized once for the largest step."""
+class _Region:
+    """One layout of the step's arrays: a pinned staging buffer and its fixed device twin."""
 
-    def __init__(self, max_tokens: int, max_entries: int, num_groups: int, device):
-        self.max_tokens, self.max_entries, self.num_groups = max_tokens, max_entries, num_groups
-        self.max_updates = max_tokens + 2 * max_entries + 8      # new pages a step can append, with slack
-        T, B, U = max_tokens, max_entries, self.max_updates
+    def __init__(self, token_cap: int, max_entries: int, num_groups: int, device):
+        self.token_cap = token_cap
+        self.max_updates = token_cap + 2 * max_entries + 8       # new pages a step can append, with slack
+        T, B, U = token_cap, max_entries, self.max_updates
         off = 0
         self.off = {}
         for name, n in (("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
@@ -51,11 +51,9 @@ class StepBuffers:
             self.off[f"upd_value{g}"] = (off, U)
             off += U
         self.size = off
-        self.device = torch.device(device)
         self.pinned = torch.zeros(off, dtype=torch.int32, pin_memory=True)
         self.host = self.pinned.numpy()
-        self.dev = torch.zeros(off, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.dev = torch.zeros(off, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event()
         self._in_flight = False
 
@@ -76,6 +74,35 @@ class StepBuffers:
         self.dev.copy_(self.pinned, non_blocking=True)
         self.copied.record()
         self._in_flight = True
+
+
+class StepBuffers:
+    """Pinned staging and device arrays sized once: a large layout for the largest step and a
+    small one for steps of at most `max_entries` tokens (decode steps), so that those copy a few
+    kilobytes to the device instead of the large layout's hundred and more.  A step lives in one
+    of the two; device addresses inside each are fixed, which is what a captured graph needs."""
+
+    def __init__(self, max_tokens: int, max_entries: int, num_groups: int, device):
+        self.max_tokens, self.max_entries, self.num_groups = max_tokens, max_entries, num_groups
+        self.device = torch.device(device)
+        self.large = _Region(max_tokens, max_entries, num_groups, self.device)
+        self.small = _Region(min(max_tokens, max_entries), max_entries, num_groups, self.device)
+        self.max_updates = self.large.max_updates
+        self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.last = self.large                                    # the region of the step packed last
+
+    def host_view(self, name: str) -> np.ndarray:
+        """Of the step packed last."""
+        return self.last.host_view(name)
+
+    def dev_view(self, name: str, count: Optional[int] = None) -> torch.Tensor:
+        return self.last.dev_view(name, count)
+
+    def region_for(self, num_tokens: int, updates) -> _Region:
+        small = self.small
+        if num_tokens <= small.token_cap and all(len(idx) <= small.max_updates for idx, _ in updates):
+            return small
+        return self.large
 
 
 @dataclass
@@ -102,6 +129,7 @@ class StepBatch:
     num_prefill_tiles: int = 0
     entries: List[StepEntry] = field(default_factory=list)
     feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
+    layout: str = "large"                     # which of StepBuffers' two layouts holds this step's arrays
 
 
 def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
@@ -113,8 +141,11 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
     if T > buffers.max_tokens or B > buffers.max_entries:
         raise ValueError(f"a step of {T} tokens in {B} entries exceeds the limits "
                          f"({buffers.max_tokens} tokens, {buffers.max_entries} entries)")
-    buffers.wait_reusable()
-    hv = buffers.host_view
+    updates = list(updates)
+    region = buffers.region_for(T, updates)
+    buffers.last = region
+    region.wait_reusable()
+    hv = region.host_view
     tok, pos, ent = hv("token_ids"), hv("positions"), hv("token_entry")
     slot, qs, ql, kl = hv("entry_slot"), hv("entry_q_start"), hv("entry_q_len"), hv("entry_kv_len")
     wr, ws = hv("want_rows"), hv("want_slot")
@@ -157,12 +188,12 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         hv(f"upd_index{g}")[:len(idx)] = idx
         hv(f"upd_value{g}")[:len(val)] = val
         counts[8 + g] = len(idx)
-    buffers.upload()
-    dv = buffers.dev_view
+    region.upload()
+    dv = region.dev_view
     return StepBatch(
         token_ids=dv("token_ids", T), positions=dv("positions", T), token_entry=dv("token_entry", T),
         entry_slot=dv("entry_slot", B), entry_q_start=dv("entry_q_start", B), entry_q_len=dv("entry_q_len", B),
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
         decode_rows=dv("decode_rows", n_dec), prefill_tiles=dv("prefill_tiles", 2 * n_tiles).view(n_tiles, 2),
         num_decode=n_dec, num_prefill_tiles=n_tiles, status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
-        entries=entries, feedback=feedback)
+        entries=entries, feedback=feedback, layout="small" if region is buffers.small else "large")

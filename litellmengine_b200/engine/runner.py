@@ -119,12 +119,13 @@ class ModelRunner:
         for e in entries:
             self.cache.ensure(e.slot, e.past + len(e.tokens))
         batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled)
-        counts = self.buffers.dev_view("counts")
+        region = self.buffers.last                              # where pack_step put this step
+        counts = region.dev_view("counts")
         for g, group in enumerate(self.cache.groups):
-            n = int(self.buffers.host_view("counts")[8 + g])
+            n = int(region.host_view("counts")[8 + g])
             if n:
-                ops.scatter_int32(group.table_dev, self.buffers.dev_view(f"upd_index{g}", n),
-                                  self.buffers.dev_view(f"upd_value{g}", n), counts[8 + g:9 + g], n,
+                ops.scatter_int32(group.table_dev, region.dev_view(f"upd_index{g}", n),
+                                  region.dev_view(f"upd_value{g}", n), counts[8 + g:9 + g], n,
                                   self.buffers.status)
         return batch
 
@@ -140,10 +141,11 @@ class ModelRunner:
         (sample, copy) before stepping again."""
         B = batch.num_tokens
         if self.use_graphs and batch.num_decode == B and batch.num_want == B:
-            g = self._graphs.get(B)
+            key = (B, batch.layout)                  # a graph holds the device addresses of one layout
+            g = self._graphs.get(key)
             if g is None:
-                seen = self._graph_seen.get(B, 0)
-                self._graph_seen[B] = seen + 1
+                seen = self._graph_seen.get(key, 0)
+                self._graph_seen[key] = seen + 1
                 if seen >= 1:
                     g = self._capture(batch)
             if g is not None:
@@ -173,8 +175,8 @@ class ModelRunner:
         kernels = ops.launch_count - before     # counted while capturing, not run
         ops.launch_count = before
         batch.max_kv_len = real_max_kv
-        self._graphs[B] = (graph, logits, kernels)
-        return self._graphs[B]
+        self._graphs[(B, batch.layout)] = (graph, logits, kernels)
+        return self._graphs[(B, batch.layout)]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; returns float32 [wanted, vocab] in the order of
