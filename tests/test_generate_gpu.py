@@ -119,6 +119,41 @@ def test_pipelined_and_unpipelined_stepping_give_the_same_tokens():
         assert (eng.scheduler.num_preemptions > 0) == (pool == 48)
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_many_requests_arriving_over_time_under_page_pressure(seed):
+    """Forty greedy requests of random lengths, added a few at a time while others run, some ending
+    at an end-of-sequence token, in a cache too small for all of them (preemptions) and with
+    pipelined steps: every request's tokens are those of the plain implementation run alone."""
+    import random
+    rng = random.Random(seed)
+    cfg, w = tm.TINY_A, tm.make_weights(tm.TINY_A, tm.TINY_A_SEED)
+    jobs = []
+    for i in range(40):
+        prompt = tm.random_tokens(cfg, rng.randint(1, 30), 500 + 40 * seed + i)
+        n_new = rng.randint(1, 20)
+        free = pq.greedy_generate(prompt, w, cfg, n_new)
+        eos = free[rng.randrange(len(free))] if rng.random() < 0.3 else -1
+        want = free[:free.index(eos) + 1] if eos >= 0 else free
+        jobs.append((prompt, n_new, eos, want))
+    eng = engine_for(cfg, w, "float32", 4, pool=96, max_requests=6, chunk=rng.choice([3, 7, 16]), max_tokens_per_step=24)
+    ids, pending, steps = [], list(range(len(jobs))), 0
+    while pending or eng.has_work():
+        for _ in range(rng.randint(0, 3)):
+            if pending:
+                j = pending.pop(0)
+                ids.append((j, eng.add_request(jobs[j][0], jobs[j][1], eos_token_id=jobs[j][2])))
+        if eng.has_work():
+            eng.step()
+        steps += 1
+        assert steps < 5000
+    eng.runner.check_status()
+    for j, rid in ids:
+        assert eng.request(rid).generated_ids == jobs[j][3], f"request {j}"
+    assert eng.scheduler.num_preemptions > 0
+    eng.runner.cache.check_invariants()
+    assert all(g.pool.free_count == g.pool.num_pages for g in eng.runner.cache.groups)
+
+
 def test_temperature_sampling_is_reproducible_and_batch_independent():
     """Tiny configuration B: 12 sampling steps at temperature 0.8 with a fixed seed."""
     from litellmengine_b200.csrc import ops
