@@ -183,8 +183,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
 // the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for this kernel's strided
 // form).  The tokens' rows still come by cp.async.  The wait on a stage's mbarrier is bounded;
 // when it runs out the kernel records status code 8 and goes on (its result is then flagged).
-#define GS_TILED_BK 256
-#define GS_TILED_STAGES 3
+#define GS_TILED_BK 256          // k-values of a stored block
 #define GS_TILED_WAIT_LIMIT 2000000
 
 __device__ __forceinline__ unsigned gs_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
@@ -200,13 +199,16 @@ __device__ __forceinline__ bf16* gs_at_tiled(bf16* base, int row, int chunk) {
     return base + (chunk >> 3) * (GS_ROWS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
-template <typename TO>
+// MT = 8: stages of 256 k-values (a whole 32 KB block), three of them; MT = 16: stages of 128 k-values
+// (half a block: two sub-tiles, 16 KB contiguous), five of them, so that two CTAs fit an SM.
+template <int MT, typename TO>
 __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const bf16* __restrict__ x,
                                                                          const bf16* __restrict__ w_tiled, TO* __restrict__ y,
                                                                          float* __restrict__ partial, int M, int N, int K,
                                                                          int slices, int per_tile, int32_t* __restrict__ status) {
-    constexpr int MT = 8, GS_STAGES = GS_TILED_STAGES, GS_BK = GS_TILED_BK;
+    constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT);
     constexpr unsigned W_BYTES = GS_ROWS * GS_BK * sizeof(bf16);
+    const long long halves_per_tile = static_cast<long long>((K + 255) / 256) * (256 / GS_BK);   // stages of GS_BK in a tile's row of blocks
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK], as stored in w_tiled
     bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
@@ -234,7 +236,8 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(W_BYTES) : "memory");
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
                              "r"(gs_smem(w_s + (i % GS_STAGES) * GS_ROWS * GS_BK)),
-                         "l"(w_tiled + static_cast<size_t>(begin + i) * (GS_ROWS * GS_BK)), "r"(W_BYTES), "r"(gs_smem(bar)) : "memory");
+                         "l"(w_tiled + (static_cast<size_t>((begin + i) / nk) * halves_per_tile + (begin + i) % nk) * (GS_ROWS * GS_BK)),
+                         "r"(W_BYTES), "r"(gs_smem(bar)) : "memory");
         }
     };
     auto load_x = [&](int i) {
@@ -264,7 +267,9 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
         gs_commit();
     }
     __syncthreads();                                                     // the barriers exist for everyone
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc[MT / 8][4];
+#pragma unroll
+    for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
     int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk);
     for (int i = 0; i < count; ++i) {
         gs_wait<GS_STAGES - 2>();                                        // this thread's copies of the tokens' rows
@@ -287,12 +292,16 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
         bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
 #pragma unroll
         for (int kp = 0; kp < GS_BK / 32; ++kp) {
-            unsigned a0[4], a1[4], b[4];
+            unsigned a0[4], a1[4];
             gs_ldmatrix_x4(a0, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
             gs_ldmatrix_x4(a1, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
-            gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, (lane & 7), kp * 4 + (lane >> 3)));
-            gs_mma(acc, a0, b[0], b[1]);
-            gs_mma(acc, a1, b[2], b[3]);
+#pragma unroll
+            for (int j = 0; j < MT / 8; ++j) {
+                unsigned b[4];                                           // tokens 8j..8j+7, two k-steps
+                gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
+                gs_mma(acc[j], a0, b[0], b[1]);
+                gs_mma(acc[j], a1, b[2], b[3]);
+            }
         }
         const bool tile_done = kt == nk - 1;
         if (tile_done || i == count - 1) {
@@ -300,18 +309,21 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
             const int slice = per_tile ? static_cast<int>(blockIdx.x % per_tile)
                                        : static_cast<int>(blockIdx.x - gs_cta_of(static_cast<long long>(tile) * nk, total, ctas));
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int f = f0 + (e >> 1) * 8, tok = t0 + (e & 1);
-                if (f < N && tok < M) {
-                    if (slices == 1) {
-                        y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[e]);
-                    } else {
-                        partial[(static_cast<size_t>(slice) * M + tok) * N + f] = acc[e];
-                        if (tile_done && !per_tile)
-                            for (int z = slice + 1; z < slices; ++z) partial[(static_cast<size_t>(z) * M + tok) * N + f] = 0.0f;
+            for (int j = 0; j < MT / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int f = f0 + (e >> 1) * 8, tok = j * 8 + t0 + (e & 1);
+                    if (f < N && tok < M) {
+                        if (slices == 1) {
+                            y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[j][e]);
+                        } else {
+                            partial[(static_cast<size_t>(slice) * M + tok) * N + f] = acc[j][e];
+                            if (tile_done && !per_tile)
+                                for (int z = slice + 1; z < slices; ++z) partial[(static_cast<size_t>(z) * M + tok) * N + f] = 0.0f;
+                        }
                     }
+                    acc[j][e] = 0.0f;
                 }
-                acc[e] = 0.0f;
             }
         }
         if (tile_done) { kt = 0; ++tile; } else ++kt;
@@ -418,16 +430,16 @@ extern "C" long long llm_linear_skinny_tiled_elems(int N, int K) {
     return static_cast<long long>((N + GS_ROWS - 1) / GS_ROWS) * ((K + GS_TILED_BK - 1) / GS_TILED_BK) * GS_ROWS * GS_TILED_BK;
 }
 
-template <typename TO>
+template <int MT, typename TO>
 static int launch_skinny_tiled(const bf16* x, const bf16* wt, void* y, float* scratch, long long scratch_floats, int M, int N,
                                int K, int keep_partials, int32_t* status, cudaStream_t s) {
     if (!skinny_device()) return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(GS_TILED_STAGES) * (GS_ROWS + 8) * GS_TILED_BK * sizeof(bf16);
-    auto kern = linear_skinny_tiled_kernel<TO>;
+    const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK_FOR(MT) * sizeof(bf16);
+    auto kern = linear_skinny_tiled_kernel<MT, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     int ctas, slices, per_tile;
-    skinny_plan(N, K, GS_TILED_BK, &ctas, &slices, &per_tile);
+    skinny_plan(N, K, GS_BK_FOR(MT), &ctas, &slices, &per_tile);
     if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * M * N)) return LLM_REFUSED_SIZE;
     launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, wt, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile, status);
     int rc = launch_status();
@@ -440,14 +452,17 @@ static int launch_skinny_tiled(const bf16* x, const bf16* wt, void* y, float* sc
 extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void* y, int out_dtype, float* scratch,
                                        long long scratch_floats, int M, int N, int K, int keep_partials, int32_t* status,
                                        uintptr_t stream) {
-    if (!llm_linear_skinny_supported(M, N, K) || M > 8) return LLM_REFUSED_SIZE;
+    if (!llm_linear_skinny_supported(M, N, K)) return LLM_REFUSED_SIZE;
     if (!aligned16(x) || (reinterpret_cast<uintptr_t>(w_tiled) & 127u) != 0 || status == nullptr) return LLM_REFUSED_ALIGN;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bf16* xp = static_cast<const bf16*>(x);
     const bf16* wp = static_cast<const bf16*>(w_tiled);
-    if (out_dtype == LLM_DT_F32) return launch_skinny_tiled<float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
-    if (out_dtype == LLM_DT_BF16) return launch_skinny_tiled<bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
-    return LLM_REFUSED_DTYPE;
+    if (out_dtype != LLM_DT_F32 && out_dtype != LLM_DT_BF16) return LLM_REFUSED_DTYPE;
+    if (M <= 8)
+        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                       : launch_skinny_tiled<8, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                   : launch_skinny_tiled<16, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 
 // x: bfloat16 [M, K]; w: bfloat16 [N, K]; y: [M, N] float32 (out_dtype 0) or bfloat16 (1);

@@ -465,7 +465,7 @@ def tile_weight(weight: torch.Tensor) -> torch.Tensor:
 
 
 def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
-    """Keep a tiled copy of a bfloat16 weight for decode steps of up to 8 tokens (twice the
+    """Keep a tiled copy of a bfloat16 weight for decode steps of up to 16 tokens (twice the
     memory for that weight; `LLM_TILED=off` keeps one copy).  The copy lives as long as the weight."""
     if (weight is None or _TILED_POLICY == "off" or not weight.is_cuda or weight.dtype != torch.bfloat16
             or weight.dim() != 2 or weight.shape[1] % 8 != 0):
@@ -490,7 +490,7 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     if weight.shape[1] != K:
         raise KernelError("x and weight disagree on K")
     global launch_count
-    tiled = _tiled.get(weight.data_ptr()) if M <= 8 else None
+    tiled = _tiled.get(weight.data_ptr())
     if tiled is not None:
         g = _fn("gemm_skinny", "llm_linear_skinny_tiled",
                 [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])

@@ -466,7 +466,9 @@ def test_skinny_product(M, N, K, out_dtype):
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (7, 48, 4096), (8, 1000, 1544),
-                                   (5, 17, 8), (8, 6144, 4096), (2, 4096, 12288)])
+                                   (5, 17, 8), (8, 6144, 4096), (2, 4096, 12288),
+                                   (9, 100, 520), (16, 331, 80), (13, 1000, 1544), (16, 6144, 4096), (11, 4096, 12288),
+                                   (12, 70, 384), (16, 64, 128)])
 def test_skinny_product_over_tiled_weights(M, N, K, out_dtype):
     """The same product reading a copy of the weights stored tile by tile (one bulk copy per
     stage): same sums as over the plain layout, at sizes with ragged edge tiles."""
