@@ -441,7 +441,8 @@ _SKINNY_POLICY = os.environ.get("LLM_SKINNY", "all")     # all | auto | off: whi
 
 
 # ---- weights stored tile by tile for the streaming product ----------------------------------
-_TILED_POLICY = os.environ.get("LLM_TILED", "on")     # on | off: keep a tiled copy of decode weights
+_TILED_POLICY = os.environ.get("LLM_TILED", "auto")   # on | auto | off: keep a tiled copy of decode weights
+_TILED_RESERVE = 0.30                                  # auto: only while this share of the device's memory stays free
 _tiled: Dict[int, torch.Tensor] = {}                   # weight.data_ptr() -> its tiled copy
 TILE_ROWS, TILE_K = 64, 256
 
@@ -466,13 +467,21 @@ def tile_weight(weight: torch.Tensor) -> torch.Tensor:
 
 def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
     """Keep a tiled copy of a bfloat16 weight for decode steps of up to 16 tokens (twice the
-    memory for that weight; `LLM_TILED=off` keeps one copy).  The copy lives as long as the weight."""
+    memory for that weight).  `LLM_TILED=off` keeps one copy, `on` always makes the second, `auto`
+    (the default) makes it while 30 % of the device's memory stays free afterwards, so that a model
+    that fills most of the device leaves its room to the cache.  The copy lives as long as the weight."""
     if (weight is None or _TILED_POLICY == "off" or not weight.is_cuda or weight.dtype != torch.bfloat16
             or weight.dim() != 2 or weight.shape[1] % 8 != 0):
         return
     key = weight.data_ptr()
     if key in _tiled:
         return
+    if _TILED_POLICY != "on":
+        free, total = torch.cuda.mem_get_info(weight.device)
+        free += torch.cuda.memory_reserved(weight.device) - torch.cuda.memory_allocated(weight.device)   # cached blocks are free
+        size = weight.numel() * weight.element_size()
+        if free - size < _TILED_RESERVE * total or free < 3 * size:     # what stays; what making it needs meanwhile
+            return
     _tiled[key] = tile_weight(weight)
     weakref.finalize(weight, _tiled.pop, key, None)
 
