@@ -100,7 +100,7 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--out-dtype", default="bfloat16")
-    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "stream"],
+    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "stream", "pair", "pair_silu", "library_silu"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
     ap.add_argument("--tiled", action="store_true", help="linear --impl own: over a tile-by-tile copy of the weights")
     ap.add_argument("--chain", type=int, default=0,
@@ -178,6 +178,12 @@ def main():
             fn = lambda: ops.linear_skinny(x, w, od)
         elif args.impl == "stream":
             fn = lambda: ops.linear_stream(x, w, od)
+        elif args.impl == "pair":
+            fn = lambda: ops.linear_pair(x, w, od)
+        elif args.impl == "pair_silu":                            # w is [gate; up]: N = 2 I
+            fn = lambda: ops.linear_pair_silu_mul(x, w)
+        elif args.impl == "library_silu":
+            fn = lambda: ops.silu_and_mul(torch.mm(x, w.t()))
         else:
             fn = lambda: ops.linear(x, w, out_dtype=od)
         if args.chain:

@@ -530,7 +530,8 @@ _stream_status: Dict[str, torch.Tensor] = {}
 
 
 def stream_status(device) -> torch.Tensor:
-    """The status word of the tcgen05 streaming product (code 7: a bounded wait ran out)."""
+    """The status word of the tcgen05 products (code 7: a bounded wait of the streaming product ran
+    out; 9: of the paired product)."""
     key = str(device)
     t = _stream_status.get(key)
     if t is None:
@@ -569,6 +570,43 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     _check(f(_ptr(x), _ptr(tiled), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
              T, N, K, 0, _ptr(status), _stream()), "linear_stream")
     launch_count += 1 if slices > 1 else 0        # the kernel that adds the slices
+    return out
+
+
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, K] @ weight[N, K]^T for prompt portions with the engine's own tcgen05 kernel, in which
+    two CTAs of a cluster share a tile of 256 tokens x 256 features (bfloat16 operands, float32
+    accumulation in tensor memory, float32 or bfloat16 result)."""
+    _dev(x, weight, out)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError("the paired product takes bfloat16 operands")
+    T, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError("x and weight disagree on K")
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    f = _fn("gemm_pair_tcgen05", "llm_linear_pair", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), T, N, K, _ptr(stream_status(x.device)), _stream()), "linear_pair")
+    return out
+
+
+def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x @ gate^T) * (x @ up^T) for w_gate_up = [gate; up] of 2 I rows, as bfloat16 [T, I]: the
+    paired tcgen05 product with the activation in its epilogue (gate and up are rounded to bfloat16
+    before the activation, as the separate kernel would read them)."""
+    _dev(x, w_gate_up, out)
+    if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
+        raise KernelError("the paired product takes bfloat16 operands")
+    T, K = x.shape
+    if w_gate_up.shape[1] != K or w_gate_up.shape[0] % 2 != 0:
+        raise KernelError("x and the gate/up weight disagree")
+    inter = w_gate_up.shape[0] // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=torch.bfloat16, device=x.device)
+    f = _fn("gemm_pair_tcgen05", "llm_linear_pair_silu_mul", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, _ptr(stream_status(x.device)), _stream()), "linear_pair_silu_mul")
     return out
 
 

@@ -514,6 +514,41 @@ def test_stream_tcgen05_product(T, N, K, out_dtype):
     assert ops().stream_status(DEV).tolist() == [0, 0]
 
 
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,N,K", [(256, 256, 64), (128, 64, 512), (300, 520, 136), (513, 1000, 1544), (17, 8, 8),
+                                   (1100, 776, 448), (2048, 1024, 4096), (260, 6144, 640)])
+def test_paired_tcgen05_product(T, N, K, out_dtype):
+    """The product that two CTAs of a cluster compute together (256 tokens x 256 features a tile)
+    against float64, at sizes that are no multiple of its tiles, with one tile and with several
+    tiles per cluster (both accumulators, the ring of stages wrapping)."""
+    torch.manual_seed(T * 1000 + N)
+    x = torch.randn(T, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    got = ops().linear_pair(x.to(DEV), w.to(DEV), DT[out_dtype])
+    assert got.dtype == DT[out_dtype] and got.shape == (T, N)
+    close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    assert ops().stream_status(DEV).tolist() == [0, 0]
+
+
+@pytest.mark.parametrize("T,inter,K", [(256, 128, 64), (300, 264, 136), (700, 1000, 520), (130, 8, 64), (2048, 3072, 1024)])
+def test_paired_tcgen05_gate_up_product(T, inter, K):
+    """The same with silu(gate) * up in its epilogue: bit for bit what the bfloat16 product followed
+    by the separate activation kernel gives when both add in the same order; checked here against
+    float64 products rounded to bfloat16 before the activation."""
+    torch.manual_seed(T + inter)
+    x = torch.randn(T, K).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K) * 0.05).to(torch.bfloat16)
+    gu = (x.double() @ w.double().T).to(torch.bfloat16).double()
+    ref = (gu[:, :inter] / (1.0 + torch.exp(-gu[:, :inter]))) * gu[:, inter:]
+    got = ops().linear_pair_silu_mul(x.to(DEV), w.to(DEV))
+    assert got.dtype == torch.bfloat16 and got.shape == (T, inter)
+    close(got, ref, 1e-2)           # a product that lands on a bfloat16 rounding boundary may fall either way
+    two_step = ops().silu_and_mul(ops().linear_pair(x.to(DEV), w.to(DEV), torch.bfloat16))
+    assert torch.equal(got, two_step)
+    assert ops().stream_status(DEV).tolist() == [0, 0]
+
+
 # ---- the tcgen05 / TMEM / TMA prompt-portion attention kernel ------------------------------------
 @pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 64), (3, 1, 8), (6, 2, 64), (4, 2, 32), (5, 5, 16)])
 def test_prefill_tcgen05_kernel(nq, nkv, page):
