@@ -33,6 +33,9 @@
 #define GP_BN 256                 // accumulator columns per tile (features; gate|up in gate/up mode)
 #define GP_BK 64                  // k-values per stage: one 128-byte swizzled row
 #define GP_STAGES 6
+#ifndef GP_MAX_CUT
+#define GP_MAX_CUT 2              // units of 64 columns (4) run at well under a quarter of a tile's time each
+#endif
 #define GP_THREADS 192            // producer warp, issuing warp, 4 epilogue warps
 #define GP_WAIT_LIMIT 2000000
 #define GP_STAGE_BYTES (2 * GP_BM * GP_BK * 2)      // one CTA's part of a stage: 128 rows of x and 128 rows of w
@@ -132,18 +135,50 @@ __device__ __forceinline__ void gp_cluster_sync() {
 }
 __device__ __forceinline__ float gp_silu(float g) { return g / (1.0f + expf(-g)); }
 
+// The work of one cluster, in order: whole tiles c, c + C, ... below `whole` (a multiple of C), then the
+// remaining tiles cut `cut` ways along the features (units of 256 / cut accumulator columns), dealt
+// round-robin as well.  Tiles are numbered token tile fastest.
+struct GpPlan {
+    int tiles_m, tiles;      // token tiles; all tiles
+    int whole, cut;          // tiles below `whole` are taken whole; the rest in `cut` parts (1, 2 or 4)
+};
+struct GpUnit {
+    int mt, nt, part, cut;
+};
+__device__ __forceinline__ bool gp_unit(const GpPlan& p, int i, int cluster, int clusters, GpUnit* u) {
+    const int rounds = p.whole / clusters;
+    int tile;
+    if (i < rounds) {
+        tile = i * clusters + cluster;
+        u->part = 0;
+        u->cut = 1;
+    } else {
+        const int j = (i - rounds) * clusters + cluster;
+        if (j >= (p.tiles - p.whole) * p.cut) return false;
+        tile = p.whole + j / p.cut;
+        u->part = j % p.cut;
+        u->cut = p.cut;
+    }
+    u->mt = tile % p.tiles_m;
+    u->nt = tile / p.tiles_m;
+    return true;
+}
+
 // MODE 0: y[T, N] = x . w^T.  MODE 1: w is [gate; up] of 2 * inter rows, y[T, inter] = silu(gate) * up.
-// tiles_n counts tiles of 256 features (MODE 0) or of 128 features with their gate and up rows (MODE 1).
+// MODE 2: y[T, N] (float32) += x . w^T: the product joins the residual stream where it lies.
+// w_map, w_map2, w_map4: the same weights read in boxes of 128, 64 and 32 rows (for units of a tile
+// cut 1, 2 or 4 ways).
 template <int MODE, typename TO>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS) linear_pair_tcgen05_kernel(
-    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, TO* __restrict__ y,
-    int T, int N, int K, int inter, int tiles_m, int tiles_n, int32_t* __restrict__ status) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linear_pair_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+    const __grid_constant__ CUtensorMap w_map2, const __grid_constant__ CUtensorMap w_map4, TO* __restrict__ y,
+    int T, int N, int K, int inter, GpPlan plan, int32_t* __restrict__ status) {
     pdl_invite();
     constexpr int TILE_ELEMS = GP_BM * GP_BK;
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     bf16* a_s = reinterpret_cast<bf16*>(smem_al);                 // [STAGES][128 tokens][64]
-    bf16* b_s = a_s + GP_STAGES * TILE_ELEMS;                     // [STAGES][128 rows of w][64]
+    bf16* b_s = a_s + GP_STAGES * TILE_ELEMS;                     // [STAGES][up to 128 rows of w][64]
     __shared__ __align__(8) unsigned long long full[GP_STAGES], empty[GP_STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_flag;
@@ -151,7 +186,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS) linear_p
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const unsigned rank = gp_cta_rank();
     const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
-    const int nk = (K + GP_BK - 1) / GP_BK, tiles = tiles_m * tiles_n;
+    const int nk = (K + GP_BK - 1) / GP_BK;
 
     if (tid == 0) {
         abort_flag = 0;
@@ -176,17 +211,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS) linear_p
             const unsigned full_first = gp_map_to(gp_smem(&full[0]), 0);       // the first CTA's barriers
             int it = 0;
             bool ok = true;
-            for (int tile = cluster; tile < tiles && ok; tile += clusters) {
-                const int mt = tile % tiles_m, nt = tile / tiles_m;
-                const int row_x = mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM;
-                const int row_w = MODE == 0 ? nt * GP_BN + static_cast<int>(rank) * (GP_BN / 2)
-                                            : (rank == 0 ? nt * (GP_BN / 2) : inter + nt * (GP_BN / 2));
+            GpUnit u;
+            for (int i = 0; ok && gp_unit(plan, i, cluster, clusters, &u); ++i) {
+                const int half = (GP_BN / 2) / u.cut;             // rows of w this CTA brings per stage
+                const int row_x = u.mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM;
+                const int row_w = MODE == 1 ? (rank == 0 ? 0 : inter) + u.nt * (GP_BN / 2) + u.part * half
+                                            : u.nt * GP_BN + u.part * (2 * half) + static_cast<int>(rank) * half;
+                const CUtensorMap* wm = u.cut == 1 ? &w_map : (u.cut == 2 ? &w_map2 : &w_map4);
+                const unsigned bytes = 2u * (GP_BM + half) * GP_BK * sizeof(bf16);          // both CTAs' boxes
                 for (int kb = 0; kb < nk; ++kb, ++it) {
                     const int s = it % GP_STAGES;
                     if (it >= GP_STAGES && !gp_wait<false>(&empty[s], ((it / GP_STAGES) - 1) & 1, &abort_flag, status)) { ok = false; break; }
-                    if (rank == 0) gp_arrive_expect_tx(&full[s], 2 * GP_STAGE_BYTES);      // both CTAs' boxes
+                    if (rank == 0) gp_arrive_expect_tx(&full[s], bytes);
                     gp_tma_2d(a_s + s * TILE_ELEMS, &x_map, kb * GP_BK, row_x, full_first + s * 8);
-                    gp_tma_2d(b_s + s * TILE_ELEMS, &w_map, kb * GP_BK, row_w, full_first + s * 8);
+                    gp_tma_2d(b_s + s * TILE_ELEMS, wm, kb * GP_BK, row_w, full_first + s * 8);
                 }
             }
             if (!ok)                                              // let what is in flight land before the CTA goes away
@@ -195,13 +233,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS) linear_p
     } else if (warp == 1) {
         // ---- product issuer (first CTA of the pair) ----
         if (lane == 0 && rank == 0) {
-            constexpr unsigned IDESC = gp_idesc(2 * GP_BM, GP_BN);
             const unsigned long long ad0 = gp_desc(a_s), bd0 = gp_desc(b_s);
-            int it = 0, tcount = 0;
+            int it = 0;
             bool ok = true;
-            for (int tile = cluster; tile < tiles && ok; tile += clusters, ++tcount) {
-                const int buf = tcount & 1;
-                if (tcount >= 2 && !gp_wait<true>(&acc_empty[buf], ((tcount >> 1) - 1) & 1, &abort_flag, status)) break;
+            GpUnit u;
+            for (int i = 0; ok && gp_unit(plan, i, cluster, clusters, &u); ++i) {
+                const int buf = i & 1;
+                const unsigned idesc = gp_idesc(2 * GP_BM, GP_BN / u.cut);
+                if (i >= 2 && !gp_wait<true>(&acc_empty[buf], ((i >> 1) - 1) & 1, &abort_flag, status)) break;
                 gp_fence_after();
                 for (int kb = 0; kb < nk; ++kb, ++it) {
                     const int s = it % GP_STAGES;
@@ -211,67 +250,86 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS) linear_p
                     const unsigned long long bd = bd0 + static_cast<unsigned long long>(s) * (TILE_ELEMS * sizeof(bf16) >> 4);
 #pragma unroll
                     for (int k = 0; k < GP_BK / 16; ++k)          // 16 k-values = 32 bytes further along the swizzled row
-                        gp_mma_pair(tmem + buf * GP_BN, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) ? 1u : 0u);
+                        gp_mma_pair(tmem + buf * GP_BN, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
                     gp_commit_pair(&empty[s], 3);                 // the stage is free in both CTAs when these have run
                 }
                 if (ok) gp_commit_pair(&acc_full[buf], 3);
             }
         }
     } else {
-        // ---- epilogue: warps 2..5 of both CTAs, thread = one token = one TMEM lane ----
+        // ---- epilogue: warps 2..5 of both CTAs.  A thread reads one token's sums (one TMEM lane), 32
+        // columns at a time; the warp turns its 32 x 32 block through shared memory (16-byte chunks
+        // XOR-swizzled by the row) so that eight lanes write one token's 32 columns side by side ----
         const int quarter = warp & 3;                             // the TMEM lanes this warp may touch
         const unsigned lane_addr = static_cast<unsigned>(quarter * 32) << 16;
         const unsigned acc_empty_first = gp_map_to(gp_smem(&acc_empty[0]), 0);
-        int tcount = 0;
-        for (int tile = cluster; tile < tiles; tile += clusters, ++tcount) {
-            const int mt = tile % tiles_m, nt = tile / tiles_m, buf = tcount & 1;
-            if (!gp_wait<false>(&acc_full[buf], (tcount >> 1) & 1, &abort_flag, status)) break;
+        float4* turn = reinterpret_cast<float4*>(b_s + GP_STAGES * TILE_ELEMS) + (warp - 2) * (32 * 8);    // [32 rows][8 chunks]
+        const int out_n = MODE == 1 ? inter : N;
+        GpUnit u;
+        for (int i = 0; gp_unit(plan, i, cluster, clusters, &u); ++i) {
+            const int buf = i & 1;
+            if (!gp_wait<false>(&acc_full[buf], (i >> 1) & 1, &abort_flag, status)) break;
             gp_fence_after();
-            const int tok = mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM + quarter * 32 + lane;
+            const int tok0 = u.mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM + quarter * 32;       // the warp's first token
             const unsigned acc = tmem + lane_addr + buf * GP_BN;
-            if (MODE == 0) {
-                TO* row = y + static_cast<size_t>(tok) * N + static_cast<size_t>(nt) * GP_BN;
+            const int cols = GP_BN / u.cut;                       // accumulator columns of this unit
+            const int out_cols = MODE == 1 ? cols / 2 : cols;     // columns it writes
+            const int f0 = (MODE == 1 ? u.nt * (GP_BN / 2) : u.nt * GP_BN) + u.part * out_cols;
 #pragma unroll 1
-                for (int c = 0; c < GP_BN; c += 32) {
+            for (int c = 0; c < out_cols; c += 32) {
+                float v[32];
+                float4 old[8];                                    // MODE 2: what y holds, asked for before anything waits
+                if (MODE == 2) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int tok = tok0 + k * 4 + (lane >> 3), col = f0 + c + (lane & 7) * 4;
+                        old[k] = (tok < T && col < out_n)
+                                     ? *reinterpret_cast<const float4*>(y + static_cast<size_t>(tok) * out_n + col)
+                                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                }
+                if (MODE == 1) {
+                    unsigned g[32], up[32];
+                    gp_ld32(acc + c, g);
+                    gp_ld32(acc + out_cols + c, up);
+                    gp_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[e])));
+                        const float upv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[e])));
+                        v[e] = gp_silu(gate) * upv;
+                    }
+                } else {
                     unsigned r[32];
                     gp_ld32(acc + c, r);
                     gp_ld_wait();
-                    if (tok < T) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            if (nt * GP_BN + c + j < N) {         // N is a multiple of 8
-                                float v[8];
+                    for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+                }
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                                store8(row + c + j, v);
-                            }
+                for (int j = 0; j < 8; ++j)
+                    turn[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int rl = k * 4 + (lane >> 3), q = lane & 7;
+                    float4 val = turn[rl * 8 + (q ^ (rl & 7))];
+                    const int tok = tok0 + rl, col = f0 + c + q * 4;
+                    if (tok < T && col < out_n) {                 // out_n is a multiple of 8
+                        TO* dst = y + static_cast<size_t>(tok) * out_n + col;
+                        if constexpr (sizeof(TO) == 4) {
+                            if (MODE == 2) { val.x += old[k].x; val.y += old[k].y; val.z += old[k].z; val.w += old[k].w; }
+                            *reinterpret_cast<float4*>(dst) = val;
+                        } else {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(val.x, val.y), hi = __floats2bfloat162_rn(val.z, val.w);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<unsigned*>(&lo);
+                            packed.y = *reinterpret_cast<unsigned*>(&hi);
+                            *reinterpret_cast<uint2*>(dst) = packed;
                         }
                     }
                 }
-            } else {
-                bf16* row = reinterpret_cast<bf16*>(y) + static_cast<size_t>(tok) * inter + static_cast<size_t>(nt) * (GP_BN / 2);
-#pragma unroll 1
-                for (int c = 0; c < GP_BN / 2; c += 32) {
-                    unsigned g[32], u[32];
-                    gp_ld32(acc + c, g);
-                    gp_ld32(acc + GP_BN / 2 + c, u);
-                    gp_ld_wait();
-                    if (tok < T) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            if (nt * (GP_BN / 2) + c + j < inter) {
-                                float v[8];
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + e])));
-                                    const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + e])));
-                                    v[e] = gp_silu(gate) * up;
-                                }
-                                store8(row + c + j, v);
-                            }
-                        }
-                    }
-                }
+                __syncwarp();
             }
             gp_fence_before();
             __syncwarp();
@@ -313,12 +371,12 @@ static bool gp_ready() {
     return g_gp_state > 0;
 }
 
-// A [rows, cols] bfloat16 matrix, row-major, read in boxes of 128 rows x 64 columns (128-byte swizzle);
-// rows and columns past the end read as zero.
-static bool gp_encode(CUtensorMap* map, const void* base, long long rows, long long cols) {
+// A [rows, cols] bfloat16 matrix, row-major, read in boxes of box_rows rows x 64 columns (128-byte
+// swizzle); rows and columns past the end read as zero.
+static bool gp_encode(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(bf16)};
-    const cuuint32_t box[2] = {GP_BK, GP_BM};
+    const cuuint32_t box[2] = {GP_BK, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[2] = {1u, 1u};
     return g_gp_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -330,35 +388,78 @@ extern "C" int llm_linear_pair_supported(int T, int N, int K) {
     return T >= 1 && N >= 8 && K >= 8 && (K % 8) == 0 && (N % 8) == 0;
 }
 
+// Whole tiles for as many full rounds of all clusters as there are; the tiles left over are cut 1, 2 or 4
+// ways along the features, whichever ends soonest (a unit of a tile cut n ways counts as 1/n of a round;
+// four ways only if GP_MAX_CUT allows it).
+static void gp_make_plan(int tiles_m, int tiles_n, GpPlan* plan, int* clusters) {
+    const int tiles = tiles_m * tiles_n, slots = g_gp_sms / 2;
+    const int whole = tiles >= slots ? (tiles / slots) * slots : 0, rest = tiles - whole;
+    int cut = 1;
+    for (int c = 2; c <= GP_MAX_CUT; c *= 2)                      // strictly sooner, else the wider unit
+        if (((rest * c + slots - 1) / slots) * cut < ((rest * cut + slots - 1) / slots) * c) cut = c;
+    plan->tiles_m = tiles_m;
+    plan->tiles = tiles;
+    plan->whole = whole;
+    plan->cut = cut;
+    *clusters = whole > 0 ? slots : (rest * cut < slots ? rest * cut : slots);
+}
+
+// How full the clusters are kept by a product of T tokens and N output features (gate/up mode: N =
+// inter), in thousandths: the tiles' share of the time that the rounds of the plan take.  0 if the
+// device or the sizes are not taken.
+extern "C" int llm_linear_pair_efficiency(int T, int N, int K, int gate_up) {
+    if (!llm_linear_pair_supported(T, N, K) || !gp_ready()) return 0;
+    const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
+    const int per_tile = gate_up ? GP_BN / 2 : GP_BN;
+    const long long tiles_n = (N + per_tile - 1) / per_tile;
+    if (tiles_m * tiles_n > (1LL << 28)) return 0;
+    GpPlan plan;
+    int clusters;
+    gp_make_plan(tiles_m, static_cast<int>(tiles_n), &plan, &clusters);
+    const int slots = g_gp_sms / 2, rest = plan.tiles - plan.whole;
+    const double rounds = plan.whole / slots + static_cast<double>((rest * plan.cut + slots - 1) / slots) / plan.cut;
+    const double work = static_cast<double>(T) * N / (2.0 * GP_BM * per_tile) / slots;
+    return static_cast<int>(1000.0 * work / rounds);
+}
+
 template <int MODE, typename TO>
 static int gp_launch(const bf16* x, const bf16* w, void* y, int T, int N, int K, int inter, long long w_rows, int32_t* status,
                      cudaStream_t s) {
-    CUtensorMap x_map, w_map;
-    if (!gp_encode(&x_map, x, T, K) || !gp_encode(&w_map, w, w_rows, K)) return LLM_REFUSED_SIZE;
+    CUtensorMap x_map, w_map, w_map2, w_map4;
+    if (!gp_encode(&x_map, x, T, K, GP_BM) || !gp_encode(&w_map, w, w_rows, K, GP_BN / 2) ||
+        !gp_encode(&w_map2, w, w_rows, K, GP_BN / 4) || !gp_encode(&w_map4, w, w_rows, K, GP_BN / 8))
+        return LLM_REFUSED_SIZE;
     const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
-    const int tiles_n = MODE == 0 ? (N + GP_BN - 1) / GP_BN : (inter + GP_BN / 2 - 1) / (GP_BN / 2);
-    const long long tiles = static_cast<long long>(tiles_m) * tiles_n;
-    const int clusters = static_cast<int>(tiles < g_gp_sms / 2 ? tiles : g_gp_sms / 2);
-    const size_t smem = static_cast<size_t>(GP_STAGES) * GP_STAGE_BYTES + 1024;
+    const int tiles_n = MODE == 1 ? (inter + GP_BN / 2 - 1) / (GP_BN / 2) : (N + GP_BN - 1) / GP_BN;
+    if (static_cast<long long>(tiles_m) * tiles_n > (1LL << 28)) return LLM_REFUSED_SIZE;
+    GpPlan plan;
+    int clusters;
+    gp_make_plan(tiles_m, tiles_n, &plan, &clusters);
+    const size_t smem = static_cast<size_t>(GP_STAGES) * GP_STAGE_BYTES + 4 * 32 * 32 * sizeof(float) + 1024;   // stages, the epilogue's four blocks, alignment
     auto kern = linear_pair_tcgen05_kernel<MODE, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    launch_pdl(kern, dim3(2 * clusters), dim3(GP_THREADS), smem, s, x_map, w_map, static_cast<TO*>(y), T, N, K, inter, tiles_m,
-               tiles_n, status);
+    launch_pdl(kern, dim3(2 * clusters), dim3(GP_THREADS), smem, s, x_map, w_map, w_map2, w_map4, static_cast<TO*>(y), T, N, K,
+               inter, plan, status);
     return launch_status();
 }
 
-// x: bfloat16 [T, K]; w: bfloat16 [N, K]; y: [T, N] float32 (out_dtype 0) or bfloat16 (1).
-extern "C" int llm_linear_pair(const void* x, const void* w, void* y, int out_dtype, int T, int N, int K, int32_t* status,
-                               uintptr_t stream) {
+// x: bfloat16 [T, K]; w: bfloat16 [N, K]; y: [T, N] float32 (out_dtype 0) or bfloat16 (1).  accumulate: y (float32)
+// holds a summand already and the product is added to it.
+extern "C" int llm_linear_pair(const void* x, const void* w, void* y, int out_dtype, int accumulate, int T, int N, int K,
+                               int32_t* status, uintptr_t stream) {
     if (!llm_linear_pair_supported(T, N, K)) return LLM_REFUSED_SIZE;
     if (!aligned16(x) || !aligned16(w) || !aligned16(y) || status == nullptr) return LLM_REFUSED_ALIGN;
     if (!gp_ready()) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (out_dtype == LLM_DT_F32)
-        return gp_launch<0, float>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), y, T, N, K, 0, N, status, s);
-    if (out_dtype == LLM_DT_BF16)
-        return gp_launch<0, bf16>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), y, T, N, K, 0, N, status, s);
+    const bf16* xp = static_cast<const bf16*>(x);
+    const bf16* wp = static_cast<const bf16*>(w);
+    if (accumulate) {
+        if (out_dtype != LLM_DT_F32) return LLM_REFUSED_DTYPE;
+        return gp_launch<2, float>(xp, wp, y, T, N, K, 0, N, status, s);
+    }
+    if (out_dtype == LLM_DT_F32) return gp_launch<0, float>(xp, wp, y, T, N, K, 0, N, status, s);
+    if (out_dtype == LLM_DT_BF16) return gp_launch<0, bf16>(xp, wp, y, T, N, K, 0, N, status, s);
     return LLM_REFUSED_DTYPE;
 }
 

@@ -574,10 +574,13 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 
 
 def linear_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
     """x [T, K] @ weight[N, K]^T for prompt portions with the engine's own tcgen05 kernel, in which
     two CTAs of a cluster share a tile of 256 tokens x 256 features (bfloat16 operands, float32
-    accumulation in tensor memory, float32 or bfloat16 result)."""
+    accumulation in tensor memory, float32 or bfloat16 result).  With `accumulate` the product is
+    added to the float32 `out` in place."""
+    if accumulate and (out is None or out.dtype != torch.float32):
+        raise KernelError("accumulating wants a float32 out")
     _dev(x, weight, out)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError("the paired product takes bfloat16 operands")
@@ -587,8 +590,12 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         raise KernelError("x and weight disagree on K")
     if out is None:
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
-    f = _fn("gemm_pair_tcgen05", "llm_linear_pair", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), T, N, K, _ptr(stream_status(x.device)), _stream()), "linear_pair")
+    if out.shape != (T, N) or not out.is_contiguous():
+        raise KernelError("out must be a contiguous [T, N]")
+    f = _fn("gemm_pair_tcgen05", "llm_linear_pair",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(out), _dt(out), 1 if accumulate else 0, T, N, K, _ptr(stream_status(x.device)),
+             _stream()), "linear_pair")
     return out
 
 
@@ -610,13 +617,56 @@ def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional
     return out
 
 
+_PAIR_POLICY = os.environ.get("LLM_PAIR", "auto")       # auto | all | off: which prompt-portion products take the paired kernel
+PAIR_MIN_ROWS = 129                                      # fewer rows leave the second CTA of a pair idle
+# Thousandths of the clusters' time that a product's tiles must fill for the paired kernel to be taken
+# under `auto`.  With the activation in its epilogue it saves a kernel and wins from 0.85 on (a
+# 2,048-token prefill of the Qwen3-8B shape: 27.7 ms against 28.5).  Alone it is level with the library
+# at 0.87 and ahead at 0.99.  Adding into the residual was slower inside a whole prefill (28.9 ms: under
+# the power cap the clocks settle lower than with the library's kernels) and is left to `all`.
+_PAIR_NEEDS = {"plain": 960, "silu": 850, "into": None}
+
+
+def _pair_takes(x: torch.Tensor, weight: torch.Tensor, n: int, kind: str) -> bool:
+    """Whether the paired tcgen05 product is the faster way for these operands: bfloat16 on the GPU,
+    enough rows, and tiles that keep the clusters busy."""
+    if (_PAIR_POLICY == "off" or not x.is_cuda or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16
+            or x.shape[0] < PAIR_MIN_ROWS or not x.is_contiguous() or not weight.is_contiguous()):
+        return False
+    eff = _fn("gemm_pair_tcgen05", "llm_linear_pair_efficiency", [c_int, c_int, c_int, c_int])(
+        x.shape[0], n, x.shape[1], 1 if kind == "silu" else 0)
+    if eff <= 0:
+        return False
+    need = _PAIR_NEEDS[kind]
+    return _PAIR_POLICY == "all" or (need is not None and eff >= need)
+
+
+def linear_into(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> bool:
+    """residual (float32 [T, N]) += x @ weight^T in the product's epilogue, if the paired kernel takes
+    these operands; False, and nothing done, if not."""
+    if (residual.dtype != torch.float32 or not residual.is_contiguous() or residual.shape != (x.shape[0], weight.shape[0])
+            or not _pair_takes(x, weight, weight.shape[0], "into")):
+        return False
+    linear_pair(x, weight, torch.float32, out=residual, accumulate=True)
+    return True
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype):
+    """silu(x @ gate^T) * (x @ up^T) for w_gate_up = [gate; up]: one kernel where the paired product
+    takes it, else the product (which may stay a sum of k-splits) followed by the activation kernel."""
+    if out_dtype == torch.bfloat16 and _pair_takes(x, w_gate_up, w_gate_up.shape[0] // 2, "silu"):
+        return linear_pair_silu_mul(x, w_gate_up)
+    return silu_and_mul(linear(x, w_gate_up, out_dtype=out_dtype, partials_ok=True))
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            partials_ok: bool = False):
     """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's
     own weight-streaming kernel: alone it is level with the library for N = 4096..24576 and
     faster for K = 12288 (32 us against 36) and N = 151936 (203 against 218), and in a step it
     starts fetching weights while the kernel before it drains (a whole decode step of the
-    Qwen3-8B shape at batch 8: 4.35 ms against 4.77 with the library products).  Everything else
+    Qwen3-8B shape at batch 8: 4.35 ms against 4.77 with the library products).  Prompt portions
+    whose tiles keep the clusters busy take the paired tcgen05 product (`linear_pair`).  Everything else
     goes through the library matrix product (the reference uses cuBLAS for all its products,
     src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a float32 weight
     keeps its product in true float32 (no TF32), whatever x is."""
@@ -628,6 +678,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
             and x.shape[1] % 8 == 0 and _STREAM_POLICY == "on" and weight.data_ptr() in _tiled):
         return linear_stream(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
+    if x.shape[0] >= PAIR_MIN_ROWS and (out_dtype or x.dtype) in (torch.float32, torch.bfloat16) and _pair_takes(
+            x, weight, weight.shape[0], "plain"):
+        return linear_pair(x, weight, out_dtype or x.dtype)
     if weight.dtype == torch.float32:
         y = torch.mm(x if x.dtype == torch.float32 else x.float(), weight.t())
         want = out_dtype or x.dtype

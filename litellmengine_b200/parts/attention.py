@@ -95,6 +95,9 @@ class AttentionMixer:
             ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype)
         a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
         # joins the float32 residual; may stay a sum of k-splits if the layer's norm adds them itself
+        residual = getattr(ctx, "residual", None)
+        if residual is not None and ops.linear_into(a, self.w_o, residual):
+            return None                                           # added to the residual in the product's epilogue
         return ops.linear(a, self.w_o, out_dtype=torch.float32, partials_ok=getattr(ctx, "partials_ok", False))
 
 

@@ -51,18 +51,22 @@ def pre_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: 
     """h += mixer(norm1(h)); h += ffn(norm2(h))  (src/model/qwen3.cpp:948-968).
 
     `h` is the float32 residual stream; `delta` is the previous layer's feed-forward output
-    that has not been added yet.  Each add is fused into the norm that follows it, so the
-    layer returns its own feed-forward output as the next pending delta.
+    that has not been added yet (None if nothing is pending).  Each add is fused into the norm
+    that follows it, so the layer returns its own feed-forward output as the next pending delta,
+    unless the part added it to `h` itself (in the epilogue of its last product).
     """
     from ..csrc import ops
     if not getattr(block.mixer_norm, "accepts_partials", False):
         delta = ops.as_tensor(delta)
     x = block.mixer_norm.forward(h, block.dtype, delta=delta, write_sum=delta is not None)
     ctx.partials_ok = getattr(block.feed_forward_norm, "accepts_partials", False)
+    ctx.residual = h                                            # a part may add its result here itself and return None
     a = block.mixer.forward(x, ctx)
-    y = block.feed_forward_norm.forward(h, block.dtype, delta=a, write_sum=True)
+    y = block.feed_forward_norm.forward(h, block.dtype, delta=a, write_sum=a is not None)
+    extra = {}
     if getattr(block.feed_forward, "supports_partials", False):
-        f = block.feed_forward.forward(y, partials_ok=True)     # the next norm (or `pre_norm` above) adds the splits
-    else:
-        f = block.feed_forward.forward(y)
+        extra["partials_ok"] = True                             # the next norm (or `pre_norm` above) adds the splits
+    if getattr(block.feed_forward, "supports_residual", False):
+        extra["residual"] = h
+    f = block.feed_forward.forward(y, **extra)
     return h, f

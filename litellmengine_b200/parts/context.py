@@ -23,6 +23,9 @@ class StageContext:
     status       device int32 [2] where kernels record a refused index instead of trapping.
     partials_ok  True when whoever consumes the mixer's output adds up an `ops.PartialSum`
                  itself, so the mixer may return one instead of a tensor.
+    residual     the float32 residual stream [T, hidden] that the mixer's result is about to be
+                 added to, if the arrangement offers it: a mixer may add its result there itself
+                 (in the epilogue of its last product) and return None.
     """
     batch: Any
     stage: int
@@ -33,3 +36,4 @@ class StageContext:
     state: Optional[torch.Tensor]
     status: torch.Tensor
     partials_ok: bool = False
+    residual: Optional[torch.Tensor] = None

@@ -39,8 +39,10 @@ class SwiGLU:
         ops.prepare_streaming(self.w_down)
 
     supports_partials = True   # forward(x, partials_ok=True) may return an ops.PartialSum
+    supports_residual = True   # forward(x, residual=h) may add its result to h itself and return None
 
-    def forward(self, x: torch.Tensor, partials_ok: bool = False):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=self.dtype, partials_ok=True)     # silu_and_mul adds the slices
-        return ops.linear(ops.silu_and_mul(gu), self.w_down, out_dtype=torch.float32,
-                          partials_ok=partials_ok)                                    # joins the residual
+    def forward(self, x: torch.Tensor, partials_ok: bool = False, residual: Optional[torch.Tensor] = None):
+        act = ops.linear_silu_mul(x, self.w_gate_up, self.dtype)
+        if residual is not None and ops.linear_into(act, self.w_down, residual):
+            return None                                                               # joined the residual in the product
+        return ops.linear(act, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok)

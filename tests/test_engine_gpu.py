@@ -188,3 +188,27 @@ def test_one_layer_at_real_widths():
         runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=rh.peak_tokens(steps, page), max_requests=4,
                                 max_tokens_per_step=256)
         rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.BF16_TOL, f"wide {what}")
+
+
+@pytest.mark.parametrize("policy", ["all", "off"])
+def test_prompt_portions_through_the_paired_product(policy, monkeypatch):
+    """Portions of 129 tokens and more in bfloat16 with every product they allow forced through the
+    paired tcgen05 kernel (the activation in the gate/up product's epilogue, the attention's and the
+    feed-forward's last products added to the residual where it lies), and with that kernel off:
+    both against the plain code, whole and cut into portions that are no multiple of its tiles."""
+    from litellmengine_b200.csrc import ops
+    monkeypatch.setattr(ops, "_PAIR_POLICY", policy)
+    before = ops.launch_count
+    for cfg, seed, page, lens in ((tm.TINY_E, tm.TINY_E_SEED, tm.TINY_E_PAGE, [300, 140]),
+                                  (tm.WIDE_G, tm.WIDE_G_SEED, tm.WIDE_G_PAGE, [260, 131])):
+        w = tm.make_weights(cfg, seed, bf16_exact=True, matrix_std=0.02)
+        reqs = rh.requests_for(cfg, lens, seed)
+        ref = rh.plain_rows(cfg, w, reqs, "bfloat16")
+        for what, steps in (("whole", rh.trace_whole(reqs)), ("portions", rh.trace_portions(reqs, seed=5, sizes=(129, 133, 170)))):
+            runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=rh.peak_tokens(steps, page), max_requests=4,
+                                    max_tokens_per_step=512)
+            rh.assert_rows_match(rh.run_trace(runner, steps), ref, rh.BF16_TOL, f"paired product {policy} {what}")
+    assert ops.launch_count > before
+    if policy == "all":
+        assert any("gemm_pair_tcgen05" in name for name in ops.loaded_libraries())
+

@@ -516,11 +516,13 @@ def test_stream_tcgen05_product(T, N, K, out_dtype):
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,N,K", [(256, 256, 64), (128, 64, 512), (300, 520, 136), (513, 1000, 1544), (17, 8, 8),
-                                   (1100, 776, 448), (2048, 1024, 4096), (260, 6144, 640)])
+                                   (1100, 776, 448), (2048, 1024, 4096), (260, 6144, 640), (2048, 2560, 128),
+                                   (512, 9472, 64), (4000, 2552, 200)])
 def test_paired_tcgen05_product(T, N, K, out_dtype):
     """The product that two CTAs of a cluster compute together (256 tokens x 256 features a tile)
-    against float64, at sizes that are no multiple of its tiles, with one tile and with several
-    tiles per cluster (both accumulators, the ring of stages wrapping)."""
+    against float64, at sizes that are no multiple of its tiles; with fewer tiles than clusters (cut
+    four and two ways), exactly one round of whole tiles, and whole rounds followed by cut tiles
+    (both accumulators, the ring of stages wrapping, units of 256, 128 and 64 columns in one launch)."""
     torch.manual_seed(T * 1000 + N)
     x = torch.randn(T, K).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
@@ -528,10 +530,15 @@ def test_paired_tcgen05_product(T, N, K, out_dtype):
     got = ops().linear_pair(x.to(DEV), w.to(DEV), DT[out_dtype])
     assert got.dtype == DT[out_dtype] and got.shape == (T, N)
     close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    if out_dtype == "float32":                              # added onto a float32 tensor in place
+        base = torch.randn(T, N)
+        acc = ops().linear_pair(x.to(DEV), w.to(DEV), torch.float32, out=base.to(DEV), accumulate=True)
+        assert torch.equal(acc, base.to(DEV) + got)
     assert ops().stream_status(DEV).tolist() == [0, 0]
 
 
-@pytest.mark.parametrize("T,inter,K", [(256, 128, 64), (300, 264, 136), (700, 1000, 520), (130, 8, 64), (2048, 3072, 1024)])
+@pytest.mark.parametrize("T,inter,K", [(256, 128, 64), (300, 264, 136), (700, 1000, 520), (130, 8, 64), (2048, 3072, 1024),
+                                       (2048, 1280, 128), (520, 4736, 64)])
 def test_paired_tcgen05_gate_up_product(T, inter, K):
     """The same with silu(gate) * up in its epilogue: bit for bit what the bfloat16 product followed
     by the separate activation kernel gives when both add in the same order; checked here against
