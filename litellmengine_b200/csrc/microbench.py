@@ -155,8 +155,9 @@ def main():
         qkv = torch.randn(args.tokens, (nq + 2 * nkv) * d, device=dev)
         w = torch.ones(d, device=dev)
         inv = torch.rand(d // 2, device=dev)
+        angles = ops.rope_angles(pos, inv) if args.tokens >= ops.ROPE_TABLE_MIN_TOKENS and args.impl != "own" else None
         fn = lambda: ops.qk_norm_rope_kv_write(qkv, cache, pos, ent, slot, table, w, w, 1e-6, inv, d, nq, nkv, d, P,
-                                               True, status, q_dtype=torch.bfloat16)
+                                               True, status, q_dtype=torch.bfloat16, angles=angles)
         res.update(tokens=args.tokens, bytes=args.tokens * (nq + 2 * nkv) * d * (4 + 2))
     elif args.kernel == "silu_and_mul":
         gu = torch.randn(args.tokens, 2 * args.inter, device=dev, dtype=torch.bfloat16)

@@ -212,10 +212,11 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
                           block_table: Optional[torch.Tensor], q_norm_w, k_norm_w, eps: float, inv_freq,
                           rotary_dim: int, nq: int, nkv: int, d: int, page_size: int, has_kv: bool,
                           status: torch.Tensor, q_out: Optional[torch.Tensor] = None,
-                          q_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                          q_dtype: Optional[torch.dtype] = None, angles: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Normalise and rotate q and k, write k and v into the cache pages, return q [T, nq*d]
     in `q_dtype` (default: qkv's).
-    cache: [num_pages, 2, nkv, page_size, d] of one stage (None with has_kv False)."""
+    cache: [num_pages, 2, nkv, page_size, d] of one stage (None with has_kv False).
+    angles: the step's table from `rope_angles`, which saves every layer the sines and cosines."""
     parts, part_stride = 1, 0
     if isinstance(qkv, PartialSum):
         parts, part_stride = qkv.parts.shape[0], qkv.parts.stride(0)
@@ -236,21 +237,40 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
             raise KernelError("q/k norm weight must be float32 [head_dim]")
     if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim):
         raise KernelError("inv_freq must be float32 [rotary_dim/2]")
+    if angles is not None and (inv_freq is None or angles.dtype != torch.float32 or not angles.is_contiguous()
+                               or tuple(angles.shape) != (T, inv_freq.numel(), 2)):
+        raise KernelError("angles must be float32 [T, rotary_dim/2, 2] from rope_angles")
     if q_out is None:
         q_out = torch.empty((T, nq * d), dtype=q_dtype or qkv.dtype, device=qkv.device)
     f = _fn("rope_cache", "llm_qk_norm_rope_kv_write",
             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_int, c_longlong, c_void_p])
+             c_void_p, c_int, c_longlong, c_void_p, c_void_p])
     _check(f(_ptr(qkv), _dt(qkv), _ptr(q_out), _dt(q_out), _ptr(cache),
              _dt(cache) if cache is not None else _dt(q_out),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table),
              block_table.shape[1] if block_table is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
              _ptr(inv_freq), rotary_dim if inv_freq is not None else 0, T, nq, nkv, d, page_size,
              1 if has_kv else 0, cache.shape[0] if cache is not None else 0, _ptr(status), parts, part_stride,
-             _stream()),
+             _ptr(angles), _stream()),
            "qk_norm_rope_kv_write")
     return q_out
+
+
+ROPE_TABLE_MIN_TOKENS = 64     # steps of fewer tokens compute their angles inside the kernel, before it waits
+
+
+def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(sin, cos) of float32(position) * inv_freq for every token of a step: float32 [T, rotary_dim/2, 2],
+    computed once for all layers (a prompt portion's rotation kernel is bound by its instructions, and
+    most of them are these)."""
+    _dev(positions, inv_freq)
+    _i32(positions, "positions")
+    T, half = positions.numel(), inv_freq.numel()
+    out = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    f = _fn("rope_cache", "llm_rope_angles", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(positions), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rope_angles")
+    return out
 
 
 def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, positions, token_entry, entry_slot,

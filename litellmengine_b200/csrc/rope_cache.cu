@@ -131,7 +131,8 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int num_tokens, int nq, int nkv, int page_size, int has_kv,
-    int num_pages, int32_t* __restrict__ status, int qkv_parts, long long qkv_part_stride) {
+    int num_pages, int32_t* __restrict__ status, int qkv_parts, long long qkv_part_stride,
+    const float4* __restrict__ angles) {
     constexpr int N = D / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
@@ -147,7 +148,14 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
     // block table and the weights (position, sines and cosines, norm weights, the page).
     const int pos = positions[t];
     float sn[N], cs[N], wq[N], wk[N];
-    if (inv_freq) {
+    if (angles) {                                                        // the step's table: (sin, cos) pairs [T][D/2]
+        const float4* a = angles + (static_cast<size_t>(t) * (D / 2) + (e0 & (D / 2 - 1))) / 2;
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float4 v = a[i / 2];
+            sn[i] = v.x; cs[i] = v.y; sn[i + 1] = v.z; cs[i + 1] = v.w;
+        }
+    } else if (inv_freq) {
 #pragma unroll
         for (int i = 0; i < N; ++i) sincosf(static_cast<float>(pos) * inv_freq[(e0 + i) & (D / 2 - 1)], &sn[i], &cs[i]);
     }
@@ -196,7 +204,7 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
 #pragma unroll
             for (int i = 0; i < N; ++i) x[j][i] = x[j][i] * inv * (is_q ? wq[i] : wk[i]);
         }
-        if ((is_q || is_k) && inv_freq) {
+        if ((is_q || is_k) && (inv_freq || angles)) {
 #pragma unroll
             for (int i = 0; i < N; ++i) {
                 const float other = __shfl_xor_sync(0xffffffffu, x[j][i], 16);
@@ -221,25 +229,54 @@ static void launch_rope_vec(const void* qkv, void* q_out, void* cache, const int
                             const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
                             int table_stride, const float* q_norm_w, const float* k_norm_w, float eps,
                             const float* inv_freq, int num_tokens, int nq, int nkv, int page_size, int has_kv,
-                            int num_pages, int32_t* status, int qkv_parts, long long qkv_part_stride, cudaStream_t s) {
+                            int num_pages, int32_t* status, int qkv_parts, long long qkv_part_stride, const float* angles,
+                            cudaStream_t s) {
     const int heads_total = nq + (has_kv ? 2 * nkv : 0);
     const long long items = static_cast<long long>(num_tokens) * ((heads_total + HPW - 1) / HPW);
     const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
     launch_pdl((qk_norm_rope_kv_write_vec_kernel<D, HPW, TI, T, TC>), dim3(blocks), dim3(RC_WARPS * 32), 0, s,
                static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions, token_entry,
                entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv,
-               page_size, has_kv, num_pages, status, qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride);
+               page_size, has_kv, num_pages, status, qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride,
+               reinterpret_cast<const float4*>(angles));
+}
+
+// The sines and cosines of a step, once for all its layers: out[t][i] = (sin, cos)(float(positions[t]) * inv_freq[i]),
+// the same float32 expressions as inside the kernels above.  It does not let the next kernel start early:
+// every later kernel of the step then starts after this one has finished and may read the table before its
+// own griddepcontrol.wait.
+__global__ void rope_angles_kernel(const int32_t* __restrict__ positions, const float* __restrict__ inv_freq,
+                                   float2* __restrict__ out, int num_tokens, int half) {
+    pdl_wait();
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(num_tokens) * half) return;
+    float sn, cs;
+    sincosf(static_cast<float>(positions[i / half]) * inv_freq[i % half], &sn, &cs);
+    out[i] = make_float2(sn, cs);
+}
+
+extern "C" int llm_rope_angles(const int32_t* positions, const float* inv_freq, float* out, int num_tokens, int half,
+                               uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (half <= 0) return LLM_REFUSED_SIZE;
+    const long long n = static_cast<long long>(num_tokens) * half;
+    launch_pdl(rope_angles_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+               reinterpret_cast<cudaStream_t>(stream), positions, inv_freq, reinterpret_cast<float2*>(out), num_tokens, half);
+    return launch_status();
 }
 
 // qkv: [T, heads_total * d] (qkv_dtype); q_out: [T, nq * d] (q_dtype); cache (cache_dtype).
+// angles: nullptr, or the step's table from llm_rope_angles ([T][d/2] pairs; used when the whole head is rotated
+// and the head size is 64 or 128, ignored otherwise).
 extern "C" int llm_qk_norm_rope_kv_write(
     const void* qkv, int qkv_dtype, void* q_out, int q_dtype, void* cache, int cache_dtype,
     const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rotary_dim,
     int num_tokens, int nq, int nkv, int d, int page_size, int has_kv, int num_pages, int32_t* status,
-    int qkv_parts, long long qkv_part_stride, uintptr_t stream) {
+    int qkv_parts, long long qkv_part_stride, const float* angles, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
+    if (inv_freq == nullptr) angles = nullptr;
     if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || rotary_dim < 0 || rotary_dim > d ||
         (rotary_dim & 1))
         return LLM_REFUSED_SIZE;
@@ -259,11 +296,11 @@ extern "C" int llm_qk_norm_rope_kv_write(
     // the register kernel: head size 64 or 128 rotated whole, 16-byte aligned rows, float32 projection
     const bool whole = inv_freq == nullptr || rotary_dim == d;
     if ((d == 64 || d == 128) && whole && (key == 0 || key == 3) && aligned16(qkv) && aligned16(q_out) &&
-        aligned16(cache) && (qkv_part_stride % 4) == 0 && aligned16(q_norm_w) && aligned16(k_norm_w)) {
+        aligned16(cache) && (qkv_part_stride % 4) == 0 && aligned16(q_norm_w) && aligned16(k_norm_w) && aligned16(angles)) {
 #define VEC(D, HPW)                                                                                           \
     do {                                                                                                      \
-        if (key == 0) launch_rope_vec<D, HPW, float, float, float>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, s); \
-        else launch_rope_vec<D, HPW, float, bf16, bf16>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, s); \
+        if (key == 0) launch_rope_vec<D, HPW, float, float, float>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, angles, s); \
+        else launch_rope_vec<D, HPW, float, bf16, bf16>(qkv, q_out, cache, positions, token_entry, entry_slot, block_table, table_stride, q_norm_w, k_norm_w, eps, inv_freq, num_tokens, nq, nkv, page_size, has_kv, num_pages, status, qkv_parts, qkv_part_stride, angles, s); \
     } while (0)
         const bool many = num_tokens >= 64;                              // few tokens: one head per warp keeps more warps busy
         if (d == 128) { if (many) VEC(128, 4); else VEC(128, 1); }

@@ -130,6 +130,7 @@ class StepBatch:
     entries: List[StepEntry] = field(default_factory=list)
     feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
     layout: str = "large"                     # which of StepBuffers' two layouts holds this step's arrays
+    tables: dict = field(default_factory=dict)   # what parts compute once a step and share between layers
 
 
 def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,

@@ -92,7 +92,8 @@ class AttentionMixer:
             self.q_norm.weight if self.q_norm is not None else None,
             self.k_norm.weight if self.k_norm is not None else None, eps,
             self.position.inv_freq, self.position.rotary_dim, self.nq, self.nkv, self.d,
-            ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype)
+            ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype,
+            angles=self.position.angles(b) if hasattr(self.position, "angles") else None)
         a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
         # joins the float32 residual; may stay a sum of k-splits if the layer's norm adds them itself
         residual = getattr(ctx, "residual", None)

@@ -14,6 +14,9 @@ class NoPosition:
         self.inv_freq = None
         self.rotary_dim = 0
 
+    def angles(self, batch):
+        return None
+
 
 @register_position("rope")
 class RotaryPosition:
@@ -37,3 +40,18 @@ class RotaryPosition:
         theta32 = torch.tensor(spec.theta, dtype=torch.float32)
         inv = torch.pow(theta32.double(), expo.double()).to(torch.float32)
         self.inv_freq = inv.to(device).contiguous()
+        self._key = ("rope", float(spec.theta), rd)
+        self._table_ok = rd == head_dim and head_dim in (64, 128)      # what the kernel that reads the table takes
+
+    def angles(self, batch):
+        """The step's table of sines and cosines, made by the first layer that asks and shared by
+        all layers with the same theta and rotary_dim; None for steps of few tokens, whose kernels
+        compute their own before they wait for the projection."""
+        from ..csrc import ops
+        tables = getattr(batch, "tables", None)
+        if (tables is None or not self._table_ok or batch.num_tokens < ops.ROPE_TABLE_MIN_TOKENS
+                or not self.inv_freq.is_cuda):
+            return None
+        if self._key not in tables:
+            tables[self._key] = ops.rope_angles(batch.positions, self.inv_freq)
+        return tables[self._key]

@@ -161,6 +161,16 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, rot, T):
         for r in range(page):
             if (pg, r) not in touched:
                 assert c[pg, :, :, r].abs().sum() == 0, "a row nobody owns was written"
+    # with the step's table of sines and cosines instead of its own: the same bits
+    angles = ops().rope_angles(pos.to(DEV), inv.to(DEV))
+    ang = pos.float()[:, None] * inv[None, :]
+    close(angles[..., 0], torch.sin(ang.double()), 1e-6)
+    close(angles[..., 1], torch.cos(ang.double()), 1e-6)
+    cache2 = torch.zeros_like(cache)
+    q2 = ops().qk_norm_rope_kv_write(qkv.to(DEV), cache2, pos.to(DEV), entry.to(DEV), slots.to(DEV), table.to(DEV),
+                                     qw.to(DEV), kw.to(DEV), eps, inv.to(DEV), rot, nq, nkv, d, page, True, st,
+                                     q_dtype=DT[dtype], angles=angles)
+    assert torch.equal(q2, q) and torch.equal(cache2, cache)
 
 
 def _rope_custom(x, pos, inv):
