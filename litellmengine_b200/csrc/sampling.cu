@@ -37,7 +37,17 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
 
 __device__ MaxIdx block_argmax(const float* __restrict__ row, int vocab, MaxIdx* sh) {
     MaxIdx best = {-CUDART_INF_F, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    int i = threadIdx.x;
+    const int step = blockDim.x;
+    for (; i + 7 * step < vocab; i += 8 * step) {                        // eight loads in flight, then the comparisons in index order
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = row[i + k * step];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (v[k] > best.v || (v[k] == best.v && i + k * step < best.i)) best = {v[k], i + k * step};
+    }
+    for (; i < vocab; i += step) {
         const float v = row[i];
         if (v > best.v || (v == best.v && i < best.i)) best = {v, i};    // NaN never wins
     }
