@@ -33,9 +33,6 @@
 #define GP_BN 256                 // accumulator columns per tile (features; gate|up in gate/up mode)
 #define GP_BK 64                  // k-values per stage: one 128-byte swizzled row
 #define GP_STAGES 6
-#ifndef GP_MAX_CUT
-#define GP_MAX_CUT 2              // units of 64 columns (4) run at well under a quarter of a tile's time each
-#endif
 #define GP_THREADS 192            // producer warp, issuing warp, 4 epilogue warps
 #define GP_WAIT_LIMIT 2000000
 #define GP_STAGE_BYTES (2 * GP_BM * GP_BK * 2)      // one CTA's part of a stage: 128 rows of x and 128 rows of w
@@ -140,7 +137,7 @@ __device__ __forceinline__ float gp_silu(float g) { return g / (1.0f + expf(-g))
 // round-robin as well.  Tiles are numbered token tile fastest.
 struct GpPlan {
     int tiles_m, tiles;      // token tiles; all tiles
-    int whole, cut;          // tiles below `whole` are taken whole; the rest in `cut` parts (1, 2 or 4)
+    int whole, cut;          // tiles below `whole` are taken whole; the rest in `cut` parts (1 or 2)
 };
 struct GpUnit {
     int mt, nt, part, cut;
@@ -166,12 +163,11 @@ __device__ __forceinline__ bool gp_unit(const GpPlan& p, int i, int cluster, int
 
 // MODE 0: y[T, N] = x . w^T.  MODE 1: w is [gate; up] of 2 * inter rows, y[T, inter] = silu(gate) * up.
 // MODE 2: y[T, N] (float32) += x . w^T: the product joins the residual stream where it lies.
-// w_map, w_map2, w_map4: the same weights read in boxes of 128, 64 and 32 rows (for units of a tile
-// cut 1, 2 or 4 ways).
+// w_map, w_map2: the same weights read in boxes of 128 and 64 rows (for whole tiles and for halves).
 template <int MODE, typename TO>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linear_pair_tcgen05_kernel(
     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
-    const __grid_constant__ CUtensorMap w_map2, const __grid_constant__ CUtensorMap w_map4, TO* __restrict__ y,
+    const __grid_constant__ CUtensorMap w_map2, TO* __restrict__ y,
     int T, int N, int K, int inter, GpPlan plan, int32_t* __restrict__ status) {
     pdl_invite();
     constexpr int TILE_ELEMS = GP_BM * GP_BK;
@@ -217,7 +213,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GP_THREADS, 1) linea
                 const int row_x = u.mt * (2 * GP_BM) + static_cast<int>(rank) * GP_BM;
                 const int row_w = MODE == 1 ? (rank == 0 ? 0 : inter) + u.nt * (GP_BN / 2) + u.part * half
                                             : u.nt * GP_BN + u.part * (2 * half) + static_cast<int>(rank) * half;
-                const CUtensorMap* wm = u.cut == 1 ? &w_map : (u.cut == 2 ? &w_map2 : &w_map4);
+                const CUtensorMap* wm = u.cut == 1 ? &w_map : &w_map2;
                 const unsigned bytes = 2u * (GP_BM + half) * GP_BK * sizeof(bf16);          // both CTAs' boxes
                 for (int kb = 0; kb < nk; ++kb, ++it) {
                     const int s = it % GP_STAGES;
@@ -388,15 +384,13 @@ extern "C" int llm_linear_pair_supported(int T, int N, int K) {
     return T >= 1 && N >= 8 && K >= 8 && (K % 8) == 0 && (N % 8) == 0;
 }
 
-// Whole tiles for as many full rounds of all clusters as there are; the tiles left over are cut 1, 2 or 4
-// ways along the features, whichever ends soonest (a unit of a tile cut n ways counts as 1/n of a round;
-// four ways only if GP_MAX_CUT allows it).
+// Whole tiles for as many full rounds of all clusters as there are; the tiles left over are taken whole or
+// cut in two along the features, whichever ends sooner (a half counts as half a round).  Narrower units
+// do not pay: 64 columns take 0.42 of a tile's time.
 static void gp_make_plan(int tiles_m, int tiles_n, GpPlan* plan, int* clusters) {
     const int tiles = tiles_m * tiles_n, slots = g_gp_sms / 2;
     const int whole = tiles >= slots ? (tiles / slots) * slots : 0, rest = tiles - whole;
-    int cut = 1;
-    for (int c = 2; c <= GP_MAX_CUT; c *= 2)                      // strictly sooner, else the wider unit
-        if (((rest * c + slots - 1) / slots) * cut < ((rest * cut + slots - 1) / slots) * c) cut = c;
+    const int cut = ((rest * 2 + slots - 1) / slots) < 2 * ((rest + slots - 1) / slots) ? 2 : 1;
     plan->tiles_m = tiles_m;
     plan->tiles = tiles;
     plan->whole = whole;
@@ -425,9 +419,9 @@ extern "C" int llm_linear_pair_efficiency(int T, int N, int K, int gate_up) {
 template <int MODE, typename TO>
 static int gp_launch(const bf16* x, const bf16* w, void* y, int T, int N, int K, int inter, long long w_rows, int32_t* status,
                      cudaStream_t s) {
-    CUtensorMap x_map, w_map, w_map2, w_map4;
+    CUtensorMap x_map, w_map, w_map2;
     if (!gp_encode(&x_map, x, T, K, GP_BM) || !gp_encode(&w_map, w, w_rows, K, GP_BN / 2) ||
-        !gp_encode(&w_map2, w, w_rows, K, GP_BN / 4) || !gp_encode(&w_map4, w, w_rows, K, GP_BN / 8))
+        !gp_encode(&w_map2, w, w_rows, K, GP_BN / 4))
         return LLM_REFUSED_SIZE;
     const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
     const int tiles_n = MODE == 1 ? (inter + GP_BN / 2 - 1) / (GP_BN / 2) : (N + GP_BN - 1) / GP_BN;
@@ -439,7 +433,7 @@ static int gp_launch(const bf16* x, const bf16* w, void* y, int T, int N, int K,
     auto kern = linear_pair_tcgen05_kernel<MODE, TO>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    launch_pdl(kern, dim3(2 * clusters), dim3(GP_THREADS), smem, s, x_map, w_map, w_map2, w_map4, static_cast<TO*>(y), T, N, K,
+    launch_pdl(kern, dim3(2 * clusters), dim3(GP_THREADS), smem, s, x_map, w_map, w_map2, static_cast<TO*>(y), T, N, K,
                inter, plan, status);
     return launch_status();
 }

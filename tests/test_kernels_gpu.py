@@ -502,6 +502,26 @@ def test_skinny_product_over_tiled_weights(M, N, K, out_dtype):
     assert key not in ops()._tiled                          # the copy went with its weight
 
 
+@pytest.mark.parametrize("M", [1, 8, 13])
+def test_output_head_at_the_real_vocabulary(M):
+    """151,936 x 4,096 weights (1.2 GB, past 2^29 elements) through the streaming product, plain and
+    tiled: against the library's product in float32 accumulation, and the argmax of its rows."""
+    torch.manual_seed(M)
+    x = torch.randn(M, 4096, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(151936, 4096, device=DEV) * 0.02).to(torch.bfloat16)
+    w[151935] = x[0] * 0.05                                  # the last row wins for the first token
+    lib = torch.mm(x, w.t(), out_dtype=torch.float32)
+    plain = ops().linear_skinny(x, w, torch.float32)
+    close(plain, lib, 2e-5)
+    ops().prepare_streaming(w)
+    assert w.data_ptr() in ops()._tiled
+    tiled = ops().linear_skinny(x, w, torch.float32)
+    assert torch.equal(tiled, plain)
+    assert ops().argmax_rows(tiled).tolist() == torch.argmax(lib, dim=1).tolist()
+    assert int(ops().argmax_rows(tiled)[0]) == 151935
+    assert ops().stream_status(DEV).tolist() == [0, 0]
+
+
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,N,K", [(17, 16, 512), (33, 100, 520), (64, 331, 80), (20, 48, 4096), (128, 1000, 1544),
                                    (65, 17, 8), (64, 6144, 4096), (32, 4096, 12288), (100, 300, 64)])
@@ -530,9 +550,9 @@ def test_stream_tcgen05_product(T, N, K, out_dtype):
                                    (512, 9472, 64), (4000, 2552, 200)])
 def test_paired_tcgen05_product(T, N, K, out_dtype):
     """The product that two CTAs of a cluster compute together (256 tokens x 256 features a tile)
-    against float64, at sizes that are no multiple of its tiles; with fewer tiles than clusters (cut
-    four and two ways), exactly one round of whole tiles, and whole rounds followed by cut tiles
-    (both accumulators, the ring of stages wrapping, units of 256, 128 and 64 columns in one launch)."""
+    against float64, at sizes that are no multiple of its tiles; with fewer tiles than clusters (taken
+    whole or in halves), exactly one round of whole tiles, and whole rounds followed by halves (both
+    accumulators, the ring of stages wrapping, units of 256 and 128 columns in one launch)."""
     torch.manual_seed(T * 1000 + N)
     x = torch.randn(T, K).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
