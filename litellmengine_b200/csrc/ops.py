@@ -506,6 +506,27 @@ def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
     weakref.finalize(weight, _tiled.pop, key, None)
 
 
+_tiled_generation = 0
+
+
+def release_streaming() -> int:
+    """Drop every tiled copy (the weights themselves stay; products read them in their plain layout
+    from then on).  Returns how many copies went.  Captured CUDA graphs that read the copies must
+    not be replayed afterwards: `streaming_generation` changes, and the runner drops its graphs."""
+    global _tiled_generation
+    n = len(_tiled)
+    if n:
+        torch.cuda.synchronize()                 # nothing in flight still reads them
+        _tiled.clear()
+        _tiled_generation += 1
+    return n
+
+
+def streaming_generation() -> int:
+    """Counts the times the tiled copies were dropped."""
+    return _tiled_generation
+
+
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                   out: Optional[torch.Tensor] = None, partials_ok: bool = False):
     """x [M <= 16, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16

@@ -41,10 +41,19 @@ class ModelRunner:
         self.plan = model.plan
         self.device = model.device
         limit = min(max_request_tokens or self.plan.max_position, self.plan.max_position)
-        self.cache = CacheManager(
-            model.stage_needs(), page_size, max_total_tokens, max_requests, max_request_tokens=limit,
-            dtype=model.dtype, device=self.device,
-            extra_state={"sampler": StateNeed((4,), "int32")})
+        def make_cache():
+            return CacheManager(
+                model.stage_needs(), page_size, max_total_tokens, max_requests, max_request_tokens=limit,
+                dtype=model.dtype, device=self.device,
+                extra_state={"sampler": StateNeed((4,), "int32")})
+        try:
+            self.cache = make_cache()
+        except torch.cuda.OutOfMemoryError:
+            # The second, tiled copies of the decode weights are a convenience: the cache goes first.
+            if ops.release_streaming() == 0:
+                raise
+            torch.cuda.empty_cache()
+            self.cache = make_cache()
         self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device)
         # Tokens sampled by the step before, for entries whose last token the host has not read yet
         # (`StepEntry.feedback`); whoever samples writes them here.
@@ -59,6 +68,7 @@ class ModelRunner:
         self._graphs = {}
         self._graph_seen = {}
         self._graph_pool = None
+        self._graph_weights = ops.streaming_generation()
         self.graph_replays = 0
 
     # ---- construction ----------------------------------------------------------------------
@@ -141,6 +151,9 @@ class ModelRunner:
         (sample, copy) before stepping again."""
         B = batch.num_tokens
         if self.use_graphs and batch.num_decode == B and batch.num_want == B:
+            if self._graph_weights != ops.streaming_generation():   # the tiled weight copies a graph points at are gone
+                self._graphs.clear()
+                self._graph_weights = ops.streaming_generation()
             key = (B, batch.layout)                  # a graph holds the device addresses of one layout
             g = self._graphs.get(key)
             if g is None:

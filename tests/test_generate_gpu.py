@@ -210,3 +210,23 @@ def test_command_line_and_run_prompt(tmp_path):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "litellmengine"), "--model", d, "--input-ids", "1,x"],
                        capture_output=True, text=True, timeout=120)
     assert r.returncode == 1 and "Invalid token id: x" in r.stderr and "Usage:" in r.stderr
+
+
+def test_dropping_the_tiled_weight_copies_keeps_generation_right():
+    """The second, tiled copies of the decode weights go when the cache needs their room: captured
+    graphs that point at them are dropped with them, and the same tokens come out through the
+    plain weight layout."""
+    from litellmengine_b200.csrc import ops
+    cfg, seed, page = tm.TINY_E, tm.TINY_E_SEED, tm.TINY_E_PAGE
+    w = tm.make_weights(cfg, seed, bf16_exact=True)
+    engine = engine_for(cfg, w, "bfloat16", page, 1024, max_tokens_per_step=256)
+    runner = engine.runner
+    prompts = [tm.random_tokens(cfg, n, 40 + n) for n in (5, 31, 64)]
+    first = engine.generate(prompts, max_new_tokens=24)
+    assert runner.graph_replays > 0 and len(ops._tiled) > 0
+    replays = runner.graph_replays
+    assert ops.release_streaming() > 0 and len(ops._tiled) == 0
+    again = engine.generate(prompts, max_new_tokens=24)
+    assert again == first
+    assert runner.graph_replays > replays                   # captured anew, without the copies
+    runner.check_status()
