@@ -661,11 +661,13 @@ def linear_pair_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional
 _PAIR_POLICY = os.environ.get("LLM_PAIR", "auto")       # auto | all | off: which prompt-portion products take the paired kernel
 PAIR_MIN_ROWS = 129                                      # fewer rows leave the second CTA of a pair idle
 # Thousandths of the clusters' time that a product's tiles must fill for the paired kernel to be taken
-# under `auto`.  With the activation in its epilogue it saves a kernel and wins from 0.85 on (a
-# 2,048-token prefill of the Qwen3-8B shape: 27.7 ms against 28.5).  Alone it is level with the library
-# at 0.87 and ahead at 0.99.  Adding into the residual was slower inside a whole prefill (28.9 ms: under
-# the power cap the clocks settle lower than with the library's kernels) and is left to `all`.
-_PAIR_NEEDS = {"plain": 960, "silu": 850, "into": None}
+# under `auto`; None: only under `all`.  With the activation in its epilogue it saves a kernel and wins
+# from 0.85 on (prefill of the Qwen3-8B shape, 2,048 / 4,096 / 8,192 tokens: 26.9 / 56.2 / 123.9 ms
+# against 27.9 / 58.8 / 124.1 with the library product and the activation kernel).  Alone it is level with
+# the library kernel by kernel, but a prefill is power-bound and the clocks settle lower with it: taking
+# the other products too gave 57.6 and 127.1 ms at 4,096 and 8,192 tokens, and adding into the residual
+# 28.9 ms at 2,048.
+_PAIR_NEEDS = {"plain": None, "silu": 850, "into": None}
 
 
 def _pair_takes(x: torch.Tensor, weight: torch.Tensor, n: int, kind: str) -> bool:
