@@ -708,9 +708,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     own weight-streaming kernel: alone it is level with the library for N = 4096..24576 and
     faster for K = 12288 (32 us against 36) and N = 151936 (203 against 218), and in a step it
     starts fetching weights while the kernel before it drains (a whole decode step of the
-    Qwen3-8B shape at batch 8: 4.35 ms against 4.77 with the library products).  Prompt portions
-    whose tiles keep the clusters busy take the paired tcgen05 product (`linear_pair`).  Everything else
-    goes through the library matrix product (the reference uses cuBLAS for all its products,
+    Qwen3-8B shape at batch 8: 4.35 ms against 4.77 with the library products).  Everything else
+    goes through the library matrix product (under `LLM_PAIR=all`, prompt portions take the paired tcgen05
+    product `linear_pair`; by default only the gate/up product does, through `linear_silu_mul`) (the reference uses cuBLAS for all its products,
     src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a float32 weight
     keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
