@@ -17,6 +17,7 @@
 // One warp handles one (token, head).  Norm weights and inv_freq may be null (no norm, no
 // rotation); rotary_dim <= head_dim.  With has_kv == 0 the input holds only queries.
 #include "common.cuh"
+#include <type_traits>
 
 #define RC_WARPS 4
 
@@ -188,12 +189,18 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
             }
         }
     }
+    // second half of a head: x2 cos + x1 sin; first half: x1 cos - x2 sin
+    if (inv_freq || angles) {
 #pragma unroll
-    for (int j = 0; j < HPW; ++j) {
+        for (int i = 0; i < N; ++i) sn[i] = lane < 16 ? -sn[i] : sn[i];
+    }
+    // A warp's heads are nearly always of one kind (queries, keys or values): the kind is then a
+    // constant of the loop below instead of a choice per head.
+    auto one = [&](auto kind_c, int j) {
+        constexpr int KIND = decltype(kind_c)::value;                    // 0 q, 1 k, 2 v, 3 decide per head
         const int head = head0 + j;
-        if (head >= heads_total) break;
-        const bool is_q = head < nq;
-        const bool is_k = !is_q && head < nq + nkv;
+        const bool is_q = KIND == 0 || (KIND == 3 && head < nq);
+        const bool is_k = KIND == 1 || (KIND == 3 && !is_q && head < nq + nkv);
         const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
         if (nw) {
             float ss = 0.0f;
@@ -208,20 +215,30 @@ __global__ void __launch_bounds__(RC_WARPS * 32) qk_norm_rope_kv_write_vec_kerne
 #pragma unroll
             for (int i = 0; i < N; ++i) {
                 const float other = __shfl_xor_sync(0xffffffffu, x[j][i], 16);
-                // first half: x1 cos - x2 sin; second half: x2 cos + x1 sin
-                x[j][i] = lane < 16 ? x[j][i] * cs[i] - other * sn[i] : x[j][i] * cs[i] + other * sn[i];
+                x[j][i] = x[j][i] * cs[i] + other * sn[i];
             }
         }
         if (is_q) {
             rc_store<N>(q_out + static_cast<size_t>(t) * nq * D + static_cast<size_t>(head) * D + e0, x[j]);
-            continue;
+            return;
         }
-        if (page < 0) continue;
+        if (page < 0) return;
         const int kv_head = is_k ? head - nq : head - nq - nkv;
         TC* dst = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * nkv + kv_head) * page_size * D +
                   static_cast<size_t>(pos % page_size) * D + e0;
         rc_store<N>(dst, x[j]);
+    };
+    const int last = min(head0 + HPW, heads_total) - 1;
+#define RC_HEADS(KIND)                                                      \
+    _Pragma("unroll") for (int j = 0; j < HPW; ++j) {                       \
+        if (head0 + j >= heads_total) break;                                \
+        one(std::integral_constant<int, KIND>{}, j);                        \
     }
+    if (last < nq) { RC_HEADS(0) }
+    else if (head0 >= nq && last < nq + nkv) { RC_HEADS(1) }
+    else if (head0 >= nq + nkv) { RC_HEADS(2) }
+    else { RC_HEADS(3) }
+#undef RC_HEADS
 }
 
 template <int D, int HPW, typename TI, typename T, typename TC>
