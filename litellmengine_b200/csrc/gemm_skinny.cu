@@ -172,12 +172,13 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* _
     gs_wait<0>();
 }
 
-// ---- the same for up to 8 tokens over weights stored tile by tile ---------------------------------
+// ---- the same over weights stored tile by tile ------------------------------------------------------
 // `w_tiled` holds the weights as the kernel wants them in shared memory: [feature tile][k-step]
 // blocks of 64 x 256 values (32 KB), each block four sub-tiles of [64 rows][64 k-values] with 128-byte
 // rows whose 16-byte chunks are XOR-swizzled by the row (chunk c of row r at position c ^ (r % 8):
 // the layout the copy engine's 128-byte swizzle writes and tcgen05 reads as a K-major operand, so
-// the same copy also serves gemm_stream_tcgen05.cu), zero-padded at the edges.  A stage of weights is then ONE contiguous 32 KB piece of memory,
+// the same copy also serves gemm_stream_tcgen05.cu), zero-padded at the edges.  A stage of weights is then ONE
+// contiguous piece of memory (a block of 32 KB for up to 8 tokens, half a block for 9 to 16),
 // fetched by one bulk copy (cp.async.bulk) of one thread instead of 2,048 sixteen-byte copies
 // of 128 threads, and DRAM sees whole pages instead of 512-byte runs 8 KB apart (measured with
 // the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for this kernel's strided

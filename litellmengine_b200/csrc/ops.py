@@ -471,7 +471,7 @@ def tile_weight(weight: torch.Tensor) -> torch.Tensor:
     """bfloat16 [N, K] -> the same values as [N/64 tiles, K/256 steps] blocks of 32 KB, each four
     sub-tiles of [64 rows][64 k-values] with 128-byte rows whose 16-byte chunks are XOR-swizzled by
     the row (chunk c of row r at position c ^ (r % 8)), zero-padded at the edges.  A stage of the
-    streaming product for up to 8 tokens is one block; a K-major tcgen05 operand of 128 rows x 64
+    streaming product is one block for up to 8 tokens and half a block for 9 to 16; a K-major tcgen05 operand of 128 rows x 64
     k-values is two sub-tiles."""
     N, K = weight.shape
     tn, nk = -(-N // TILE_ROWS), -(-K // TILE_K)
