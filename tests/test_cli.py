@@ -87,3 +87,29 @@ def test_devices():
 def test_the_chat_template_is_the_references():
     assert cli.chat_template("hi") == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n"
     assert cli.chat_template("hi", enable_thinking=True).endswith("<|im_start|>assistant\n<think>\n")
+
+
+def test_run_prompt_hands_ids_to_the_engine_and_reads_its_new_ids_line(tmp_path):
+    """The script's contract with the engine's command line (scripts/run_prompt.py:9-27,96-162): it
+    passes --input-ids, --max-tokens and --temperature 0, and picks the line after `New token ids:`.
+    A stand-in engine that prints its arguments and the two lines is enough to see both."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    fake = tmp_path / "engine.py"
+    fake.write_text("import sys\nprint('argv', ' '.join(sys.argv[1:]))\n"
+                    "print('Generated token ids:')\nprint('5,6,7,41,42')\nprint('New token ids:')\nprint('41,42')\n")
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "run_prompt"), "--model", str(tmp_path), "--engine",
+                        str(fake), "--input-ids", "5,6,7", "--max-tokens", "2"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert "--input-ids 5,6,7" in r.stdout and "--max-tokens 2" in r.stdout and "--temperature 0" in r.stdout
+    assert "[new token ids]\n41,42" in r.stdout
+    none = tmp_path / "none.py"
+    none.write_text("print('Generated token ids:')\nprint('5')\nprint('New token ids:')\nprint('<none>')\n")
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "run_prompt"), "--model", str(tmp_path), "--engine",
+                        str(none), "--input-ids", "5"], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.rstrip().endswith("[new token ids]")
+    both = subprocess.run([sys.executable, os.path.join(root, "bin", "run_prompt"), "--model", str(tmp_path),
+                           "--input-ids", "5", "--prompt", "x"], capture_output=True, text=True)
+    assert both.returncode != 0 and "exactly one" in both.stderr
