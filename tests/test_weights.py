@@ -126,3 +126,31 @@ def test_random_weights_mode_writes_a_model_folder(tmp_path):
     assert not torch.equal(other, again)
     alone = RandomSource({"model.norm.weight": params["model.norm.weight"]}, 5, torch.float32).get("model.norm.weight")
     assert torch.equal(alone.to(torch.bfloat16).float(), n)
+
+
+def test_a_folder_of_shards(tmp_path):
+    """Several files: those the index names if there is one, else every *.safetensors; a tensor
+    that two files hold is refused by name, and so is a folder without any."""
+    a = {"w1": torch.ones(2, 2), "w2": torch.zeros(3)}
+    b = {"w3": torch.full((2,), 7.0)}
+    write_safetensors(str(tmp_path / "model-00001-of-00002.safetensors"), a)
+    write_safetensors(str(tmp_path / "model-00002-of-00002.safetensors"), b)
+    src = SafetensorsSource(str(tmp_path))
+    assert sorted(src.names()) == ["w1", "w2", "w3"] and torch.equal(src.get("w3"), b["w3"]) and src.shape("w1") == (2, 2)
+    # a stray file beside the shards is read too, unless an index says which files belong to the model
+    write_safetensors(str(tmp_path / "stray.safetensors"), {"w1": torch.ones(2, 2)})
+    with pytest.raises(SafetensorsError, match="'w1' is in both"):
+        SafetensorsSource(str(tmp_path))
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {
+        "w1": "model-00001-of-00002.safetensors", "w2": "model-00001-of-00002.safetensors",
+        "w3": "model-00002-of-00002.safetensors"}}))
+    assert sorted(SafetensorsSource(str(tmp_path)).names()) == ["w1", "w2", "w3"]
+    (tmp_path / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(SafetensorsError, match="no weight_map"):
+        SafetensorsSource(str(tmp_path))
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(SafetensorsError, match="no .safetensors file"):
+        SafetensorsSource(str(empty))
+    with pytest.raises(SafetensorsError, match="cannot list"):
+        SafetensorsSource(str(tmp_path / "nowhere"))
