@@ -140,3 +140,22 @@ def test_random_orders_never_lose_or_duplicate_a_page(seed):
         m.release(s)
     m.check_invariants()
     assert all(g.pool.free_count == g.pool.num_pages for g in m.groups)
+
+
+def test_reserve_adds_up_a_step_one_request_at_a_time():
+    """`reserve` answers for one more request on top of what a step has promised already, and
+    agrees with `can_hold` for the whole list; it takes nothing itself."""
+    m = CacheManager([FULL], page_size=4, max_total_tokens=24, max_slots=4, max_request_tokens=16)   # 6 pages
+    a = m.admit()
+    m.ensure(a, 6)
+    m.commit(a, 6)                                           # holds 2 pages, 4 free
+    need = m.reserve([0], a, 7)
+    assert need == [0]                                       # position 6 lies in a page it has
+    need = m.reserve(need, a, 9)
+    assert need == [1]
+    need2 = m.reserve(need, None, 9)                         # a newcomer of 9 tokens: 3 pages
+    assert need2 == [4] and m.can_hold([(a, 9), (None, 9)])
+    assert m.reserve(need2, None, 1) is None and not m.can_hold([(a, 9), (None, 9), (None, 1)])
+    assert m.reserve([0], None, 17) is None                  # longer than a request may be
+    assert m.groups[0].pool.free_count == 4                  # asking took nothing
+    m.check_invariants()
