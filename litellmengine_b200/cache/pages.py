@@ -218,8 +218,10 @@ class CacheManager:
             n = g.need
             g.kv = torch.zeros((len(g.stages), g.pool.num_pages, 2, n.num_kv_heads, self.page_size, n.head_dim),
                                dtype=self.dtype, device=self.device)
-            g.table_dev = torch.zeros((self.max_slots, g.max_pages_per_request), dtype=torch.int32,
-                                      device=self.device)
+            # -1 like the host mirror: a kernel that reads an entry no request was ever given refuses
+            # it (status 3 or 4) instead of reading page 0 of someone else
+            g.table_dev = torch.full((self.max_slots, g.max_pages_per_request), -1, dtype=torch.int32,
+                                     device=self.device)
         for key, need in list(self.stage_state.items()) + list(self._extra_state.items()):
             self.state[key] = torch.zeros((self.max_slots,) + tuple(need.shape),
                                           dtype=getattr(torch, need.dtype), device=self.device)

@@ -54,25 +54,6 @@ __device__ __forceinline__ bool t5_try_wait(unsigned long long* bar, unsigned pa
                  : "=r"(ok) : "r"(t5_smem(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Built with -DT5_TRACE, CTA 0 records (event, tile, SM clock) triples of its issuing thread
-// and of its first softmax thread; llm_t5_trace_read copies them out.  A debugging aid only.
-#ifdef T5_TRACE
-#define T5_TRACE_LEN 8192
-__device__ long long g_t5_trace[4][T5_TRACE_LEN];
-#define T5_EVENT(role, n, code, u)                                                      \
-    do {                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (n) + 2 < T5_TRACE_LEN) {                                \
-            g_t5_trace[role][(n)++] = (static_cast<long long>(code) << 32) | (u);       \
-            g_t5_trace[role][(n)++] = clock64();                                        \
-        }                                                                               \
-    } while (0)
-extern "C" int llm_t5_trace_read(long long* host, int role) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, g_t5_trace, sizeof(long long) * T5_TRACE_LEN,
-                                                 sizeof(long long) * T5_TRACE_LEN * role));
-}
-#else
-#define T5_EVENT(role, n, code, u) do { } while (0)
-#endif
 
 __device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag,
                                         int32_t* status, int where) {
@@ -264,7 +245,6 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
             constexpr unsigned IDESC_QK = t5_idesc(T5_BM, T5_BN, 0);
             constexpr unsigned IDESC_PV = t5_idesc(T5_BM, T5_D, 1);
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
-            int tn = 0; (void)tn;
             // Descriptors are built once: a tile further on in shared memory is the same descriptor
             // plus its byte offset / 16 in the address field (one thread issues every product, so
             // what it computes per instruction is what limits the rate of issue).
@@ -273,9 +253,7 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
             constexpr unsigned long long STAGE_STEP = (T5_TILE * sizeof(bf16)) >> 4;
             auto issue_qk = [&](int u) -> bool {
                 const int st = u % STAGES, sb = u & 1;
-                T5_EVENT(0, tn, 1, u);
                 if (!t5_wait(&kv_full[st], (u / STAGES) & 1, &abort_flag, status, row_base)) return false;
-                T5_EVENT(0, tn, 2, u);
                 if (u >= 2) {                                     // the buffer's previous tile must be done with it
                     const int prev = u - 2;
                     const bool a = prev < n_tiles;
@@ -284,7 +262,6 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                         return false;
                 }
                 t5_fence_after();
-                T5_EVENT(0, tn, 3, u);
 #pragma unroll
                 for (int g = 0; g < HEADS; ++g)
 #pragma unroll
@@ -295,7 +272,6 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                     }
                 t5_commit(&s_full[sb]);
                 if (u < n_tiles) t5_commit(&kv_empty[st]);        // pass A: the keys are all this stage held
-                T5_EVENT(0, tn, 4, u);
                 return true;
             };
             if (ok && total > 0) ok = issue_qk(0);
@@ -303,10 +279,8 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                 if (u + 1 < total) ok = issue_qk(u + 1);          // the next S while this tile's softmax runs
                 if (!ok || u < n_tiles) continue;
                 const int st = u % STAGES, sb = u & 1, v = u - n_tiles;
-                T5_EVENT(0, tn, 5, u);
                 if (!t5_wait(&p_full[sb], (v >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
                 t5_fence_after();
-                T5_EVENT(0, tn, 6, u);
 #pragma unroll
                 for (int g = 0; g < HEADS; ++g)
 #pragma unroll
@@ -318,7 +292,6 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
                 t5_commit(&kv_empty[st]);
                 t5_commit(&s_used[sb]);
                 if (u == total - 1) t5_commit(&o_done);
-                T5_EVENT(0, tn, 7, u);
             }
         }
     } else {
@@ -332,20 +305,15 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
-        int tn = 0; (void)tn;
-        const bool tracer = (warp == 2 && lane == 0); (void)tracer;
         for (int u = 0; ok && u < n_tiles; ++u) {                 // pass A: maxima
             const int sb = u & 1, kt = k_lo + u * T5_BN;
-            if (tracer) T5_EVENT(1, tn, 11, u);
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
-            if (tracer) T5_EVENT(1, tn, 12, u);
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned r[2][32];                                    // both halves of the row are requested at once
             t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
             t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
             t5_wait_ld();
-            if (tracer) T5_EVENT(1, tn, 13, u);
             t5_fence_before();
             t5_arrive(&s_read[sb]);                               // S is in registers: the buffer may be overwritten
 #pragma unroll
@@ -365,16 +333,13 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
         const float msub = (m == -CUDART_INF_F) ? 0.0f : m * scale_log2e;
         for (int u = n_tiles; ok && u < total; ++u) {             // pass B: numerators with the final maximum
             const int sb = u & 1, v = u - n_tiles, kt = k_lo + v * T5_BN;
-            if (tracer) T5_EVENT(1, tn, 21, u);
             if (!t5_wait(&s_full[sb], (u >> 1) & 1, &abort_flag, status, row_base)) { ok = false; break; }
             t5_fence_after();
-            if (tracer) T5_EVENT(1, tn, 22, u);
             const bool full_tile = (kt + T5_BN - 1 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned pk[32], r[2][32];
             t5_ld32(tmem + lane_addr + s_col(g, sb), r[0]);
             t5_ld32(tmem + lane_addr + s_col(g, sb) + 32, r[1]);
             t5_wait_ld();
-            if (tracer) T5_EVENT(1, tn, 23, u);
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 if (full_tile) {
@@ -402,11 +367,9 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { a[i] = pk[i]; b[i] = pk[16 + i]; }
                 t5_st16(tmem + lane_addr + s_col(g, sb), a);
-                if (tracer) T5_EVENT(1, tn, 24, u);
                 t5_st16(tmem + lane_addr + s_col(g, sb) + 16, b);
             }
             t5_wait_st();
-            if (tracer) T5_EVENT(1, tn, 25, u);
             t5_fence_before();
             t5_arrive(&p_full[sb]);
         }
@@ -456,7 +419,7 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
 // Roles: warp 0 looks up pages and asks the copy engine for keys and values (rings of two tiles
 // each); one lane of warp 1 issues every product; then eight softmax warps per head, two threads
 // to a query row with 64 columns of S each.  What limited earlier forms, in the order found by
-// reading the SM clock inside the kernel (-DT5_TRACE): the order of CTAs (long tiles must start
+// reading the SM clock inside the kernel: the order of CTAs (long tiles must start
 // first), one thread requesting the copies box by box (140 clocks a request), one thread per row in
 // the softmax; what is left is the chain S -> weights -> P V of one head, about 4,000 clocks a
 // tile against 2,050 of tensor work for both heads.
@@ -565,7 +528,6 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
             return page;
         };
         int issued_k = 0, issued_v = 0;
-        int tn = 0; (void)tn;
         int next_page = page_of(0);
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
@@ -576,10 +538,8 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
             for (int values = 0; values < 2; ++values) {
                 unsigned long long* full = values ? &v_full[st] : &k_full[st];
                 if (lane == 0) {
-                    T5_EVENT(3, tn, 30 + values, j);
                     if (j >= STAGES && !t5_wait(values ? &v_empty[st] : &k_empty[st], ((j / STAGES) - 1) & 1, &abort_flag, status, row_base))
                         ok = false;
-                    T5_EVENT(3, tn, 32 + values, j);
                     if (ok) t5_expect_tx(full, T5O_TILE * sizeof(bf16));
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -590,7 +550,6 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                     t5_tma_2d(dst + lane * page_size * 64, &kv_map, 0, row0, full);
                     t5_tma_2d(dst + T5O_HALF + lane * page_size * 64, &kv_map, 64, row0, full);
                 }
-                if (lane == 0) T5_EVENT(3, tn, 34 + values, j);
                 if (values) issued_v = j + 1; else issued_k = j + 1;
             }
             if (!ok) break;
@@ -636,31 +595,22 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 t5_commit(&pv_done[g]);
             };
             bool ok = t5_wait(&q_full, 0, &abort_flag, status, row_base);
-            int tn = 0; (void)tn;
             auto one_tile = [&](int j, int st) -> bool {          // st = j % 2, a constant where this is inlined
-                T5_EVENT(0, tn, 0, j);
                 if (!t5_wait(&k_full[st], (j >> 1) & 1, &abort_flag, status, row_base)) return false;
                 t5_fence_after();
-                T5_EVENT(0, tn, 1, j);
                 qk(0, st);
-                T5_EVENT(0, tn, 2, j);
                 if (j > 0) {
                     if (!t5_wait(&p_full[1], (j - 1) & 1, &abort_flag, status, row_base)) return false;
                     t5_fence_after();
-                    T5_EVENT(0, tn, 3, j);
                     pv(1, 1 - st, j == 1);
                     t5_commit(&v_empty[1 - st]);                       // the last reader of the values of tile j-1
-                    T5_EVENT(0, tn, 4, j);
                 }
                 qk(1, st);
                 t5_commit(&k_empty[st]);                               // the last reader of the keys of tile j
-                T5_EVENT(0, tn, 5, j);
                 if (!t5_wait(&p_full[0], j & 1, &abort_flag, status, row_base)) return false;
                 if (!t5_wait(&v_full[st], (j >> 1) & 1, &abort_flag, status, row_base)) return false;
                 t5_fence_after();
-                T5_EVENT(0, tn, 6, j);
                 pv(0, st, j == 0);
-                T5_EVENT(0, tn, 7, j);
                 return true;
             };
             static_assert(T5O_STAGES == 2, "the issue loop is unrolled by the number of stages");
@@ -692,16 +642,12 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
         float m = -CUDART_INF_F, l = 0.0f;                        // m: the reference maximum, in units of log2
         bool ok = true;
-        int tn = 0; (void)tn;
-        const bool tracer = (wl == 0 || wl == 8) && lane == 0; (void)tracer;
         for (int j = 0; j < n_tiles; ++j) {
             const int kt = k_lo + j * T5O_BN + half * 64;         // this thread's first key of the tile
-            if (tracer) T5_EVENT(1 + g, tn, 10, j);
             // After a wait has run out (ok false) a thread still passes every barrier below, the same
             // number of times as the others, and touches nothing else.
             if (ok && !t5_wait(&s_full[g], j & 1, &abort_flag, status, row_base)) ok = false;
             t5_fence_after();
-            if (tracer) T5_EVENT(1 + g, tn, 11, j);
             const bool full_tile = (kt + 63 <= pos_first) && (window <= 0) && (rows_here == T5_BM);
             unsigned ra[32], rb[32];
             float mx = -CUDART_INF_F;
@@ -724,7 +670,6 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
             asm volatile("bar.sync %0, 256;\n" ::"r"(1 + g) : "memory");      // the 8 softmax warps of this head
             if (!ok) continue;
             mx = fmaxf(mx, x_max[j & 1][g][half ^ 1][row]) * scale_log2e;     // scale > 0; -inf stays -inf
-            if (tracer) T5_EVENT(1 + g, tn, 12, j);
             // move the reference up only when the maximum has run away from it (both threads of a row
             // see the same numbers and decide alike)
             const bool adopt = (m == -CUDART_INF_F) && (mx > m);  // nothing accumulated under the old reference
@@ -746,7 +691,6 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
                 t5_wait_st();
                 t5_ld32(my_s, ra);
                 t5_wait_ld();
-                if (tracer) T5_EVENT(1 + g, tn, 13, j);
             }
             if (adopt || jump) m = mx;
             const float msub = (m == -CUDART_INF_F) ? 0.0f : m;
@@ -777,7 +721,6 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
             weights(ra, 0);
             weights(rb, 32);
             t5_wait_st();
-            if (tracer) T5_EVENT(1 + g, tn, 14, j);
             t5_fence_before();
             t5_arrive(&p_full[g]);
         }

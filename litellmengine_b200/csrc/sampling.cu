@@ -147,7 +147,7 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
     __shared__ MaxIdx sh[33];
     __shared__ float fs[33];
     __shared__ float warp_tot[32];
-    __shared__ int result;
+    __shared__ int result, owner;
     const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
     int32_t* st = sampler_state + static_cast<size_t>(row_slot[blockIdx.x]) * 4;
     const float temperature = __int_as_float(st[3]);
@@ -168,7 +168,11 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
     for (int i = c0; i < c1; ++i) mine += expf((row[i] - top.v) * inv_t);
     const float total = block_sum(mine, fs);
 
-    // exclusive prefix of `mine` over threads: inclusive scan inside the warp, then warp totals
+    // Exclusive prefix of `mine` over threads: thread i owns the targets in [prefix[i], prefix[i+1]),
+    // the last thread everything from its prefix on.  The prefixes come
+    // out of a shuffle tree, so rounding may leave neighbours a few units in the last place out of
+    // order; the owner is therefore the LAST thread whose prefix is not above the target, which is
+    // one thread whatever the rounding did (prefix[0] is 0, so there always is one).
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float incl = mine;
 #pragma unroll
@@ -176,19 +180,29 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int vocab,
         const float n = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += n;
     }
+    const float left = __shfl_up_sync(0xffffffffu, incl, 1);       // the inclusive sum of the lane before
     if (lane == 31) warp_tot[warp] = incl;
-    if (threadIdx.x == 0) result = top.i;     // rounding may leave u*total past the last run
+    if (threadIdx.x == 0) owner = 0;
     __syncthreads();
     float before = 0.0f;
     for (int wi = 0; wi < warp; ++wi) before += warp_tot[wi];
-    const float excl = before + incl - mine;
+    const float excl = before + (lane > 0 ? left : 0.0f);
     const float target = u * total;
-    if (c1 > c0 && target >= excl && target < excl + mine) {
+    if (excl <= target) atomicMax(&owner, static_cast<int>(threadIdx.x));
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) == owner) {
         float run = excl;
-        int pick = c1 - 1;
+        int pick = -1;
         for (int i = c0; i < c1; ++i) {
             run += expf((row[i] - top.v) * inv_t);
             if (target < run) { pick = i; break; }
+        }
+        if (pick < 0) {
+            // rounding left the target past this run (or the run is empty): the last token at or
+            // before its end that has any weight
+            for (int i = min(c1, vocab) - 1; i >= 0; --i)
+                if (expf((row[i] - top.v) * inv_t) > 0.0f) { pick = i; break; }
+            if (pick < 0) pick = top.i;
         }
         result = pick;
     }

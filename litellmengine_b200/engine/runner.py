@@ -20,7 +20,11 @@ STATUS_TEXT = {1: "a token id outside the vocabulary reached the embedding kerne
                2: "a block-table update pointed outside the table",
                3: "the cache write met a page number outside the pool",
                4: "attention met a page number outside the pool",
-               5: "a wait on a copy barrier in the decode attention kernel ran out"}
+               5: "a wait on a copy barrier in the decode attention kernel ran out",
+               6: "a wait on a barrier in the tcgen05 prompt attention kernel ran out",
+               7: "a wait on a barrier in the tcgen05 streaming product ran out",
+               8: "a wait on a copy barrier in the weight-streaming product ran out",
+               9: "a wait on a barrier in the paired tcgen05 product ran out"}
 
 
 class ModelRunner:
@@ -200,8 +204,10 @@ class ModelRunner:
         return logits
 
     def check_status(self) -> None:
-        """Raise if a kernel recorded a refused index (reads two ints back; synchronises)."""
-        code, where = self.buffers.status.tolist()
-        if code:
-            self.buffers.status.zero_()
-            raise RuntimeError(f"device status {code}: {STATUS_TEXT.get(code, 'unknown')} (at index {where})")
+        """Raise if a kernel recorded a refused index or a wait that gave up (reads the step's
+        status word and the matrix products' own; synchronises).  Both words are cleared."""
+        for word in (self.buffers.status, ops.stream_status(self.device)):
+            code, where = word.tolist()
+            if code:
+                word.zero_()
+                raise RuntimeError(f"device status {code}: {STATUS_TEXT.get(code, 'unknown')} (at index {where})")

@@ -1,10 +1,12 @@
-"""What `bench.py` promises before it touches a GPU: one line and exit code 2 for more than one
-GPU, the `unavailable` line for the reference arm, peaks from MEASURED_PEAKS.json when that file
-exists and the stated fallback when it does not."""
+"""What `bench.py` promises: one line and exit code 2 for more than one GPU; a reference arm that
+prints either the contract's keys or one `unavailable` line with the reason; peaks from
+MEASURED_PEAKS.json when that file exists and the stated fallback when it does not."""
 import json
 import os
 import subprocess
 import sys
+
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -21,11 +23,36 @@ def test_more_than_one_gpu_is_one_line_and_exit_code_2():
     assert len(lines) == 1 and json.loads(lines[0])["n_gpus"] == 2
 
 
-def test_the_reference_arm_says_why_it_is_unavailable():
-    r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
+def test_the_reference_arm_without_a_gpu_is_one_line_with_the_reason():
+    """Here the reference's engine cannot run (it needs a CUDA device, or its sources are not at
+    hand): the arm still exits 0 with one JSON line."""
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3", "--layers", "1")
     assert r.returncode == 0
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    d = json.loads(lines[-1])
+    assert len(lines) == 1 and d["impl"] == "reference"
+    if "unavailable" in d:
+        assert isinstance(d["unavailable"], str) and d["unavailable"] and "\n" not in d["unavailable"]
+    else:
+        assert d["value"] > 0
+
+
+@pytest.mark.gpu
+def test_the_reference_arm_times_the_reference_engine():
+    """One layer of the benchmark's shape through the unmodified reference: the line has the
+    contract's keys, float32 as its dtype, and an end-to-end figure of its own."""
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "3", "--warmup", "3", "--layers", "1")
+    assert r.returncode == 0, r.stderr[-400:]
     d = json.loads(r.stdout.strip().splitlines()[-1])
-    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and "\n" not in d["unavailable"]
+    assert d["impl"] == "reference"
+    if "unavailable" in d and "no checkout of the reference" in d["unavailable"]:
+        pytest.skip("the reference's sources are not on this machine")
+    assert "unavailable" not in d, d
+    assert d["dtype"] == "fp32" and d["n_gpus"] == 1 and d["steps"] == 3 and d["unit"] == "tokens/s"
+    assert d["value"] > 0 and d["ms_per_step"] > 0 and d["e2e"]["value"] > 0
+    assert d["e2e"]["value"] <= d["value"] * 1.05                 # the wall clock holds the device time
+    assert d["config"]["layers"] == 1 and d["config"]["layers_full"] == 36 and d["config"]["global_batch"] == 8
+    assert d["e2e"]["h2d_bytes_per_step"] > 0 and d["e2e"]["d2h_bytes_per_step"] >= 32
 
 
 def test_peaks_come_from_the_measured_file_or_the_fallback(tmp_path, monkeypatch):

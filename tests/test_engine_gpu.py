@@ -150,6 +150,23 @@ def test_step_refuses_bad_input_without_launching():
     runner.cache.check_invariants()
 
 
+def test_a_status_code_in_either_word_is_raised_and_cleared():
+    """Kernels record a refused index or a wait that ran out in the step's status word; the engine's
+    matrix products record theirs in a word of their own.  `check_status` reads both.  The codes are
+    written from the host here: nothing on the device is made to fail."""
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.engine.runner import STATUS_TEXT
+    cfg, page, w, _ = setup("A", "float32")
+    runner = rh.make_runner(cfg, w, "float32", page, max_total_tokens=16, max_requests=2)
+    assert set(STATUS_TEXT) >= set(range(1, 10))
+    for word, code in ((runner.buffers.status, 4), (ops.stream_status(runner.device), 8),
+                       (ops.stream_status(runner.device), 9), (runner.buffers.status, 6)):
+        word.copy_(torch.tensor([code, 123], dtype=torch.int32))
+        with pytest.raises(RuntimeError, match=f"device status {code}: .*index 123"):
+            runner.check_status()
+        runner.check_status()                                   # cleared by the raise
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_replayed_as_graphs_match_kernel_by_kernel_launches(dtype):
     """Steps made only of single decoded tokens are replayed as CUDA graphs from the third step of
