@@ -344,10 +344,14 @@ class Bench:
                       "h2d_bytes_per_step": runner.buffers.last.size * 4, "d2h_bytes_per_step": args.batch * 4}
         if "decode" in want_points:
             for b in (1, 64):
-                r = self.decode_device_timed(runner, b, max(8, min(args.steps, 32)), 3)
+                r = self.decode_device_timed(runner, b, max(8, min(args.steps, 32)), 3, keep=True)
+                c = self.check_last_step(runner, r)
+                allowed = CHECK_RMS_PER_SQRT_LAYER * args.layers ** 0.5 * c["scale"]
                 points[f"decode_b{b}"] = round(r["tok_s"], 1)
                 points[f"decode_b{b}_ms"] = round(r["ms"], 3)
                 points[f"decode_b{b}_frac"] = round(r["frac"], 4)
+                points[f"decode_b{b}_check"] = {"ok": c["rms"] <= allowed, "rms_err": float("%.3g" % c["rms"]),
+                                                "allowed_rms": float("%.3g" % allowed)}
         if "generate" in want_points:
             # the workload the baseline states: 2,048-token prompts, then 256 new tokens, end to end
             for b in (1, 8, 64):
@@ -480,7 +484,7 @@ def main() -> int:
 
     bad = [k for k, v in points.items() if isinstance(v, dict) and v.get("ok") is False]
     if bad:
-        print(json.dumps({"error": "float32 decode steps differ from the same positions run as whole prompts",
+        print(json.dumps({"error": "decode steps differ from the same positions run as whole prompts",
                           **{k: points[k] for k in bad}}))
         return 1
 

@@ -80,10 +80,21 @@ class PagePool:
 
 @dataclass(frozen=True)
 class PagedNeed:
-    """What a stage asks of the cache when it keeps keys and values by position."""
+    """What a stage asks of the cache when it keeps keys and values by position: per position,
+    `num_kv_heads` keys of `head_dim` values and as many values of `value_dim` (None: of
+    `head_dim` too, and keys and values then share one tensor with an axis of two)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every earlier position stays; w: only the last w
+    value_dim: Optional[int] = None
+
+    @property
+    def key_width(self) -> int:
+        return self.head_dim
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -105,7 +116,9 @@ class CacheGroup:
         self.first_held = [0] * max_slots     # lowest logical page still held
         self.num_logical = [0] * max_slots    # logical pages ever appended
         self.pending: List[Tuple[int, int]] = []    # (flat table index, page id) not yet on the device
-        self.kv = None                        # device tensor [stages, pages, 2, kv_heads, P, d]
+        self.kv = None                        # device tensor [stages, pages, 2, kv_heads, P, d] when keys and values are equally wide
+        self.keys = None                      # [stages, pages, kv_heads, P, key width] (a view of `kv` when that exists)
+        self.values = None                    # [stages, pages, kv_heads, P, value width]
         self.table_dev = None                 # device int32 [max_slots, max_pages_per_request]
 
     def pages_for(self, length: int) -> int:
@@ -216,8 +229,15 @@ class CacheManager:
         import torch
         for g in self.groups:
             n = g.need
-            g.kv = torch.zeros((len(g.stages), g.pool.num_pages, 2, n.num_kv_heads, self.page_size, n.head_dim),
-                               dtype=self.dtype, device=self.device)
+            if n.key_width == n.value_width:
+                g.kv = torch.zeros((len(g.stages), g.pool.num_pages, 2, n.num_kv_heads, self.page_size, n.head_dim),
+                                   dtype=self.dtype, device=self.device)
+                g.keys, g.values = g.kv[:, :, 0], g.kv[:, :, 1]
+            else:
+                g.keys = torch.zeros((len(g.stages), g.pool.num_pages, n.num_kv_heads, self.page_size, n.key_width),
+                                     dtype=self.dtype, device=self.device)
+                g.values = torch.zeros((len(g.stages), g.pool.num_pages, n.num_kv_heads, self.page_size, n.value_width),
+                                       dtype=self.dtype, device=self.device)
             # -1 like the host mirror: a kernel that reads an entry no request was ever given refuses
             # it (status 3 or 4) instead of reading page 0 of someone else
             g.table_dev = torch.full((self.max_slots, g.max_pages_per_request), -1, dtype=torch.int32,
@@ -227,15 +247,23 @@ class CacheManager:
                                           dtype=getattr(torch, need.dtype), device=self.device)
 
     def stage_cache(self, stage: int):
-        """(kv tensor [pages, 2, kv_heads, P, d] of the stage, its group's device table, group)."""
+        """(kv tensor [pages, 2, kv_heads, P, d] of the stage, or None when its keys and values differ
+        in width; its group's device table; the group)."""
         gi, k = self.stage_group[stage]
         g = self.groups[gi]
         return (g.kv[k] if g.kv is not None else None), g.table_dev, g
 
+    def stage_pages(self, stage: int):
+        """(keys [pages, kv_heads, P, key width], values [pages, kv_heads, P, value width]) of the stage."""
+        gi, k = self.stage_group[stage]
+        g = self.groups[gi]
+        return (g.keys[k] if g.keys is not None else None), (g.values[k] if g.values is not None else None)
+
     def bytes_per_token(self) -> int:
         import torch
         esz = torch.empty((), dtype=self.dtype).element_size() if self.dtype is not None else 2
-        return sum(2 * g.need.num_kv_heads * g.need.head_dim * esz * len(g.stages) for g in self.groups)
+        return sum(g.need.num_kv_heads * (g.need.key_width + g.need.value_width) * esz * len(g.stages)
+                   for g in self.groups)
 
     # ---- slots -----------------------------------------------------------------------------
     @property

@@ -103,7 +103,9 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_invite() {
-    if (gridDim.x * gridDim.y * gridDim.z <= 1184u) pdl_launch_dependents();
+    unsigned sms;
+    asm("mov.u32 %0, %%nsmid;\n" : "=r"(sms));                 // this device's number of SMs
+    if (gridDim.x * gridDim.y * gridDim.z <= 8u * sms) pdl_launch_dependents();     // a "big" grid: over 8 CTAs an SM
 }
 __device__ __forceinline__ void pdl_begin() {
     pdl_invite();

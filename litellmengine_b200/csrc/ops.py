@@ -257,6 +257,59 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, cache: Optional[torch.Tensor], posi
     return q_out
 
 
+def qk_head_norm(qkv, q_norm_w, k_norm_w, eps: float, nq: int, nkv: int, d: int, has_kv: bool):
+    """The first half of `qk_norm_rope_kv_write` alone: the per-head norms of q and k (a null weight:
+    no norm), nothing rotated, nothing written to the cache.  Returns float32 q [T, nq*d] and k
+    [T, nkv*d] (None without keys), for a position part that encodes them itself."""
+    parts, part_stride = 1, 0
+    if isinstance(qkv, PartialSum):
+        parts, part_stride = qkv.parts.shape[0], qkv.parts.stride(0)
+        qkv = qkv.parts[0]
+    _dev(qkv, q_norm_w, k_norm_w)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + (2 * nkv if has_kv else 0)) * d:
+        raise KernelError(f"qkv row is {qkv.shape[1]}, expected {(nq + (2 * nkv if has_kv else 0)) * d}")
+    for w in (q_norm_w, k_norm_w):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != d):
+            raise KernelError("q/k norm weight must be float32 [head_dim]")
+    q = torch.empty((T, nq * d), dtype=torch.float32, device=qkv.device)
+    k = torch.empty((T, nkv * d), dtype=torch.float32, device=qkv.device) if has_kv else None
+    f = _fn("rope_cache", "llm_qk_head_norm",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_longlong, c_void_p])
+    _check(f(_ptr(qkv), _dt(qkv), _ptr(q), _ptr(k), _ptr(q_norm_w), _ptr(k_norm_w), float(eps), T, nq, nkv, d,
+             1 if has_kv else 0, parts, part_stride, _stream()), "qk_head_norm")
+    return q, k
+
+
+def qk_store(q: torch.Tensor, k: Optional[torch.Tensor], qkv, cache: Optional[torch.Tensor], positions, token_entry,
+             entry_slot, block_table: Optional[torch.Tensor], nq: int, nkv: int, d: int, page_size: int, has_kv: bool,
+             status: torch.Tensor, q_dtype: torch.dtype) -> torch.Tensor:
+    """The second half: q (float32, encoded by the position part) rounded to `q_dtype`; k (float32,
+    encoded) and the v columns of `qkv` written into the pages of `cache`."""
+    parts, part_stride = 1, 0
+    if isinstance(qkv, PartialSum):
+        parts, part_stride = qkv.parts.shape[0], qkv.parts.stride(0)
+        qkv = qkv.parts[0]
+    _dev(q, k, qkv, cache, positions, token_entry, entry_slot, block_table, status)
+    T = qkv.shape[0]
+    if q.dtype != torch.float32 or tuple(q.shape) != (T, nq * d) or (has_kv and (
+            k is None or k.dtype != torch.float32 or tuple(k.shape) != (T, nkv * d))):
+        raise KernelError("q and k must be float32 [T, heads * head_dim]")
+    if has_kv and (cache is None or block_table is None or tuple(cache.shape[1:]) != (2, nkv, page_size, d)):
+        raise KernelError("cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    q_out = torch.empty((T, nq * d), dtype=q_dtype, device=q.device)
+    f = _fn("rope_cache", "llm_qk_store",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(q), _ptr(k), _ptr(qkv), _dt(qkv), _ptr(q_out), _dt(q_out), _ptr(cache),
+             _dt(cache) if cache is not None else _dt(q_out), _ptr(positions), _ptr(token_entry), _ptr(entry_slot),
+             _ptr(block_table), block_table.shape[1] if block_table is not None else 0, T, nq, nkv, d, page_size,
+             1 if has_kv else 0, cache.shape[0] if cache is not None else 0, _ptr(status), parts, part_stride,
+             _stream()), "qk_store")
+    return q_out
+
+
 ROPE_TABLE_MIN_TOKENS = 64     # steps of fewer tokens compute their angles inside the kernel, before it waits
 
 

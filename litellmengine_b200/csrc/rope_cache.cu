@@ -282,6 +282,136 @@ extern "C" int llm_rope_angles(const int32_t* positions, const float* inv_freq, 
     return launch_status();
 }
 
+// ---- the same work in two halves, for position encodings this file does not know ---------------
+// A mixer whose position part is not a rotation runs `llm_qk_head_norm` (the per-head norms only:
+// q and k leave as float32 [T, heads * d]), lets the part encode q and k in its own way, and then
+// `llm_qk_store` (q rounded to the compute type, the encoded k and the projected v written into
+// their pages by the same address rule as above).  One warp per (token, head) in both.
+template <typename TI>
+__global__ void qk_head_norm_kernel(const TI* __restrict__ qkv, float* __restrict__ q_out, float* __restrict__ k_out,
+                                    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+                                    int num_tokens, int nq, int nkv, int d, int heads_total, int qkv_parts,
+                                    long long qkv_part_stride) {
+    pdl_begin();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nq + nkv;
+    const long long item = static_cast<long long>(blockIdx.x) * RC_WARPS + warp;
+    if (item >= static_cast<long long>(num_tokens) * heads) return;
+    const int t = static_cast<int>(item / heads);
+    const int head = static_cast<int>(item - static_cast<long long>(t) * heads);
+    const bool is_q = head < nq;
+    const TI* src = qkv + static_cast<size_t>(t) * heads_total * d + static_cast<size_t>(head) * d;
+    float* dst = is_q ? q_out + (static_cast<size_t>(t) * nq + head) * d
+                      : k_out + (static_cast<size_t>(t) * nkv + (head - nq)) * d;
+    float ss = 0.0f;
+    for (int i = lane; i < d; i += 32) {
+        float v = to_f32(src[i]);
+        for (int part = 1; part < qkv_parts; ++part) v += to_f32(src[part * qkv_part_stride + i]);
+        dst[i] = v;
+        ss += v * v;
+    }
+    const float* nw = is_q ? q_norm_w : k_norm_w;
+    if (nw) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(d) + eps);
+        for (int i = lane; i < d; i += 32) dst[i] = dst[i] * inv * nw[i];     // each lane rereads what it wrote
+    }
+}
+
+extern "C" int llm_qk_head_norm(const void* qkv, int qkv_dtype, float* q_out, float* k_out, const float* q_norm_w,
+                                const float* k_norm_w, float eps, int num_tokens, int nq, int nkv, int d, int has_kv,
+                                int qkv_parts, long long qkv_part_stride, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0) return LLM_REFUSED_SIZE;
+    const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+    const int heads = nq + (has_kv ? nkv : 0);
+    const long long items = static_cast<long long>(num_tokens) * heads;
+    const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int parts = qkv_parts < 1 ? 1 : qkv_parts;
+    if (qkv_dtype == LLM_DT_F32)
+        launch_pdl(qk_head_norm_kernel<float>, dim3(blocks), dim3(RC_WARPS * 32), 0, s, static_cast<const float*>(qkv),
+                   q_out, k_out, q_norm_w, k_norm_w, eps, num_tokens, nq, has_kv ? nkv : 0, d, heads_total, parts, qkv_part_stride);
+    else
+        launch_pdl(qk_head_norm_kernel<bf16>, dim3(blocks), dim3(RC_WARPS * 32), 0, s, static_cast<const bf16*>(qkv),
+                   q_out, k_out, q_norm_w, k_norm_w, eps, num_tokens, nq, has_kv ? nkv : 0, d, heads_total, parts, qkv_part_stride);
+    return launch_status();
+}
+
+template <typename TI, typename T, typename TC>
+__global__ void qk_store_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in, const TI* __restrict__ qkv,
+                                T* __restrict__ q_out, TC* __restrict__ cache, const int32_t* __restrict__ positions,
+                                const int32_t* __restrict__ token_entry, const int32_t* __restrict__ entry_slot,
+                                const int32_t* __restrict__ block_table, int table_stride, int num_tokens, int nq, int nkv,
+                                int d, int page_size, int has_kv, int num_pages, int32_t* __restrict__ status,
+                                int qkv_parts, long long qkv_part_stride) {
+    pdl_begin();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+    const long long item = static_cast<long long>(blockIdx.x) * RC_WARPS + warp;
+    if (item >= static_cast<long long>(num_tokens) * heads_total) return;
+    const int t = static_cast<int>(item / heads_total);
+    const int head = static_cast<int>(item - static_cast<long long>(t) * heads_total);
+    if (head < nq) {
+        const float* src = q_in + (static_cast<size_t>(t) * nq + head) * d;
+        T* dst = q_out + (static_cast<size_t>(t) * nq + head) * d;
+        for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(src[i]);
+        return;
+    }
+    const bool is_k = head < nq + nkv;
+    const int kv_head = is_k ? head - nq : head - nq - nkv;
+    const int pos = positions[t];
+    const int slot = entry_slot[token_entry[t]];
+    const int logical = pos / page_size;
+    const int page = (pos >= 0 && logical < table_stride)
+                         ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (lane == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
+        return;
+    }
+    TC* dst = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * nkv + kv_head) * page_size * d +
+              static_cast<size_t>(pos % page_size) * d;
+    if (is_k) {
+        const float* src = k_in + (static_cast<size_t>(t) * nkv + kv_head) * d;
+        for (int i = lane; i < d; i += 32) dst[i] = from_f32<TC>(src[i]);
+    } else {
+        const TI* src = qkv + static_cast<size_t>(t) * heads_total * d + static_cast<size_t>(head) * d;
+        for (int i = lane; i < d; i += 32) {
+            float v = to_f32(src[i]);
+            for (int part = 1; part < qkv_parts; ++part) v += to_f32(src[part * qkv_part_stride + i]);
+            dst[i] = from_f32<TC>(v);
+        }
+    }
+}
+
+// q_in, k_in: float32 [T, nq * d] and [T, nkv * d] as the position part left them; qkv: the projection
+// (its v columns are read); q_out in q_dtype; cache in cache_dtype.
+extern "C" int llm_qk_store(const float* q_in, const float* k_in, const void* qkv, int qkv_dtype, void* q_out, int q_dtype,
+                            void* cache, int cache_dtype, const int32_t* positions, const int32_t* token_entry,
+                            const int32_t* entry_slot, const int32_t* block_table, int table_stride, int num_tokens, int nq,
+                            int nkv, int d, int page_size, int has_kv, int num_pages, int32_t* status, int qkv_parts,
+                            long long qkv_part_stride, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || page_size <= 0) return LLM_REFUSED_SIZE;
+    const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+    const long long items = static_cast<long long>(num_tokens) * heads_total;
+    const unsigned blocks = static_cast<unsigned>((items + RC_WARPS - 1) / RC_WARPS);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define STORE(TI, T, TC)                                                                                          \
+    launch_pdl((qk_store_kernel<TI, T, TC>), dim3(blocks), dim3(RC_WARPS * 32), 0, s, q_in, k_in,                 \
+               static_cast<const TI*>(qkv), static_cast<T*>(q_out), static_cast<TC*>(cache), positions, token_entry, \
+               entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, page_size, has_kv, num_pages, status,  \
+               qkv_parts < 1 ? 1 : qkv_parts, qkv_part_stride)
+    const int key = qkv_dtype * 4 + q_dtype * 2 + cache_dtype;
+    if (key == 0) STORE(float, float, float);
+    else if (key == 3) STORE(float, bf16, bf16);
+    else if (key == 7) STORE(bf16, bf16, bf16);
+    else if (key == 1) STORE(float, float, bf16);
+    else return LLM_REFUSED_DTYPE;
+#undef STORE
+    return launch_status();
+}
+
 // qkv: [T, heads_total * d] (qkv_dtype); q_out: [T, nq * d] (q_dtype); cache (cache_dtype).
 // angles: nullptr, or the step's table from llm_rope_angles ([T][d/2] pairs; used when the whole head is rotated
 // and the head size is 64 or 128, ignored otherwise).

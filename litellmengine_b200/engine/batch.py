@@ -5,17 +5,22 @@ The reference builds fresh host vectors and device tensors for every call and on
 two shapes of batch: one prompt from position 0, or B single tokens
 (src/engine/paged_generate_engine.cpp:221-278,444-473).  Here a batch is any list of
 (request, its next tokens): prompt portions at any past length beside single decoded tokens.
+
+The batch itself carries only facts about entries and tokens.  Work lists that one kind of
+kernel wants (which rows go to which kernel, tiles, sorted orders) belong to the part that
+launches that kernel: it offers a `StepPrelude`, which is given room in the same pinned
+buffer, fills it from the entries once per step, and finds its device views in
+`batch.preludes[name]` in every layer.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
 
-
-PREFILL_TILE_ROWS = 128         # query rows per tile of the tensor-core prefill attention kernel
+from ..parts.context import StepFacts, StepPrelude
 
 
 @dataclass
@@ -33,23 +38,23 @@ class StepEntry:
 class _Region:
     """One layout of the step's arrays: a pinned staging buffer and its fixed device twin."""
 
-    def __init__(self, token_cap: int, max_entries: int, num_groups: int, device):
+    def __init__(self, token_cap: int, max_entries: int, num_groups: int, device, preludes: Sequence[StepPrelude]):
         self.token_cap = token_cap
         self.max_updates = token_cap + 2 * max_entries + 8       # new pages a step can append, with slack
         T, B, U = token_cap, max_entries, self.max_updates
         off = 0
         self.off = {}
-        for name, n in (("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
-                        ("entry_q_start", B), ("entry_q_len", B), ("entry_kv_len", B), ("want_rows", T),
-                        ("want_slot", T), ("decode_rows", T), ("prefill_tiles", 2 * (T // PREFILL_TILE_ROWS + B + 1)),
-                        ("counts", 8 + num_groups)):
+        sections = [("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
+                    ("entry_q_start", B), ("entry_q_len", B), ("entry_kv_len", B), ("want_rows", T),
+                    ("want_slot", T), ("counts", 8 + num_groups)]
+        for p in preludes:
+            sections += [(f"{p.name}:{k}", int(n)) for k, n in p.sections(T, B).items()]
+        self.prelude_keys = {p.name: list(p.sections(T, B)) for p in preludes}
+        for g in range(num_groups):
+            sections += [(f"upd_index{g}", U), (f"upd_value{g}", U)]
+        for name, n in sections:
             self.off[name] = (off, n)
             off += n
-        for g in range(num_groups):
-            self.off[f"upd_index{g}"] = (off, U)
-            off += U
-            self.off[f"upd_value{g}"] = (off, U)
-            off += U
         self.size = off
         self.pinned = torch.zeros(off, dtype=torch.int32, pin_memory=True)
         self.host = self.pinned.numpy()
@@ -82,11 +87,16 @@ class StepBuffers:
     kilobytes to the device instead of the large layout's hundred and more.  A step lives in one
     of the two; device addresses inside each are fixed, which is what a captured graph needs."""
 
-    def __init__(self, max_tokens: int, max_entries: int, num_groups: int, device):
+    def __init__(self, max_tokens: int, max_entries: int, num_groups: int, device,
+                 preludes: Sequence[StepPrelude] = ()):
         self.max_tokens, self.max_entries, self.num_groups = max_tokens, max_entries, num_groups
         self.device = torch.device(device)
-        self.large = _Region(max_tokens, max_entries, num_groups, self.device)
-        self.small = _Region(min(max_tokens, max_entries), max_entries, num_groups, self.device)
+        self.preludes: List[StepPrelude] = []
+        for p in preludes:                                        # one per name, first come
+            if all(p.name != q.name for q in self.preludes):
+                self.preludes.append(p)
+        self.large = _Region(max_tokens, max_entries, num_groups, self.device, self.preludes)
+        self.small = _Region(min(max_tokens, max_entries), max_entries, num_groups, self.device, self.preludes)
         self.max_updates = self.large.max_updates
         self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.last = self.large                                    # the region of the step packed last
@@ -117,28 +127,29 @@ class StepBatch:
     entry_kv_len: torch.Tensor       # int32 [B] cached length after this step
     want_rows: torch.Tensor          # int32 [W] rows whose logits are wanted
     want_slot: torch.Tensor          # int32 [W] slot of each wanted row
-    decode_rows: torch.Tensor        # int32 [n_decode] rows of entries that bring a single token
-    prefill_tiles: torch.Tensor      # int32 [n_tiles, 2] (entry, first row inside it) of entries that bring more
     status: torch.Tensor             # int32 [2]
     num_tokens: int
     num_entries: int
     num_want: int
     max_q_len: int
     max_kv_len: int
-    num_decode: int = 0
-    num_prefill_tiles: int = 0
     entries: List[StepEntry] = field(default_factory=list)
     feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
     layout: str = "large"                     # which of StepBuffers' two layouts holds this step's arrays
-    tables: dict = field(default_factory=dict)   # what parts compute once a step and share between layers
+    preludes: Dict[str, object] = field(default_factory=dict)   # the parts' `StepPrelude` views by name
+    # what a part computes on the device in the first layer that needs it and shares with the layers
+    # after it (emptied before a step is captured as a graph, so that the graph holds the kernel)
+    tables: Dict[object, object] = field(default_factory=dict)
 
 
 def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
               feedback: Optional[torch.Tensor] = None) -> StepBatch:
     """Fill the pinned buffer from `entries` (whose `past` is set) and the cache manager's
-    pending table `updates`, start the copy, and return the device views."""
-    T = sum(len(e.tokens) for e in entries)
+    pending table `updates`, let every prelude fill its share, start the copy, and return the
+    device views."""
     B = len(entries)
+    q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+    T = int(q_len.sum())
     if T > buffers.max_tokens or B > buffers.max_entries:
         raise ValueError(f"a step of {T} tokens in {B} entries exceeds the limits "
                          f"({buffers.max_tokens} tokens, {buffers.max_entries} entries)")
@@ -147,42 +158,39 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
     buffers.last = region
     region.wait_reusable()
     hv = region.host_view
-    tok, pos, ent = hv("token_ids"), hv("positions"), hv("token_entry")
-    slot, qs, ql, kl = hv("entry_slot"), hv("entry_q_start"), hv("entry_q_len"), hv("entry_kv_len")
+    past = np.fromiter((e.past for e in entries), dtype=np.int64, count=B)
+    slot = np.fromiter((e.slot for e in entries), dtype=np.int64, count=B)
+    q_start = np.cumsum(q_len) - q_len
+    tok = hv("token_ids")
+    if T == B:                                                    # single tokens only: no lists to join
+        tok[:T] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=B)
+        ent = np.arange(B)
+        hv("positions")[:T] = past
+    else:
+        tok[:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        ent = np.repeat(np.arange(B), q_len)
+        hv("positions")[:T] = np.arange(T) - np.repeat(q_start - past, q_len)
+    hv("token_entry")[:T] = ent
+    w = 0
     wr, ws = hv("want_rows"), hv("want_slot")
-    dec, tiles = hv("decode_rows"), hv("prefill_tiles")
-    n_dec = n_tiles = 0
-    row = w = 0
-    max_q = max_kv = 0
     for i, e in enumerate(entries):
-        n = len(e.tokens)
-        tok[row:row + n] = np.asarray(e.tokens, dtype=np.int32)
+        n = int(q_len[i])
         if e.feedback >= 0:
-            tok[row + n - 1] = -1 - e.feedback
-        pos[row:row + n] = np.arange(e.past, e.past + n, dtype=np.int32)
-        ent[row:row + n] = i
-        slot[i], qs[i], ql[i], kl[i] = e.slot, row, n, e.past + n
+            tok[int(q_start[i]) + n - 1] = -1 - e.feedback
         for j in e.want:
             if not 0 <= j < n:
                 raise ValueError(f"want={j} is outside the entry's {n} tokens")
-            wr[w], ws[w] = row + j, e.slot
+            wr[w], ws[w] = int(q_start[i]) + j, e.slot
             w += 1
-        if n == 1:
-            dec[n_dec] = row
-            n_dec += 1
-        else:
-            for q0 in range(0, n, PREFILL_TILE_ROWS):
-                tiles[2 * n_tiles], tiles[2 * n_tiles + 1] = i, q0
-                n_tiles += 1
-        max_q, max_kv = max(max_q, n), max(max_kv, e.past + n)
-        row += n
+    hv("entry_slot")[:B] = slot
+    hv("entry_q_start")[:B] = q_start
+    hv("entry_q_len")[:B] = q_len
+    hv("entry_kv_len")[:B] = past + q_len
     counts = hv("counts")
-    counts[0], counts[1], counts[2], counts[3], counts[4] = T, B, w, n_dec, n_tiles
-    if n_tiles > 1:
-        # longest first: a tile late in a long prompt walks the most keys, so it should start early
-        tl = tiles[:2 * n_tiles].reshape(n_tiles, 2)
-        cost = np.array([entries[int(e)].past + int(q0) for e, q0 in tl])
-        tl[:] = tl[np.argsort(-cost, kind="stable")]
+    counts[0], counts[1], counts[2] = T, B, w
+    facts = StepFacts(q_start=q_start, q_len=q_len, past=past, slot=slot, num_tokens=T)
+    filled = [(p, p.fill(facts, {k: hv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}))
+              for p in buffers.preludes]
     for g, (idx, val) in enumerate(updates):
         if len(idx) > buffers.max_updates:
             raise ValueError("more block-table changes than the step buffer holds")
@@ -191,10 +199,13 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         counts[8 + g] = len(idx)
     region.upload()
     dv = region.dev_view
-    return StepBatch(
+    batch = StepBatch(
         token_ids=dv("token_ids", T), positions=dv("positions", T), token_entry=dv("token_entry", T),
         entry_slot=dv("entry_slot", B), entry_q_start=dv("entry_q_start", B), entry_q_len=dv("entry_q_len", B),
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
-        decode_rows=dv("decode_rows", n_dec), prefill_tiles=dv("prefill_tiles", 2 * n_tiles).view(n_tiles, 2),
-        num_decode=n_dec, num_prefill_tiles=n_tiles, status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q, max_kv_len=max_kv,
-        entries=entries, feedback=feedback, layout="small" if region is buffers.small else "large")
+        status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=int(q_len.max()),
+        max_kv_len=int((past + q_len).max()), entries=entries, feedback=feedback,
+        layout="small" if region is buffers.small else "large")
+    for p, got in filled:
+        batch.preludes[p.name] = p.views({k: dv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}, got)
+    return batch

@@ -58,7 +58,8 @@ class ModelRunner:
                 raise
             torch.cuda.empty_cache()
             self.cache = make_cache()
-        self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device)
+        self.buffers = StepBuffers(max_tokens_per_step, max_requests, len(self.cache.groups), self.device,
+                                   preludes=model.step_preludes())
         # Tokens sampled by the step before, for entries whose last token the host has not read yet
         # (`StepEntry.feedback`); whoever samples writes them here.
         self.sampled = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
@@ -154,7 +155,7 @@ class ModelRunner:
         one.  A graph's logits tensor is reused by the next replay of that batch size: read it
         (sample, copy) before stepping again."""
         B = batch.num_tokens
-        if self.use_graphs and batch.num_decode == B and batch.num_want == B:
+        if self.use_graphs and batch.max_q_len == 1 and batch.num_want == B:
             if self._graph_weights != ops.streaming_generation():   # the tiled weight copies a graph points at are gone
                 self._graphs.clear()
                 self._graph_weights = ops.streaming_generation()
@@ -183,6 +184,7 @@ class ModelRunner:
             self.model.forward(batch, self.cache)
         cur.wait_stream(side)
         torch.cuda.synchronize()
+        batch.tables.clear()                    # what the warm-up computed once for its layers: the graph must compute its own
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()

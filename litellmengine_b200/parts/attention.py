@@ -3,16 +3,55 @@ from __future__ import annotations
 
 import math
 import os
+from dataclasses import dataclass
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from ..cache import PagedNeed
 from ..config.specs import MixerSpec
 from ..csrc import ops
 from ..weights.loader import ParamSpec
-from .context import StageContext
+from .context import StageContext, StepPrelude
 from .registry import lookup, register_mixer
+
+
+class AttentionWork(StepPrelude):
+    """How the attention kernels cut a step: rows of entries that bring one token go to the
+    split-key decode kernel, longer portions are cut into tiles of `ops.PREFILL_TILE_ROWS` query
+    rows (entry, first row inside it) for the tensor-core prompt kernel, longest walk first."""
+    name = "attention_work"
+
+    @dataclass
+    class Views:
+        decode_rows: torch.Tensor        # int32 [num_decode] rows of entries that bring a single token
+        prefill_tiles: torch.Tensor      # int32 [num_prefill_tiles, 2]
+        num_decode: int
+        num_prefill_tiles: int
+
+    def sections(self, max_tokens: int, max_entries: int):
+        return {"decode_rows": max_tokens,
+                "prefill_tiles": 2 * (max_tokens // ops.PREFILL_TILE_ROWS + max_entries + 1)}
+
+    def fill(self, facts, out):
+        R = ops.PREFILL_TILE_ROWS
+        single = facts.q_len == 1
+        n_dec = int(single.sum())
+        out["decode_rows"][:n_dec] = facts.q_start[single]
+        n_tiles = 0
+        if n_dec < len(facts.q_len):
+            tiles = [(i, q0) for i in np.nonzero(~single)[0] for q0 in range(0, int(facts.q_len[i]), R)]
+            # longest first: a tile late in a long prompt walks the most keys, so it should start early
+            tiles.sort(key=lambda t: -(int(facts.past[t[0]]) + t[1]))
+            n_tiles = len(tiles)
+            out["prefill_tiles"][:2 * n_tiles] = np.asarray(tiles, dtype=np.int64).reshape(-1)
+        return n_dec, n_tiles
+
+    def views(self, dev, filled):
+        n_dec, n_tiles = filled
+        return AttentionWork.Views(dev["decode_rows"][:n_dec], dev["prefill_tiles"][:2 * n_tiles].view(n_tiles, 2),
+                                   n_dec, n_tiles)
 
 
 @register_mixer("attention")
@@ -79,6 +118,9 @@ class AttentionMixer:
             return None
         return PagedNeed(self.nkv, self.d, self.spec.window)
 
+    def step_prelude(self):
+        return AttentionWork()
+
     def forward(self, x: torch.Tensor, ctx: StageContext) -> torch.Tensor:
         b = ctx.batch
         qkv = ops.linear(x, self.w_qkv, out_dtype=torch.float32, partials_ok=True)   # normalised, rotated in 32-bit
@@ -86,14 +128,27 @@ class AttentionMixer:
         if self.spec.has_kv and not ctx.writes_cache:
             raise RuntimeError("a mixer with its own keys and values was given a borrowed cache")
         eps = self.spec.qk_norm.eps if self.spec.qk_norm is not None else 0.0
-        q = ops.qk_norm_rope_kv_write(
-            qkv, ctx.cache if has_kv else None, b.positions, b.token_entry, b.entry_slot,
-            ctx.block_table if has_kv else None,
-            self.q_norm.weight if self.q_norm is not None else None,
-            self.k_norm.weight if self.k_norm is not None else None, eps,
-            self.position.inv_freq, self.position.rotary_dim, self.nq, self.nkv, self.d,
-            ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype,
-            angles=self.position.angles(b) if hasattr(self.position, "angles") else None)
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        cache, table = (ctx.cache, ctx.block_table) if has_kv else (None, None)
+        if hasattr(self.position, "rotation"):
+            # a rotation (or nothing): norms, rotation and cache write in one kernel
+            rot = self.position.rotation(b)
+            q = ops.qk_norm_rope_kv_write(
+                qkv, cache, b.positions, b.token_entry, b.entry_slot, table, qw, kw, eps,
+                rot.inv_freq if rot is not None else None, rot.rotary_dim if rot is not None else 0,
+                self.nq, self.nkv, self.d, ctx.page_size, has_kv, ctx.status, q_dtype=self.dtype,
+                angles=rot.angles if rot is not None else None)
+        else:
+            # an encoding of the part's own: norms, then the part, then the cache write
+            q32, k32 = ops.qk_head_norm(qkv, qw, kw, eps, self.nq, self.nkv, self.d, has_kv)
+            T = q32.shape[0]
+            q32, k32 = self.position.apply(q32.view(T, self.nq, self.d),
+                                           k32.view(T, self.nkv, self.d) if k32 is not None else None, b)
+            q = ops.qk_store(q32.reshape(T, self.nq * self.d).contiguous(),
+                             k32.reshape(T, self.nkv * self.d).contiguous() if k32 is not None else None, qkv, cache,
+                             b.positions, b.token_entry, b.entry_slot, table, self.nq, self.nkv, self.d,
+                             ctx.page_size, has_kv, ctx.status, self.dtype)
         a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, self.spec.window, self.scale)
         # joins the float32 residual; may stay a sum of k-splits if the layer's norm adds them itself
         residual = getattr(ctx, "residual", None)
@@ -122,22 +177,23 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
     float32 included, goes through the generic kernel."""
     b = ctx.batch
     cache = ctx.cache
-    if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and ops.fast_attention_supported(d, nq // nkv)):
+    work = b.preludes.get(AttentionWork.name)
+    if (work is not None and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+            and ops.fast_attention_supported(d, nq // nkv)):
         out = torch.empty_like(q)
-        if b.num_decode:
+        if work.num_decode:
             # Key splits: as many as keep the whole grid resident at once (two CTAs per SM), since
             # a second, partial wave costs more than it balances; at least 256 keys per split.
-            work = b.num_decode * nkv
-            splits = max(1, min(16, _cta_slots(q.device) // work, b.max_kv_len // 256))
-            ops.paged_attention_decode(q, out, cache, None if b.num_decode == b.num_tokens else b.decode_rows,
-                                       b.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
+            splits = max(1, min(16, _cta_slots(q.device) // (work.num_decode * nkv), b.max_kv_len // 256))
+            ops.paged_attention_decode(q, out, cache, None if work.num_decode == b.num_tokens else work.decode_rows,
+                                       work.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
                                        nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
-        if b.num_prefill_tiles:
+        if work.num_prefill_tiles:
             kernel = (ops.paged_attention_prefill_tcgen05
                       if _PREFILL_KERNEL != "mma" and ops.prefill_tcgen05_supported(d, ctx.page_size)
                       else ops.paged_attention_prefill)       # tcgen05/TMEM/TMA where it applies, mma.sync otherwise
-            kernel(q, out, cache, b.prefill_tiles, b.num_prefill_tiles, b.entry_slot, b.entry_q_start, b.entry_q_len,
-                   b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)
+            kernel(q, out, cache, work.prefill_tiles, work.num_prefill_tiles, b.entry_slot, b.entry_q_start,
+                   b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)
         return out
     return ops.paged_attention_generic(q, cache, b.positions, b.token_entry, b.entry_slot,
                                        ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

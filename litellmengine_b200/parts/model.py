@@ -76,6 +76,17 @@ class Model:
                 needs.append(self.blocks[st.block].mixer.cache_need())
         return needs
 
+    def step_preludes(self) -> list:
+        """The `StepPrelude`s the parts of this model offer (a part offers one through an optional
+        `step_prelude()` method)."""
+        out = []
+        for b in self.blocks:
+            for part in (b.mixer, b.feed_forward):
+                make = getattr(part, "step_prelude", None)
+                if make is not None:
+                    out.append(make())
+        return out
+
     def weight_bytes(self) -> int:
         """Bytes of every weight tensor one decode step reads (a tied head counts twice: the
         embedding rows read are negligible, the head is read whole)."""
@@ -112,11 +123,13 @@ class Model:
 
     def stage_context(self, s: int, batch, cache) -> StageContext:
         st = self.plan.order[s]
-        kv = table = None
+        kv = table = keys = values = None
         if s in cache.stage_group:
             kv, table, _ = cache.stage_cache(s)
+            keys, values = cache.stage_pages(s)
         return StageContext(batch=batch, stage=s, cache=kv, block_table=table, page_size=cache.page_size,
-                            writes_cache=st.cache_from is None, state=cache.state.get(s), status=batch.status)
+                            writes_cache=st.cache_from is None, state=cache.state.get(s), status=batch.status,
+                            cache_keys=keys, cache_values=values)
 
 
 def model_parameters(plan: ModelPlan) -> Dict[str, ParamSpec]:

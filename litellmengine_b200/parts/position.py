@@ -1,6 +1,18 @@
-"""Position encodings.  A position part holds the tables a mixer's kernels need; the
-rotation itself happens inside the mixer's fused kernel."""
+"""Position encodings.  A position part owns how queries and keys are encoded by position.
+
+Two ways to be one:
+  * `rotation(batch)` returns a `Rotation` (the tables of a half-split rotation) or None (nothing
+    is done to q and k): the attention mixer's fused kernel then normalises, rotates and writes
+    the cache in one pass.
+  * no `rotation` method, but `apply(q, k, batch) -> (q, k)`: float32 [T, heads, head_dim]
+    tensors (k is None for a mixer without keys of its own) after the per-head norms, returned
+    encoded.  The mixer runs the norms, this method, and the cache write as separate kernels,
+    so an encoding of any kind needs no change to the mixer or to its kernels.
+"""
 from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -8,13 +20,22 @@ from ..config.specs import PositionSpec
 from .registry import register_position
 
 
+@dataclass
+class Rotation:
+    """What the fused kernel rotates by: pairs (i, i + rotary_dim/2) of a head by the angle
+    float(position) * inv_freq[i]; `angles` is the step's table of their sines and cosines
+    (float32 [T, rotary_dim/2, 2]) or None, in which case the kernel computes them."""
+    inv_freq: torch.Tensor
+    rotary_dim: int
+    angles: Optional[torch.Tensor] = None
+
+
 @register_position("none")
 class NoPosition:
     def __init__(self, spec: PositionSpec, head_dim: int, device):
-        self.inv_freq = None
-        self.rotary_dim = 0
+        pass
 
-    def angles(self, batch):
+    def rotation(self, batch) -> Optional[Rotation]:
         return None
 
 
@@ -42,6 +63,9 @@ class RotaryPosition:
         self.inv_freq = inv.to(device).contiguous()
         self._key = ("rope", float(spec.theta), rd)
         self._table_ok = rd == head_dim and head_dim in (64, 128)      # what the kernel that reads the table takes
+
+    def rotation(self, batch) -> Rotation:
+        return Rotation(self.inv_freq, self.rotary_dim, self.angles(batch))
 
     def angles(self, batch):
         """The step's table of sines and cosines, made by the first layer that asks and shared by

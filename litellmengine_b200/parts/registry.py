@@ -12,11 +12,16 @@ changes.  The interfaces:
                      norm of x (+ delta); with write_sum the sum is stored back into x;
                      rows picks the rows to normalise.
   position       __init__(spec: PositionSpec, head_dim: int, device)
-                 tables needed by the mixer's kernels (for 'rope': `inv_freq`, `rotary_dim`)
+                 either rotation(batch) -> Rotation | None (the tables of a half-split rotation,
+                 applied inside the attention mixer's fused kernel; None: nothing is done)
+                 or apply(q, k, batch) -> (q, k) on float32 [T, heads, head_dim] after the
+                 per-head norms (any other encoding; k is None for a mixer without keys)
   mixer          __init__(spec: MixerSpec, hidden_size: int, compute_dtype, device)
                  parameters(), load(tensors)
                  cache_need() -> PagedNeed | StateNeed | None
                  forward(x [T, hidden] compute dtype, ctx: StageContext) -> [T, hidden]
+                 optional step_prelude() -> StepPrelude: work lists it wants built from a step's
+                 entries once, in the step's own upload (found in ctx.batch.preludes[name])
   feed_forward   __init__(spec: FeedForwardSpec, hidden_size: int, compute_dtype, device)
                  parameters(), load(tensors)
                  forward(x [T, hidden]) -> [T, hidden]

@@ -1,7 +1,9 @@
 """A plain, slow implementation of the Qwen3 dense decoder for the tests.
 
-Whole sequences, no cache, one function per part, float32 on the CPU with plain
-tensor arithmetic.  It shares no code with `litellmengine_b200` (it does not
+Whole sequences, no cache, one function per part, float32 with plain tensor
+arithmetic, on the CPU unless the weights it is given lie on another device (the
+tests of wide layers hand it tensors on the GPU, where the same formulas run through
+the tensor library's own float32 and float64 products).  It shares no code with `litellmengine_b200` (it does not
 import it) and is written from the reference's formulas; each function cites the
 reference file and lines it restates.  `tests/golden/` compares it once against
 the reference's own C++ code compiled for the CPU.
@@ -70,7 +72,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor
     src/layers/rotary.cu:85-117"""
     T, H, d = x.shape
     half = d // 2
-    ang = positions.to(torch.float32)[:, None] * rope_inv_freq(d, theta)[None, :]   # float32 product
+    ang = positions.to(torch.float32)[:, None] * rope_inv_freq(d, theta).to(x.device)[None, :]   # float32 product
     ang = ang.to(x.dtype)
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x1, x2 = x[..., :half], x[..., half:]
@@ -92,7 +94,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     if scale is None:
         scale = 1.0 / math.sqrt(float(d))
     out = torch.empty_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     visible = idx[None, :] <= idx[:, None]
     if window is not None:
         visible &= (idx[:, None] - idx[None, :]) < window
@@ -165,9 +167,10 @@ def forward_logits(ids, w: Dict[str, torch.Tensor], cfg: dict,
     """Logits [T, V] for a whole sequence starting at position 0: embedding, the
     layers in order, final RMSNorm, output head (the embedding table when tied and
     `lm_head.weight` is absent).  src/model/qwen3.cpp:1242-1278,1501"""
-    ids = torch.as_tensor(ids, dtype=torch.int64)
+    dev = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(ids, dtype=torch.int64, device=dev)
     w = {k: t.to(wd) for k, t in w.items()}
-    positions = torch.arange(ids.shape[0], dtype=torch.int32)
+    positions = torch.arange(ids.shape[0], dtype=torch.int32, device=dev)
     h = embedding(ids, w["model.embed_tokens.weight"]).to(wd)
     order = layer_order if layer_order is not None else list(range(cfg["num_hidden_layers"]))
     for layer in order:

@@ -159,3 +159,16 @@ def test_reserve_adds_up_a_step_one_request_at_a_time():
     assert m.reserve([0], None, 17) is None                  # longer than a request may be
     assert m.groups[0].pool.free_count == 4                  # asking took nothing
     m.check_invariants()
+
+
+def test_keys_and_values_of_different_widths_get_a_group_of_their_own():
+    narrow = PagedNeed(2, 16, None, value_dim=8)
+    assert (narrow.key_width, narrow.value_width) == (16, 8) and (FULL.key_width, FULL.value_width) == (16, 16)
+    m = CacheManager([FULL, narrow, FULL, narrow], page_size=4, max_total_tokens=32, max_slots=2)
+    assert [g.stages for g in m.groups] == [[0, 2], [1, 3]]
+    assert m.bytes_per_token() == 2 * (2 * (16 + 16) + 2 * (16 + 8)) * 2          # two stages each, 2-byte elements
+    s = m.admit()
+    m.ensure(s, 9)
+    assert [len(g.held_pages(s)) for g in m.groups] == [3, 3]
+    m.release(s)
+    m.check_invariants()

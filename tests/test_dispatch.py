@@ -29,7 +29,8 @@ def test_a_position_part_offers_its_table_only_for_steps_its_kernel_reads_it_in(
     large = types.SimpleNamespace(num_tokens=4096, tables={}, positions=None)
     assert rope.angles(small) is None
     assert rope.angles(large) is None                      # tables live on the GPU only
-    assert NoPosition(PositionSpec(kind="none"), 128, "cpu").angles(large) is None
+    assert NoPosition(PositionSpec(kind="none"), 128, "cpu").rotation(large) is None
+    assert rope.rotation(large).inv_freq is rope.inv_freq and rope.rotation(large).angles is None
     odd = RotaryPosition(PositionSpec(kind="rope", theta=10000.0, rotary_dim=32), 48, "cpu")
     assert odd._table_ok is False and rope._table_ok is True
 

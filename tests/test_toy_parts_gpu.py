@@ -188,7 +188,7 @@ def register_routed_toys():
     from litellmengine_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelPlan, NormSpec, PositionSpec,
                                            StageSpec, register_architecture)
     from litellmengine_b200.csrc import ops
-    from litellmengine_b200.parts import register_feed_forward, register_position
+    from litellmengine_b200.parts import Rotation, register_feed_forward, register_position
     from litellmengine_b200.weights import ParamSpec
 
     @register_position("toy_linear_frequencies")
@@ -200,6 +200,9 @@ def register_routed_toys():
             self.rotary_dim = spec.rotary_dim or head_dim
             half = self.rotary_dim // 2
             self.inv_freq = ((1.0 - torch.arange(half, dtype=torch.float32) / half) / spec.theta).to(device)
+
+        def rotation(self, batch):
+            return Rotation(self.inv_freq, self.rotary_dim)
 
     @register_feed_forward("toy_top1_experts")
     class Top1Experts:
@@ -341,3 +344,177 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
         unregister("feed_forward", "toy_top1_experts")
         unregister("position", "toy_linear_frequencies")
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+# ---- a position encoding that is no rotation, and a mixer whose keys and values differ in width ----
+DK, DV = 16, 8
+
+
+def register_offset_toys():
+    from litellmengine_b200.cache import PagedNeed
+    from litellmengine_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelPlan, NormSpec, PositionSpec,
+                                           StageSpec, register_architecture)
+    from litellmengine_b200.parts import register_mixer, register_position
+    from litellmengine_b200.weights import ParamSpec
+
+    @register_position("toy_offsets")
+    class Offsets:
+        """q += A[position], k += B[position] with fixed tables: an encoding by absolute position that
+        is not a rotation, so it has `apply` and no `rotation`."""
+
+        def __init__(self, spec, head_dim, device):
+            a, b = offset_tables(head_dim)
+            self.a, self.b = a.to(device), b.to(device)
+
+        def apply(self, q, k, batch):
+            pos = batch.positions.long()
+            return q + self.a[pos][:, None, :], (k + self.b[pos][:, None, :]) if k is not None else None
+
+    @register_mixer("toy_narrow_values")
+    class NarrowValues:
+        """Causal attention without any position encoding whose keys are DK wide and whose values are
+        DV wide: its pages hold two tensors of different widths."""
+
+        def __init__(self, spec, hidden_size, compute_dtype, device):
+            self.hidden = hidden_size
+            self.w = {}
+
+        def parameters(self) -> Dict[str, ParamSpec]:
+            return {"q_proj.weight": ParamSpec((NQ * DK, self.hidden)), "k_proj.weight": ParamSpec((NKV * DK, self.hidden)),
+                    "v_proj.weight": ParamSpec((NKV * DV, self.hidden)), "o_proj.weight": ParamSpec((self.hidden, NQ * DV))}
+
+        def load(self, t):
+            self.w = {k: v.float() for k, v in t.items()}
+
+        def cache_need(self):
+            return PagedNeed(NKV, DK, None, value_dim=DV)
+
+        def forward(self, x, ctx):
+            b, P = ctx.batch, ctx.page_size
+            assert ctx.cache is None and ctx.cache_keys.shape[-1] == DK and ctx.cache_values.shape[-1] == DV
+            T = x.shape[0]
+            xf = x.float()
+            q = (xf @ self.w["q_proj.weight"].T).view(T, NQ, DK)
+            k = (xf @ self.w["k_proj.weight"].T).view(T, NKV, DK)
+            v = (xf @ self.w["v_proj.weight"].T).view(T, NKV, DV)
+            pos = b.positions.long()
+            slot = b.entry_slot.long()[b.token_entry.long()]
+            page = ctx.block_table.long()[slot, pos // P]
+            ctx.cache_keys[page, :, pos % P, :] = k.to(ctx.cache_keys.dtype)
+            ctx.cache_values[page, :, pos % P, :] = v.to(ctx.cache_values.dtype)
+            out = torch.empty((T, NQ, DV), dtype=torch.float32, device=x.device)
+            row = 0
+            for e in b.entries:
+                n, kv_len = len(e.tokens), e.past + len(e.tokens)
+                pages = ctx.block_table[e.slot, :(kv_len + P - 1) // P].long()
+                keys = ctx.cache_keys[pages].permute(0, 2, 1, 3).reshape(-1, NKV, DK)[:kv_len].float()
+                vals = ctx.cache_values[pages].permute(0, 2, 1, 3).reshape(-1, NKV, DV)[:kv_len].float()
+                seen = torch.arange(kv_len, device=x.device)[None, :] <= (e.past + torch.arange(n, device=x.device))[:, None]
+                for h in range(NQ):
+                    s = (q[row:row + n, h] @ keys[:, h // (NQ // NKV)].T) / (DK ** 0.5)
+                    out[row:row + n, h] = torch.softmax(s.masked_fill(~seen, float("-inf")), dim=-1) @ vals[:, h // (NQ // NKV)]
+                row += n
+            return out.view(T, NQ * DV) @ self.w["o_proj.weight"].T
+
+    @register_architecture("ToyOffsetsForCausalLM")
+    @dataclass(frozen=True)
+    class ToyOffsets:
+        @classmethod
+        def from_dict(cls, d):
+            return cls()
+
+        def to_dict(self):
+            return {"architectures": ["ToyOffsetsForCausalLM"]}
+
+        def plan(self):
+            norm = NormSpec("rmsnorm", EPS)
+            attn = MixerSpec("attention", NQ, NKV, D, qk_norm=norm, position=PositionSpec("toy_offsets"))
+            ffn = FeedForwardSpec("swiglu", intermediate_size=INTER)
+            blocks = (BlockSpec("pre_norm", attn, ffn, norm, norm, weight_prefix="toy.0"),
+                      BlockSpec("pre_norm", MixerSpec("toy_narrow_values", weight_prefix="narrow"), ffn, norm, norm,
+                                weight_prefix="toy.1"))
+            return ModelPlan(H, VOCAB, blocks, (StageSpec(0), StageSpec(1), StageSpec(0)), norm, tie_word_embeddings=True,
+                             max_position=512, embedding_name="toy.embed", final_norm_name="toy.norm",
+                             output_name="toy.head")
+    return ToyOffsets
+
+
+def offset_tables(head_dim, positions=512):
+    p = torch.arange(positions, dtype=torch.float32)[:, None]
+    i = torch.arange(head_dim, dtype=torch.float32)[None, :]
+    return 0.5 * torch.sin(0.37 * p + i), 0.5 * torch.cos(0.11 * p * (i + 1.0))
+
+
+def plain_offsets_logits(ids, w, act=pq.identity, wd=torch.float32):
+    """Plain code for the offsets toy: whole sequence, no cache."""
+    w = {k: v.to(wd) for k, v in w.items()}
+    T = len(ids)
+    a, b = (t[:T].to(wd) for t in offset_tables(D))
+
+    def offset_attention(x, p):
+        q = pq.rms_norm((x @ w[f"{p}.q_proj.weight"].T).view(T, NQ, D), w[f"{p}.q_norm.weight"], EPS)
+        k = pq.rms_norm((x @ w[f"{p}.k_proj.weight"].T).view(T, NKV, D), w[f"{p}.k_norm.weight"], EPS)
+        v = (x @ w[f"{p}.v_proj.weight"].T).view(T, NKV, D)
+        q, k = act(q + a[:, None, :]), act(k + b[:, None, :])
+        return act(pq.causal_attention(q, k, act(v))).reshape(T, -1) @ w[f"{p}.o_proj.weight"].T
+
+    def narrow_attention(x, p):
+        q = (x @ w[f"{p}.q_proj.weight"].T).view(T, NQ, DK)
+        k = act((x @ w[f"{p}.k_proj.weight"].T).view(T, NKV, DK))
+        v = act((x @ w[f"{p}.v_proj.weight"].T).view(T, NKV, DV))
+        out = torch.empty((T, NQ, DV), dtype=wd)
+        seen = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
+        for h in range(NQ):
+            s = (q[:, h] @ k[:, h // (NQ // NKV)].T) / (DK ** 0.5)
+            out[:, h] = torch.softmax(s.masked_fill(~seen, float("-inf")), dim=-1) @ v[:, h // (NQ // NKV)]
+        return out.reshape(T, -1) @ w[f"{p}.o_proj.weight"].T
+
+    h = pq.embedding(torch.as_tensor(ids), w["toy.embed"]).to(wd)
+    for p, kind in (("toy.0", "offsets"), ("toy.1", "narrow"), ("toy.0", "offsets")):
+        x = act(pq.rms_norm(h, w[f"{p}.input_layernorm.weight"], EPS))
+        h = h + (offset_attention(x, f"{p}.self_attn") if kind == "offsets" else narrow_attention(x, f"{p}.narrow"))
+        y = act(pq.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], EPS))
+        h = h + pq.swiglu(y, w, f"{p}.mlp", act)
+    return (act(pq.rms_norm(h, w["toy.norm"], EPS)) @ w["toy.embed"].T).float()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_that_is_no_rotation_and_a_mixer_with_narrow_values(dtype, tmp_path):
+    """A position part with `apply` instead of `rotation` (the attention mixer then runs its norms,
+    the part, and the cache write as separate kernels), and a mixer that asks for pages whose keys
+    and values differ in width.  Both are registered here; nothing in the package names them."""
+    from litellmengine_b200.config import unregister_architecture
+    from litellmengine_b200.engine import ModelRunner
+    from litellmengine_b200.parts import unregister
+    from litellmengine_b200.weights import DictSource, SafetensorsSource, write_random_model
+    Toy = register_offset_toys()
+    try:
+        store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        folder = write_random_model(Toy(), str(tmp_path / "offsets"), seed=11, dtype=store)
+        src = SafetensorsSource(folder)
+        w = {n: src.get(n).float() for n in src.names()}
+        assert w["toy.1.narrow.v_proj.weight"].shape == (NKV * DV, H) and w["toy.1.narrow.o_proj.weight"].shape == (H, NQ * DV)
+        w = {k: (v * 4.0 if k.endswith("q_norm.weight") else v * 8.0 if "narrow.q_proj" in k else v) for k, v in w.items()}
+        rng = np.random.RandomState(3)
+        reqs = {f"r{i}": [int(t) for t in rng.randint(0, VOCAB, n)] for i, n in enumerate((2, 45, 70, 19, 33))}
+        if dtype == "bfloat16":
+            ref = {r: plain_offsets_logits(t, w, act=pq.to_bf16).numpy() for r, t in reqs.items()}
+        else:
+            ref = {r: plain_offsets_logits(t, w, wd=torch.float64).numpy() for r, t in reqs.items()}
+        for what, steps in (("whole", rh.trace_whole(reqs)), ("tail", rh.trace_tail_decode(reqs, 32)),
+                            ("portions", rh.trace_portions(reqs, 1)), ("mixed", rh.trace_mixed(reqs, 2, 4))):
+            runner = ModelRunner.from_config(
+                Toy(), dtype=dtype, device=DEV, page_size=4, max_requests=4, max_tokens_per_step=128,
+                max_total_tokens=rh.peak_tokens(steps, 4),
+                source=DictSource({k: (v.to(store) if v.dim() == 2 else v) for k, v in w.items()}))
+            widths = sorted((g.need.key_width, g.need.value_width, len(g.stages)) for g in runner.cache.groups)
+            assert widths == [(DK, DV, 1), (D, D, 2)]
+            narrow = [g for g in runner.cache.groups if g.need.value_width == DV][0]
+            assert narrow.kv is None and narrow.keys.shape[-1] == DK and narrow.values.shape[-1] == DV
+            assert runner.cache.bytes_per_token() == (2 * NKV * 2 * D + NKV * (DK + DV)) * (2 if dtype == "bfloat16" else 4)
+            got = rh.run_trace(runner, steps)
+            rh.assert_rows_match(got, ref, rh.tol_for(dtype), f"offsets toy {dtype} {what}")
+    finally:
+        unregister("position", "toy_offsets")
+        unregister("mixer", "toy_narrow_values")
+        unregister_architecture("ToyOffsetsForCausalLM")
