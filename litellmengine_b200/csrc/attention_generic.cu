@@ -11,14 +11,18 @@
 // so prompt portions at any past length, single decoded tokens and mixed batches all take
 // this one path; the step's own keys were written to the pages before this kernel runs.
 //
-// One warp per (token, head): each lane scores one key of the tile (a 16-byte-vectorised dot
+// One thread block of AG_WARPS warps per (token, head).  The keys are cut into tiles of 32; warp w
+// takes tiles w, w + AG_WARPS, ... : each lane scores one key of the tile (a 16-byte-vectorised dot
 // product against q held in shared memory), the warp reduces max and sum, then every lane
-// accumulates its output dimensions over the tile's values.  Tile boundaries depend only on
-// (lo, p), never on the batch, so a position's result does not depend on how the work was cut.
+// accumulates its output dimensions over the tile's values.  At the end the warps' running
+// (maximum, sum, output) triples are merged through shared memory in warp order.  Which warp takes
+// which tile depends only on (lo, p), never on the batch, so a position's result does not depend
+// on how the work was cut.  (With one warp per (token, head) a decode step of 8 requests at a
+// context of 4,096 kept two warps an SM busy: 5 ms a layer.)
 #include "common.cuh"
 #include <math_constants.h>
 
-#define AG_WARPS 4
+#define AG_WARPS 8
 #define AG_MAX_D 256
 
 template <typename T, typename TC>
@@ -31,15 +35,15 @@ __global__ void paged_attention_generic_kernel(
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long item = static_cast<long long>(blockIdx.x) * AG_WARPS + warp;
-    if (item >= static_cast<long long>(num_tokens) * nq) return;
+    const long long item = blockIdx.x;
     const int t = static_cast<int>(item / nq);
     const int h = static_cast<int>(item - static_cast<long long>(t) * nq);
     const int kvh = h / (nq / nkv);
-    float* qs = smem + warp * d;
+    float* qs = smem;                                  // [d]
+    float* merge = smem + d;                           // [AG_WARPS][d + 2]: output, maximum, sum of each warp
     const T* qrow = q + (static_cast<size_t>(t) * nq + h) * d;
-    for (int i = lane; i < d; i += 32) qs[i] = to_f32(qrow[i]) * scale;
-    __syncwarp();
+    for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) qs[i] = to_f32(qrow[i]) * scale;
+    __syncthreads();
 
     const int pos = positions[t];
     const int slot = entry_slot[token_entry[t]];
@@ -53,7 +57,7 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
     for (int r = 0; r < AG_MAX_D / 32; ++r) acc[r] = 0.0f;
 
-    for (int base = lo; base <= pos; base += 32) {
+    for (int base = lo + 32 * warp; base <= pos; base += 32 * AG_WARPS) {
         const int j = base + lane;
         const bool valid = j <= pos;
         long long koff = -1;
@@ -98,12 +102,31 @@ __global__ void paged_attention_generic_kernel(
             }
         }
     }
-    T* orow = out + (static_cast<size_t>(t) * nq + h) * d;
-    const float inv = 1.0f / l;
+    // merge the warps' partial results, in warp order (a warp without tiles has m = -inf, l = 0)
+    float* mine = merge + warp * (d + 2);
 #pragma unroll
     for (int r = 0; r < AG_MAX_D / 32; ++r) {
         const int i = lane + 32 * r;
-        if (i < d) orow[i] = from_f32<T>(acc[r] * inv);
+        if (i < d) mine[i] = acc[r];
+    }
+    if (lane == 0) { mine[d] = m; mine[d + 1] = l; }
+    __syncthreads();
+    float m_all = -CUDART_INF_F;
+    for (int w2 = 0; w2 < AG_WARPS; ++w2) m_all = fmaxf(m_all, merge[w2 * (d + 2) + d]);
+    float l_all = 0.0f;
+    for (int w2 = 0; w2 < AG_WARPS; ++w2) {
+        const float mw = merge[w2 * (d + 2) + d];
+        if (mw != -CUDART_INF_F) l_all += merge[w2 * (d + 2) + d + 1] * expf(mw - m_all);
+    }
+    T* orow = out + (static_cast<size_t>(t) * nq + h) * d;
+    const float inv = 1.0f / l_all;
+    for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) {
+        float o = 0.0f;
+        for (int w2 = 0; w2 < AG_WARPS; ++w2) {
+            const float mw = merge[w2 * (d + 2) + d];
+            if (mw != -CUDART_INF_F) o += merge[w2 * (d + 2) + i] * expf(mw - m_all);
+        }
+        orow[i] = from_f32<T>(o * inv);
     }
 }
 
@@ -116,9 +139,10 @@ extern "C" int llm_paged_attention_generic(
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || (d & 15) || page_size <= 0)
         return LLM_REFUSED_SIZE;
     if (!aligned16(cache)) return LLM_REFUSED_ALIGN;
-    const size_t smem = static_cast<size_t>(AG_WARPS) * d * sizeof(float);
+    const size_t smem = (static_cast<size_t>(d) + static_cast<size_t>(AG_WARPS) * (d + 2)) * sizeof(float);
     const long long items = static_cast<long long>(num_tokens) * nq;
-    const unsigned blocks = static_cast<unsigned>((items + AG_WARPS - 1) / AG_WARPS);
+    if (items > 0x7fffffffLL) return LLM_REFUSED_SIZE;
+    const unsigned blocks = static_cast<unsigned>(items);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(T, TC)                                                                              \
     launch_pdl((paged_attention_generic_kernel<T, TC>), dim3(blocks), dim3(AG_WARPS * 32), smem, s,                      \

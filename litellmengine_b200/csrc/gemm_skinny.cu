@@ -18,6 +18,8 @@
 // 16 tokens two).  Accumulation is float32; the result is float32 or bfloat16.
 // The reference calls cublasSgemm for every product (src/layers/linear.cu:169-215).
 #include "common.cuh"
+#include <cuda.h>
+#include <unordered_map>
 
 #define GS_ROWS 64          // output features per CTA (16 per warp)
 // k-values per stage and stages, by token tile: two CTAs per SM must fit.  Up to 8 tokens: three
@@ -202,15 +204,20 @@ __device__ __forceinline__ bf16* gs_at_tiled(bf16* base, int row, int chunk) {
 
 // MT = 8: stages of 256 k-values (a whole 32 KB block), three of them; MT = 16: stages of 128 k-values
 // (half a block: two sub-tiles, 16 KB contiguous), five of them, so that two CTAs fit an SM.
-template <int MT, typename TO>
+//
+// BOXES: the same stage fetched from the plain [N, K] weights instead, by the copy engine's tiled mode:
+// a stage is GS_BK / 64 boxes of [64 rows][64 k-values] that the 128-byte swizzle lays down in exactly
+// the order above (zeros beyond N and K), so that a model needs no second copy of its weights.
+template <int MT, typename TO, bool BOXES>
 __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const bf16* __restrict__ x,
                                                                          const bf16* __restrict__ w_tiled, TO* __restrict__ y,
                                                                          float* __restrict__ partial, int M, int N, int K,
-                                                                         int slices, int per_tile, int32_t* __restrict__ status) {
+                                                                         int slices, int per_tile, int32_t* __restrict__ status,
+                                                                         const __grid_constant__ CUtensorMap w_map) {
     constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT);
     constexpr unsigned W_BYTES = GS_ROWS * GS_BK * sizeof(bf16);
     const long long halves_per_tile = static_cast<long long>((K + 255) / 256) * (256 / GS_BK);   // stages of GS_BK in a tile's row of blocks
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];          // the swizzle's pattern repeats every 1024 bytes
     bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK], as stored in w_tiled
     bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
     __shared__ __align__(8) unsigned long long full[GS_STAGES];
@@ -235,10 +242,19 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
             unsigned long long* bar = &full[i % GS_STAGES];
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the stage was read through the generic proxy
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(W_BYTES) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
-                             "r"(gs_smem(w_s + (i % GS_STAGES) * GS_ROWS * GS_BK)),
-                         "l"(w_tiled + (static_cast<size_t>((begin + i) / nk) * halves_per_tile + (begin + i) % nk) * (GS_ROWS * GS_BK)),
-                         "r"(W_BYTES), "r"(gs_smem(bar)) : "memory");
+            if constexpr (BOXES) {
+                const int n0 = static_cast<int>((begin + i) / nk) * GS_ROWS, k0 = static_cast<int>((begin + i) % nk) * GS_BK;
+#pragma unroll
+                for (int b = 0; b < GS_BK / 64; ++b)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                                     "r"(gs_smem(w_s + (i % GS_STAGES) * GS_ROWS * GS_BK + b * (GS_ROWS * 64))), "l"(&w_map),
+                                 "r"(k0 + b * 64), "r"(n0), "r"(gs_smem(bar)) : "memory");
+            } else {
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+                                 "r"(gs_smem(w_s + (i % GS_STAGES) * GS_ROWS * GS_BK)),
+                             "l"(w_tiled + (static_cast<size_t>((begin + i) / nk) * halves_per_tile + (begin + i) % nk) * (GS_ROWS * GS_BK)),
+                             "r"(W_BYTES), "r"(gs_smem(bar)) : "memory");
+            }
         }
     };
     auto load_x = [&](int i) {
@@ -431,23 +447,87 @@ extern "C" long long llm_linear_skinny_tiled_elems(int N, int K) {
     return static_cast<long long>((N + GS_ROWS - 1) / GS_ROWS) * ((K + GS_TILED_BK - 1) / GS_TILED_BK) * GS_ROWS * GS_TILED_BK;
 }
 
-template <int MT, typename TO>
+// ---- tensor maps of plain weights: [N, K] bfloat16, boxes of 64 k-values x 64 rows, 128-byte swizzle ----
+typedef CUresult (*GsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static GsEncodeFn g_gs_encode = nullptr;
+static int g_gs_encode_state = 0;
+struct GsMapEntry { int n, k; CUtensorMap map; };
+static std::unordered_map<const void*, GsMapEntry> g_gs_maps;     // by the weights' address
+
+static const CUtensorMap* gs_weight_map(const void* w, int N, int K) {
+    if (g_gs_encode_state == 0) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess && fn != nullptr) {
+            g_gs_encode = reinterpret_cast<GsEncodeFn>(fn);
+            g_gs_encode_state = 1;
+        } else {
+            (void)cudaGetLastError();
+            g_gs_encode_state = -1;
+        }
+    }
+    if (g_gs_encode_state < 0) return nullptr;
+    auto it = g_gs_maps.find(w);
+    if (it != g_gs_maps.end() && it->second.n == N && it->second.k == K) return &it->second.map;
+    GsMapEntry e;
+    e.n = N;
+    e.k = K;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(N)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(bf16)};
+    const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(GS_ROWS)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    if (g_gs_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    g_gs_maps[w] = e;
+    return &g_gs_maps[w].map;
+}
+
+template <int MT, typename TO, bool BOXES>
 static int launch_skinny_tiled(const bf16* x, const bf16* wt, void* y, float* scratch, long long scratch_floats, int M, int N,
                                int K, int keep_partials, int32_t* status, cudaStream_t s) {
     if (!skinny_device()) return LLM_REFUSED_SIZE;
+    CUtensorMap map = {};
+    if (BOXES) {
+        const CUtensorMap* m = gs_weight_map(wt, N, K);
+        if (m == nullptr) return LLM_REFUSED_ALIGN;                      // the driver refused the weights' address or strides
+        map = *m;
+    }
     const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK_FOR(MT) * sizeof(bf16);
-    auto kern = linear_skinny_tiled_kernel<MT, TO>;
+    auto kern = linear_skinny_tiled_kernel<MT, TO, BOXES>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     int ctas, slices, per_tile;
     skinny_plan(N, K, GS_BK_FOR(MT), &ctas, &slices, &per_tile);
     if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * M * N)) return LLM_REFUSED_SIZE;
-    launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, wt, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile, status);
+    launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, wt, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile, status, map);
     int rc = launch_status();
     if (rc != LLM_OK || slices == 1 || keep_partials) return rc;
     const long long mn = static_cast<long long>(M) * N;
     launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, slices);
     return launch_status();
+}
+
+// The same product over the PLAIN weights [N, K], fetched box by box (one copy of the weights serves
+// every kernel).  w must be 16-byte aligned and K a multiple of 8 (the copy engine's rule for strides).
+extern "C" int llm_linear_skinny_boxes(const void* x, const void* w, void* y, int out_dtype, float* scratch,
+                                       long long scratch_floats, int M, int N, int K, int keep_partials, int32_t* status,
+                                       uintptr_t stream) {
+    if (!llm_linear_skinny_supported(M, N, K)) return LLM_REFUSED_SIZE;
+    if (!aligned16(x) || !aligned16(w) || status == nullptr) return LLM_REFUSED_ALIGN;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bf16* xp = static_cast<const bf16*>(x);
+    const bf16* wp = static_cast<const bf16*>(w);
+    if (out_dtype != LLM_DT_F32 && out_dtype != LLM_DT_BF16) return LLM_REFUSED_DTYPE;
+    if (M <= 8)
+        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                       : launch_skinny_tiled<8, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                   : launch_skinny_tiled<16, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 
 extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void* y, int out_dtype, float* scratch,
@@ -460,10 +540,10 @@ extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void*
     const bf16* wp = static_cast<const bf16*>(w_tiled);
     if (out_dtype != LLM_DT_F32 && out_dtype != LLM_DT_BF16) return LLM_REFUSED_DTYPE;
     if (M <= 8)
-        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
-                                       : launch_skinny_tiled<8, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
-    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
-                                   : launch_skinny_tiled<16, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                       : launch_skinny_tiled<8, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                   : launch_skinny_tiled<16, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 
 // x: bfloat16 [M, K]; w: bfloat16 [N, K]; y: [M, N] float32 (out_dtype 0) or bfloat16 (1);

@@ -599,6 +599,11 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                 [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
         st = stream_status(x.device)
         f = lambda xp, wp, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, _ptr(tiled), yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
+    elif os.environ.get("LLM_SKINNY_SRC", "boxes") == "boxes":
+        g = _fn("gemm_skinny", "llm_linear_skinny_boxes",
+                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        st = stream_status(x.device)
+        f = lambda xp, wp, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, wp, yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
     else:
         f = _fn("gemm_skinny", "llm_linear_skinny",
                 [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
