@@ -305,20 +305,9 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
         if (e != cudaSuccess) return static_cast<int>(e);
     }
     dim3 grid(num_splits, nkv, n_rows);
-    static int use_tma = -1;                                        // LLM_DECODE_TMA=0 keeps the cp.async kernel
-    if (use_tma < 0) {
-        const char* e = getenv("LLM_DECODE_TMA");
-        use_tma = (e && e[0] == '0') ? 0 : 1;
-    }
-    const CUtensorMap* map = (use_tma && decode_tma_page_ok(page_size))
-                                 ? kv_tensor_map(cache, num_pages, nkv, page_size, D) : nullptr;
+    // pages of 8 to 64 tokens are boxes the copy engine fetches; other page sizes go through cp.async
+    const CUtensorMap* map = decode_tma_page_ok(page_size) ? kv_tensor_map(cache, num_pages, nkv, page_size, D) : nullptr;
     if (map != nullptr) {
-        static int ts = 0;                                          // tiles in shared memory for the TMA kernel
-        if (ts == 0) {
-            const char* e = getenv("LLM_DECODE_TMA_STAGES");
-            ts = e ? atoi(e) : 3;
-            if (ts != 3 && ts != 4 && ts != 6) ts = 3;
-        }
 #define TMA_GO(TS)                                                                                                   \
     {                                                                                                                \
         const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;                     \
@@ -330,7 +319,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
                                                 table_stride, part_acc, part_ml, out, nq, nkv, page_size, window,    \
                                                 scale * 1.4426950408889634f, num_pages, num_splits, status);         \
     }
-        if (ts == 6) TMA_GO(6) else if (ts == 4) TMA_GO(4) else TMA_GO(3)
+        TMA_GO(3)                                                   // three tiles in shared memory: one read, two in flight
 #undef TMA_GO
     } else {
         launch_pdl(kern, dim3(grid), dim3(AD_THREADS), smem, s, q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
@@ -372,28 +361,13 @@ extern "C" int llm_paged_attention_decode(
     float* part_acc = scratch;
     float* part_ml = scratch ? scratch + static_cast<size_t>(n_rows) * nq * num_splits * d : nullptr;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    // Tiles in shared memory: one being read, the rest in flight.  More in flight per SM is what
-    // brings the kernel closer to the memory bandwidth; the count is a tuning knob.
-    static int stages = 0;
-    if (stages == 0) {
-        const char* e = getenv("LLM_DECODE_STAGES");
-        stages = e ? atoi(e) : 3;
-        if (stages != 3 && stages != 4 && stages != 6 && stages != 7) stages = 3;
-    }
+    // Three tiles in shared memory: one being read, two in flight (more did not bring more bandwidth).
 #define GO(DD, SS)                                                                                              \
     return launch_decode<DD, SS>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions, \
                                  token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,         \
                                  static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages, \
                                  num_splits, status, s)
-    if (d == 64) {
-        if (stages == 7) GO(64, 7);
-        if (stages == 6) GO(64, 6);
-        if (stages == 4) GO(64, 4);
-        GO(64, 3);
-    }
-    if (stages == 7) GO(128, 7);
-    if (stages == 6) GO(128, 6);
-    if (stages == 4) GO(128, 4);
+    if (d == 64) GO(64, 3);
     GO(128, 3);
 #undef GO
 }

@@ -824,12 +824,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
                    static_cast<bf16*>(out), tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,             \
                    block_table, table_stride, nq, nkv, page_size, window, sl2, num_pages, status);                   \
     }
-    static int two_pass = -1;                                       // LLM_PREFILL_T5=twopass keeps the two-pass kernel
-    if (two_pass < 0) {
-        const char* ev = getenv("LLM_PREFILL_T5");
-        two_pass = (ev && ev[0] == 't') ? 1 : 0;
-    }
-    if (group % 2 == 0 && !two_pass) {
+    if (group % 2 == 0) {                                           // two heads of a group share a CTA: the one-pass kernel
         const size_t smem = static_cast<size_t>(2 * 2 * T5_QHALF + 2 * T5O_STAGES * T5O_TILE) * sizeof(bf16) + 1024;
         auto kern = paged_prefill_attention_tcgen05_online_kernel;
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -839,7 +834,7 @@ extern "C" int llm_paged_attention_prefill_tcgen05(
                    window, sl2, num_pages, status);
         return launch_status();
     }
-    if (group % 2 == 0) T5_GO(2, 4) else T5_GO(1, 4)
+    T5_GO(1, 4)                                                     // odd groups: the two-pass kernel, one head per CTA
 #undef T5_GO
     return launch_status();
 }

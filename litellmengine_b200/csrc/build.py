@@ -35,7 +35,6 @@ FAMILIES: Dict[str, List[str]] = {
     "attention_prefill_tcgen05": ["attention_prefill_tcgen05.cu"],
     "sampling": ["sampling.cu"],
     "gemm_skinny": ["gemm_skinny.cu"],
-    "gemm_stream_tcgen05": ["gemm_stream_tcgen05.cu"],
     "gemm_pair_tcgen05": ["gemm_pair_tcgen05.cu"],
 }
 HEADERS = ["common.cuh", "attention_decode_noalloc.h", "attention_decode_tma.cuh"]

@@ -55,7 +55,7 @@ extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int t
 }
 
 // dst[index[i]] = value[i] for i < *count (count lives on the device so that a captured
-// graph can replay with a different number of updates).  An index outside [0, dst_len)
+// graph can replay with a different number of updates; a null count means max_count).  An index outside [0, dst_len)
 // is skipped and recorded in status.
 __global__ void scatter_int32_kernel(int32_t* __restrict__ dst, long long dst_len,
                                      const int32_t* __restrict__ index, const int32_t* __restrict__ value,
@@ -65,7 +65,7 @@ __global__ void scatter_int32_kernel(int32_t* __restrict__ dst, long long dst_le
     // griddepcontrol.wait (they only wait for the kernel just before them), which is safe
     // because nothing after this kernel starts until it has finished.
     pdl_wait();
-    const int n = min(*count, max_count);
+    const int n = count ? min(*count, max_count) : max_count;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const long long at = index[i];
         if (at < 0 || at >= dst_len) {

@@ -7,12 +7,13 @@
 // features (one 16-row tensor-core tile per warp) by 256 k-values (128 for 16 tokens), numbered
 // feature tile by feature tile, and the grid is persistent: two CTAs per SM, each taking one
 // contiguous run of items of (nearly) the same length, whatever N and K are.  A CTA streams its
-// items through three stages of shared memory (five for 16 tokens) with cp.async (32 KB of w and
-// 4 KB of x per stage) without draining the pipeline between feature tiles.  A feature tile whose items lie in
-// several CTAs gets one float32 partial sum from each, in a slice numbered by the CTA's place
-// among them (the CTA that finishes the tile zeroes the slices nobody uses); a second small
-// kernel, or the consumer, adds the slices in order (no atomics: the result does not depend on
-// timing).  When every tile lies in one CTA the result is written directly.
+// items through three stages of shared memory (five for 16 tokens): 32 KB of w per stage, brought
+// by the copy engine (one bulk copy of a stored tile, or four boxes of the plain weights; see
+// below), and 4 KB of x by cp.async, without draining the pipeline between feature tiles.  A
+// feature tile whose items lie in several CTAs gets one float32 partial sum from each, in a slice
+// numbered by the CTA's place among them (the CTA that finishes the tile zeroes the slices nobody
+// uses); a second small kernel, or the consumer, adds the slices in order (no atomics: the result
+// does not depend on timing).  When every tile lies in one CTA the result is written directly.
 // The product runs on the tensor cores with the roles swapped: w is the 16-row A operand of
 // mma.sync m16n8k16 and the tokens are the 8 columns of B (8 tokens use a full instruction,
 // 16 tokens two).  Accumulation is float32; the result is float32 or bfloat16.
@@ -56,135 +57,19 @@ __host__ __device__ __forceinline__ long long gs_cta_of(long long item, long lon
     return ((item + 1) * ctas - 1) / total;
 }
 
-// MT: token tile (8 or 16).  grid: the persistent CTAs.  slices: float32 partial-sum slices of
-// [M, N] in `partial` (1: none, y is written directly).
-template <int MT, typename TO>
-__global__ void __launch_bounds__(GS_THREADS) linear_skinny_kernel(const bf16* __restrict__ x,
-                                                                   const bf16* __restrict__ w, TO* __restrict__ y,
-                                                                   float* __restrict__ partial, int M, int N, int K,
-                                                                   int slices, int per_tile) {
-    constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT);
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK]
-    bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nk = (K + GS_BK - 1) / GS_BK, tiles = (N + GS_ROWS - 1) / GS_ROWS;
-    const long long total = static_cast<long long>(tiles) * nk, ctas = gridDim.x;
-    long long begin;
-    int count;
-    if (per_tile) {                                                      // `per_tile` CTAs share each tile's k-values evenly
-        const int t = blockIdx.x / per_tile, part = blockIdx.x % per_tile;
-        const int k_begin = static_cast<int>(static_cast<long long>(part) * nk / per_tile);
-        begin = static_cast<long long>(t) * nk + k_begin;
-        count = static_cast<int>(static_cast<long long>(part + 1) * nk / per_tile) - k_begin;
-    } else {                                                             // one run of all items, cut evenly
-        begin = blockIdx.x * total / ctas;
-        count = static_cast<int>((blockIdx.x + 1) * total / ctas - begin);
-    }
-    constexpr int CPR = GS_BK / 8;                                       // 16-byte chunks per row of a stage
-
-    auto load_w = [&](int i) {                                           // weights of item begin + i into stage i % STAGES
-        const long long item = begin + i;
-        const int n0 = static_cast<int>(item / nk) * GS_ROWS, k0 = static_cast<int>(item % nk) * GS_BK;
-        bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
-#pragma unroll
-        for (int j = 0; j < GS_ROWS * CPR / GS_THREADS; ++j) {
-            const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
-            const bool valid = (n0 + row < N) && (k0 + ch * 8 < K);
-            gs_cp_async16(gs_at<GS_BK>(ws, row, ch), w + (valid ? static_cast<size_t>(n0 + row) * K + k0 + ch * 8 : 0), valid);
-        }
-    };
-    auto load_x = [&](int i) {                                           // the tokens' rows for the same k-values
-        const int k0 = static_cast<int>((begin + i) % nk) * GS_BK;
-        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
-#pragma unroll
-        for (int j = 0; j < MT * CPR / GS_THREADS; ++j) {
-            const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
-            const bool valid = (row < M) && (k0 + ch * 8 < K);
-            gs_cp_async16(gs_at<GS_BK>(xs, row, ch), x + (valid ? static_cast<size_t>(row) * K + k0 + ch * 8 : 0), valid);
-        }
-    };
-
-    // The weights do not depend on the kernel before this one: start streaming them at once, and
-    // only then wait for that kernel (whose output is x) to finish.
-    pdl_invite();
-#pragma unroll
-    for (int s = 0; s < GS_STAGES - 1; ++s)
-        if (s < count) load_w(s);
-    pdl_wait();
-#pragma unroll
-    for (int s = 0; s < GS_STAGES - 1; ++s) {
-        if (s < count) load_x(s);
-        gs_commit();                                                     // group 0 also holds every weight copy above
-    }
-    float acc[MT / 8][4];
-#pragma unroll
-    for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-
-    int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk);
-    for (int i = 0; i < count; ++i) {
-        gs_wait<GS_STAGES - 2>();
-        __syncthreads();
-        if (i + GS_STAGES - 1 < count) {
-            load_w(i + GS_STAGES - 1);
-            load_x(i + GS_STAGES - 1);
-        }
-        gs_commit();
-        bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
-        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
-#pragma unroll
-        for (int kp = 0; kp < GS_BK / 32; ++kp) {                        // pairs of k-steps
-            unsigned a0[4], a1[4];
-            gs_ldmatrix_x4(a0, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
-            gs_ldmatrix_x4(a1, gs_at<GS_BK>(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
-#pragma unroll
-            for (int j = 0; j < MT / 8; ++j) {
-                unsigned b[4];                                           // tokens 8j..8j+7, two k-steps
-                gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
-                gs_mma(acc[j], a0, b[0], b[1]);
-                gs_mma(acc[j], a1, b[2], b[3]);
-            }
-        }
-        const bool tile_done = kt == nk - 1;
-        if (tile_done || i == count - 1) {
-            // acc[j]: features warp*16 + lane/4 (+8), tokens j*8 + (lane%4)*2 (+1)
-            const int f0 = tile * GS_ROWS + warp * 16 + (lane >> 2), t0 = (lane & 3) * 2;
-            const int slice = per_tile ? static_cast<int>(blockIdx.x % per_tile)
-                                       : static_cast<int>(blockIdx.x - gs_cta_of(static_cast<long long>(tile) * nk, total, ctas));
-#pragma unroll
-            for (int j = 0; j < MT / 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int f = f0 + (e >> 1) * 8, tok = j * 8 + t0 + (e & 1);
-                    if (f < N && tok < M) {
-                        if (slices == 1) {
-                            y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[j][e]);
-                        } else {
-                            partial[(static_cast<size_t>(slice) * M + tok) * N + f] = acc[j][e];
-                            if (tile_done && !per_tile)                  // nobody else comes after: clear the unused slices
-                                for (int z = slice + 1; z < slices; ++z) partial[(static_cast<size_t>(z) * M + tok) * N + f] = 0.0f;
-                        }
-                    }
-                    acc[j][e] = 0.0f;
-                }
-            }
-        }
-        if (tile_done) { kt = 0; ++tile; } else ++kt;
-    }
-    gs_wait<0>();
-}
-
-// ---- the same over weights stored tile by tile ------------------------------------------------------
-// `w_tiled` holds the weights as the kernel wants them in shared memory: [feature tile][k-step]
+// ---- where a stage's weights come from ----------------------------------------------------------------
+// Tiled: `w_tiled` holds the weights as the kernel wants them in shared memory: [feature tile][k-step]
 // blocks of 64 x 256 values (32 KB), each block four sub-tiles of [64 rows][64 k-values] with 128-byte
 // rows whose 16-byte chunks are XOR-swizzled by the row (chunk c of row r at position c ^ (r % 8):
 // the layout the copy engine's 128-byte swizzle writes and tcgen05 reads as a K-major operand, so
-// the same copy also serves gemm_stream_tcgen05.cu), zero-padded at the edges.  A stage of weights is then ONE
+// zero-padded at the edges.  A stage of weights is then ONE
 // contiguous piece of memory (a block of 32 KB for up to 8 tokens, half a block for 9 to 16),
 // fetched by one bulk copy (cp.async.bulk) of one thread instead of 2,048 sixteen-byte copies
 // of 128 threads, and DRAM sees whole pages instead of 512-byte runs 8 KB apart (measured with
-// the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for this kernel's strided
-// form).  The tokens' rows still come by cp.async.  The wait on a stage's mbarrier is bounded;
+// the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for the strided form; a whole
+// decode step of the Qwen3-8B shape at batch 8: 3.60 ms from the stored tiles, 3.69 ms from boxes
+// of the plain weights, 3.75 ms with sixteen-byte cp.async copies of the plain weights).  The
+// tokens' rows come by cp.async.  The wait on a stage's mbarrier is bounded;
 // when it runs out the kernel records status code 8 and goes on (its result is then flagged).
 #define GS_TILED_BK 256          // k-values of a stored block
 #define GS_TILED_WAIT_LIMIT 2000000
@@ -421,26 +306,6 @@ extern "C" int llm_linear_skinny_splits(int M, int N, int K) {
     return slices;
 }
 
-template <int MT, typename TO>
-static int launch_skinny(const bf16* x, const bf16* w, void* y, float* scratch, long long scratch_floats, int M, int N,
-                         int K, int keep_partials, cudaStream_t s) {
-    if (!skinny_device()) return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK_FOR(MT) * sizeof(bf16);
-    auto kern = linear_skinny_kernel<MT, TO>;
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    int ctas, slices, per_tile;
-    skinny_plan(N, K, GS_BK_FOR(MT), &ctas, &slices, &per_tile);
-    if (slices > 1 && (scratch == nullptr || scratch_floats < static_cast<long long>(slices) * M * N))
-        return LLM_REFUSED_SIZE;                                         // the caller sizes scratch with llm_linear_skinny_scratch_floats
-    launch_pdl(kern, dim3(ctas), dim3(GS_THREADS), smem, s, x, w, static_cast<TO*>(y), scratch, M, N, K, slices, per_tile);
-    int rc = launch_status();
-    if (rc != LLM_OK || slices == 1 || keep_partials) return rc;     // the caller's next kernel adds the slices itself
-    const long long mn = static_cast<long long>(M) * N;
-    launch_pdl((linear_skinny_sum_kernel<TO>), dim3(static_cast<unsigned>((mn + 255) / 256)), dim3(256), 0, s, scratch, static_cast<TO*>(y), mn, slices);
-    return launch_status();
-}
-
 // The tiled form of llm_linear_skinny for M <= 8: w_tiled is what llm_linear_skinny_tiled_elems
 // describes (blocks of 64 x 256 in the kernel's shared-memory order).  status: int32 [2].
 extern "C" long long llm_linear_skinny_tiled_elems(int N, int K) {
@@ -546,23 +411,3 @@ extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void*
                                    : launch_skinny_tiled<16, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 
-// x: bfloat16 [M, K]; w: bfloat16 [N, K]; y: [M, N] float32 (out_dtype 0) or bfloat16 (1);
-// scratch: float32 of scratch_floats elements (llm_linear_skinny_scratch_floats tells how many).
-// keep_partials: with more than one slice, leave the partial sums in scratch as [slices, M, N]
-// and write nothing to y (llm_linear_skinny_splits tells the count beforehand).
-extern "C" int llm_linear_skinny(const void* x, const void* w, void* y, int out_dtype, float* scratch,
-                                 long long scratch_floats, int M, int N, int K, int keep_partials, uintptr_t stream) {
-    if (!llm_linear_skinny_supported(M, N, K)) return LLM_REFUSED_SIZE;
-    if (!aligned16(x) || !aligned16(w)) return LLM_REFUSED_ALIGN;
-    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const bf16* xp = static_cast<const bf16*>(x);
-    const bf16* wp = static_cast<const bf16*>(w);
-    if (M <= 8) {
-        if (out_dtype == LLM_DT_F32) return launch_skinny<8, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
-        if (out_dtype == LLM_DT_BF16) return launch_skinny<8, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
-    } else {
-        if (out_dtype == LLM_DT_F32) return launch_skinny<16, float>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
-        if (out_dtype == LLM_DT_BF16) return launch_skinny<16, bf16>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, s);
-    }
-    return LLM_REFUSED_DTYPE;
-}

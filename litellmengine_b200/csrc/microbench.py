@@ -100,7 +100,7 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--out-dtype", default="bfloat16")
-    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "stream", "pair", "pair_silu", "library_silu"],
+    ap.add_argument("--impl", default="auto", choices=["auto", "library", "own", "tcgen05", "pair", "pair_silu", "library_silu"],
                     help="linear: the library product, the engine's own streaming kernel, or what the engine picks")
     ap.add_argument("--tiled", action="store_true", help="linear --impl own: over a tile-by-tile copy of the weights")
     ap.add_argument("--chain", type=int, default=0,
@@ -171,14 +171,12 @@ def main():
         x = torch.randn(args.tokens, args.k, device=dev, dtype=torch.bfloat16)
         w = torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02
         od = torch.float32 if args.out_dtype == "float32" else torch.bfloat16
-        if args.tiled or args.impl == "stream":
+        if args.tiled:
             ops.prepare_streaming(w)
         if args.impl == "library":
             fn = lambda: torch.mm(x, w.t(), out_dtype=od) if od != x.dtype else torch.mm(x, w.t())
         elif args.impl == "own":
             fn = lambda: ops.linear_skinny(x, w, od)
-        elif args.impl == "stream":
-            fn = lambda: ops.linear_stream(x, w, od)
         elif args.impl == "pair":
             fn = lambda: ops.linear_pair(x, w, od)
         elif args.impl == "pair_silu":                            # w is [gate; up]: N = 2 I
@@ -189,12 +187,11 @@ def main():
             fn = lambda: ops.linear(x, w, out_dtype=od)
         if args.chain:
             ws = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(args.chain)]
-            if args.tiled or args.impl == "stream":
+            if args.tiled:
                 for wi in ws:
                     ops.prepare_streaming(wi)
             one = {"library": lambda wi: torch.mm(x, wi.t(), out_dtype=od) if od != x.dtype else torch.mm(x, wi.t()),
-                   "own": lambda wi: ops.linear_skinny(x, wi, od),
-                   "stream": lambda wi: ops.linear_stream(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))
+                   "own": lambda wi: ops.linear_skinny(x, wi, od)}.get(args.impl, lambda wi: ops.linear(x, wi, out_dtype=od))
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
                 for wi in ws:

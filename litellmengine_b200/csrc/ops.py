@@ -139,7 +139,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
 
 def scatter_int32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor, count: torch.Tensor,
                   max_count: int, status: torch.Tensor) -> None:
-    """dst.flat[index[i]] = value[i] for i < count[0] (count is a device scalar)."""
+    """dst.flat[index[i]] = value[i] for i < count[0] (count is a device scalar; None: for i < max_count)."""
     _dev(dst, index, value, count, status)
     for t, n in ((dst, "dst"), (index, "index"), (value, "value"), (count, "count")):
         _i32(t, n)
@@ -509,15 +509,35 @@ def skinny_scratch(device, floats: int) -> Optional[torch.Tensor]:
     return t
 
 
-SKINNY_MAX_ROWS = 16     # rows up to which `linear` may take the engine's own streaming kernel
-_SKINNY_POLICY = os.environ.get("LLM_SKINNY", "all")     # all | auto | off: which products of few rows take it
+SKINNY_MAX_ROWS = 16     # rows up to which `linear` takes the engine's own streaming kernel
 
 
 # ---- weights stored tile by tile for the streaming product ----------------------------------
-_TILED_POLICY = os.environ.get("LLM_TILED", "auto")   # on | auto | off: keep a tiled copy of decode weights
-_TILED_RESERVE = 0.30                                  # auto: only while this share of the device's memory stays free
+# The streaming product reads the plain [N, K] weights box by box through the copy engine, or, 2.5 %
+# (batch 8) to 4.5 % (batch 1) faster per decode step, a second copy of them stored in its
+# shared-memory order.  That copy doubles the weights' memory, so it is made only for models whose
+# weights are a small share of the device: `begin_model` decides once per model.
+_TILED_POLICY = os.environ.get("LLM_TILED", "auto")   # on | auto | off
+_TILED_SHARE = 0.125                                   # auto: models whose matrices take up to this share of the device's memory
 _tiled: Dict[int, torch.Tensor] = {}                   # weight.data_ptr() -> its tiled copy
+_tiled_allowed = _TILED_POLICY != "off"          # until a model says otherwise (`begin_model`)
 TILE_ROWS, TILE_K = 64, 256
+
+
+def begin_model(matrix_bytes: int, device) -> bool:
+    """Called before a model's weights are loaded with the bytes of its bfloat16 matrices: decides
+    whether `prepare_streaming` makes tiled copies for them (all of them or none).  `LLM_TILED=on` /
+    `off` overrides the rule."""
+    global _tiled_allowed
+    device = torch.device(device)
+    if _TILED_POLICY == "off" or device.type != "cuda":
+        _tiled_allowed = False
+    elif _TILED_POLICY == "on":
+        _tiled_allowed = True
+    else:
+        _, total = torch.cuda.mem_get_info(device)
+        _tiled_allowed = matrix_bytes <= _TILED_SHARE * total
+    return _tiled_allowed
 
 
 def tile_weight(weight: torch.Tensor) -> torch.Tensor:
@@ -539,22 +559,14 @@ def tile_weight(weight: torch.Tensor) -> torch.Tensor:
 
 
 def prepare_streaming(weight: Optional[torch.Tensor]) -> None:
-    """Keep a tiled copy of a bfloat16 weight for decode steps of up to 16 tokens (twice the
-    memory for that weight).  `LLM_TILED=off` keeps one copy, `on` always makes the second, `auto`
-    (the default) makes it while 30 % of the device's memory stays free afterwards, so that a model
-    that fills most of the device leaves its room to the cache.  The copy lives as long as the weight."""
-    if (weight is None or _TILED_POLICY == "off" or not weight.is_cuda or weight.dtype != torch.bfloat16
+    """Keep a tiled copy of a bfloat16 weight for decode steps of up to 16 tokens, if `begin_model`
+    allowed copies for the model being loaded.  The copy lives as long as the weight."""
+    if (weight is None or not _tiled_allowed or not weight.is_cuda or weight.dtype != torch.bfloat16
             or weight.dim() != 2 or weight.shape[1] % 8 != 0):
         return
     key = weight.data_ptr()
     if key in _tiled:
         return
-    if _TILED_POLICY != "on":
-        free, total = torch.cuda.mem_get_info(weight.device)
-        free += torch.cuda.memory_reserved(weight.device) - torch.cuda.memory_allocated(weight.device)   # cached blocks are free
-        size = weight.numel() * weight.element_size()
-        if free - size < _TILED_RESERVE * total or free < 3 * size:     # what stays; what making it needs meanwhile
-            return
     _tiled[key] = tile_weight(weight)
     weakref.finalize(weight, _tiled.pop, key, None)
 
@@ -563,8 +575,8 @@ _tiled_generation = 0
 
 
 def release_streaming() -> int:
-    """Drop every tiled copy (the weights themselves stay; products read them in their plain layout
-    from then on).  Returns how many copies went.  Captured CUDA graphs that read the copies must
+    """Drop every tiled copy (the weights themselves stay; products fetch them box by box from their
+    plain layout from then on).  Returns how many copies went.  Captured CUDA graphs that read the copies must
     not be replayed afterwards: `streaming_generation` changes, and the runner drops its graphs."""
     global _tiled_generation
     n = len(_tiled)
@@ -594,19 +606,10 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         raise KernelError("x and weight disagree on K")
     global launch_count
     tiled = _tiled.get(weight.data_ptr())
-    if tiled is not None:
-        g = _fn("gemm_skinny", "llm_linear_skinny_tiled",
-                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-        st = stream_status(x.device)
-        f = lambda xp, wp, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, _ptr(tiled), yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
-    elif os.environ.get("LLM_SKINNY_SRC", "boxes") == "boxes":
-        g = _fn("gemm_skinny", "llm_linear_skinny_boxes",
-                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-        st = stream_status(x.device)
-        f = lambda xp, wp, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, wp, yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
-    else:
-        f = _fn("gemm_skinny", "llm_linear_skinny",
-                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    g = _fn("gemm_skinny", "llm_linear_skinny_tiled" if tiled is not None else "llm_linear_skinny_boxes",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    st, wp = stream_status(x.device), _ptr(tiled if tiled is not None else weight)
+    f = lambda xp, _w, yp, dt, sp, sn, m, n, k, keep, stream: g(xp, wp, yp, dt, sp, sn, m, n, k, keep, _ptr(st), stream)
     splits = _fn("gemm_skinny", "llm_linear_skinny_splits", [c_int, c_int, c_int])(M, N, K)
     if partials_ok and splits > 1 and out is None:
         parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
@@ -621,55 +624,17 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
-STREAM_MAX_ROWS = 128    # rows up to which `linear` may take the tcgen05 weight-streaming kernel
-# off | on.  Off by default: 52-100 us where the library's kernels for these shapes take 37-40 (see the
-# header of gemm_stream_tcgen05.cu for what was measured and what the kernel needs next).
-_STREAM_POLICY = os.environ.get("LLM_STREAM", "off")
 _stream_status: Dict[str, torch.Tensor] = {}
 
 
 def stream_status(device) -> torch.Tensor:
-    """The status word of the tcgen05 products (code 7: a bounded wait of the streaming product ran
-    out; 9: of the paired product)."""
+    """The status word of the engine's matrix products (code 8: a bounded wait of the weight-streaming
+    product ran out; 9: of the paired product)."""
     key = str(device)
     t = _stream_status.get(key)
     if t is None:
         t = _stream_status[key] = torch.zeros(2, dtype=torch.int32, device=device)
     return t
-
-
-def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
-                  out: Optional[torch.Tensor] = None, partials_ok: bool = False):
-    """x [T <= 128, K] @ weight[N, K]^T with the tcgen05 weight-streaming kernel (the weights from
-    their tile-by-tile copy, see `prepare_streaming`; float32 accumulation in tensor memory, float32
-    or bfloat16 result).  With `partials_ok` a product that is cut along K comes back as a
-    `PartialSum`."""
-    _dev(x, weight, out)
-    tiled = _tiled.get(weight.data_ptr())
-    if tiled is None:
-        raise KernelError("the streaming product wants a weight prepared with prepare_streaming")
-    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
-        raise KernelError("the streaming product takes bfloat16 operands")
-    T, K = x.shape
-    N = weight.shape[0]
-    if weight.shape[1] != K:
-        raise KernelError("x and weight disagree on K")
-    global launch_count
-    f = _fn("gemm_stream_tcgen05", "llm_linear_stream",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    slices = _fn("gemm_stream_tcgen05", "llm_linear_stream_slices", [c_int, c_int, c_int])(T, N, K)
-    status = stream_status(x.device)
-    if partials_ok and slices > 1 and out is None:
-        parts = torch.empty((slices, T, N), dtype=torch.float32, device=x.device)
-        _check(f(_ptr(x), _ptr(tiled), None, 0, _ptr(parts), parts.numel(), T, N, K, 1, _ptr(status), _stream()), "linear_stream")
-        return PartialSum(parts, None if out_dtype == torch.float32 else out_dtype)
-    if out is None:
-        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
-    scratch = skinny_scratch(x.device, slices * T * N if slices > 1 else 0)
-    _check(f(_ptr(x), _ptr(tiled), _ptr(out), _dt(out), _ptr(scratch), scratch.numel() if scratch is not None else 0,
-             T, N, K, 0, _ptr(status), _stream()), "linear_stream")
-    launch_count += 1 if slices > 1 else 0        # the kernel that adds the slices
-    return out
 
 
 def linear_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
@@ -773,12 +738,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
-            and x.shape[1] % 8 == 0 and (_SKINNY_POLICY == "all" or (
-                _SKINNY_POLICY == "auto" and (x.shape[1] >= 8192 or weight.shape[0] >= 65536)))):
+            and x.shape[1] % 8 == 0 and weight.data_ptr() % 16 == 0):
         return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
-    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
-            and x.shape[1] % 8 == 0 and _STREAM_POLICY == "on" and weight.data_ptr() in _tiled):
-        return linear_stream(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if x.shape[0] >= PAIR_MIN_ROWS and (out_dtype or x.dtype) in (torch.float32, torch.bfloat16) and _pair_takes(
             x, weight, weight.shape[0], "plain"):
         return linear_pair(x, weight, out_dtype or x.dtype)

@@ -46,7 +46,7 @@ class _Region:
         self.off = {}
         sections = [("token_ids", T), ("positions", T), ("token_entry", T), ("entry_slot", B),
                     ("entry_q_start", B), ("entry_q_len", B), ("entry_kv_len", B), ("want_rows", T),
-                    ("want_slot", T), ("counts", 8 + num_groups)]
+                    ("want_slot", T), ("counts", 8 + num_groups), ("state_index", 8 * B), ("state_value", 8 * B)]
         for p in preludes:
             sections += [(f"{p.name}:{k}", int(n)) for k, n in p.sections(T, B).items()]
         self.prelude_keys = {p.name: list(p.sections(T, B)) for p in preludes}
@@ -137,16 +137,19 @@ class StepBatch:
     feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
     layout: str = "large"                     # which of StepBuffers' two layouts holds this step's arrays
     preludes: Dict[str, object] = field(default_factory=dict)   # the parts' `StepPrelude` views by name
+    state_ranges: List[tuple] = field(default_factory=list)     # (offset, count) of each state write in the buffer
     # what a part computes on the device in the first layer that needs it and shares with the layers
     # after it (emptied before a step is captured as a graph, so that the graph holds the kernel)
     tables: Dict[object, object] = field(default_factory=dict)
 
 
 def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
-              feedback: Optional[torch.Tensor] = None) -> StepBatch:
+              feedback: Optional[torch.Tensor] = None, state_writes=()) -> StepBatch:
     """Fill the pinned buffer from `entries` (whose `past` is set) and the cache manager's
     pending table `updates`, let every prelude fill its share, start the copy, and return the
-    device views."""
+    device views.  `state_writes`: [(flat indices, int32 values)] to be written into per-request
+    state tensors by the step function after the copy (they ride in the same buffer; at most
+    8 values per entry in all); their places in the buffer come back in `batch.state_ranges`."""
     B = len(entries)
     q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
     T = int(q_len.sum())
@@ -197,6 +200,15 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         hv(f"upd_index{g}")[:len(idx)] = idx
         hv(f"upd_value{g}")[:len(val)] = val
         counts[8 + g] = len(idx)
+    at, ranges = 0, []
+    for idx, val in state_writes:
+        n = len(idx)
+        if at + n > 8 * buffers.max_entries:
+            raise ValueError("more per-request state values than the step buffer holds")
+        hv("state_index")[at:at + n] = idx
+        hv("state_value")[at:at + n] = val
+        ranges.append((at, n))
+        at += n
     region.upload()
     dv = region.dev_view
     batch = StepBatch(
@@ -206,6 +218,7 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=int(q_len.max()),
         max_kv_len=int((past + q_len).max()), entries=entries, feedback=feedback,
         layout="small" if region is buffers.small else "large")
+    batch.state_ranges = ranges
     for p, got in filled:
         batch.preludes[p.name] = p.views({k: dv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}, got)
     return batch

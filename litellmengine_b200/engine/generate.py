@@ -19,6 +19,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..sampling import Sampler
+from ..sampling.sampler import slot_state_row
 from .batch import StepEntry
 from .request import GenerationRequest, RequestStatus
 from .runner import ModelRunner
@@ -90,11 +91,12 @@ class PagedGenerateEngine:
     def _launch(self, plan: List[ScheduledPortion]):
         """Everything of a step that needs no answer from the device: pages, metadata, kernels,
         sampling into `runner.sampled`, and the start of the copy of the sampled tokens."""
-        entries, samplers = [], []
+        entries, samplers, admitted = [], [], []
         for p in plan:
             req = p.request
-            if req.cached_len == 0:           # first portion since admission: bind its random stream
-                self.sampler.admit(req.slot, req.seed, len(req.generated_ids) + req.pending, req.temperature)
+            if req.cached_len == 0:           # first portion since admission: bind its random stream (in this step's upload)
+                admitted.append(("sampler", req.slot, slot_state_row(req.seed, len(req.generated_ids) + req.pending,
+                                                                     req.temperature)))
             end = req.cached_len + p.num_tokens
             toks = req.input_ids[req.cached_len:end]
             feedback = -1
@@ -104,7 +106,7 @@ class PagedGenerateEngine:
             entries.append(StepEntry(req.slot, toks, [p.num_tokens - 1] if p.samples else [], feedback=feedback))
             if p.samples:
                 samplers.append(req)
-        batch = self.runner.prepare(entries)
+        batch = self.runner.prepare(entries, state_writes=admitted)
         logits = self.runner.forward(batch)
         self.runner.finish(batch)
         which = self._launched & 1

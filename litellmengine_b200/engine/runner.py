@@ -4,9 +4,9 @@ calls this one function; everything below it (model, cache, kernels) is called f
 """
 from __future__ import annotations
 
-import os
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages, StateNeed
@@ -22,7 +22,6 @@ STATUS_TEXT = {1: "a token id outside the vocabulary reached the embedding kerne
                4: "attention met a page number outside the pool",
                5: "a wait on a copy barrier in the decode attention kernel ran out",
                6: "a wait on a barrier in the tcgen05 prompt attention kernel ran out",
-               7: "a wait on a barrier in the tcgen05 streaming product ran out",
                8: "a wait on a copy barrier in the weight-streaming product ran out",
                9: "a wait on a barrier in the paired tcgen05 product ran out"}
 
@@ -107,8 +106,11 @@ class ModelRunner:
         self.cache.release(slot)
 
     # ---- the step --------------------------------------------------------------------------
-    def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
-        """Host half of a step: checks, pages, metadata upload, block-table updates."""
+    def prepare(self, entries: Sequence[StepEntry], state_writes=()) -> StepBatch:
+        """Host half of a step: checks, pages, metadata upload, block-table updates.
+        `state_writes`: [(name of a per-request state tensor of int32, slot, values)]: the values
+        become that slot's row before the step's first kernel runs; they travel in the step's own
+        upload, so admitting a request costs no copy of its own."""
         entries = list(entries)
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -120,9 +122,11 @@ class ModelRunner:
             if len(e.tokens) == 0:
                 raise ValueError("an entry needs at least one token")
             known = e.tokens if e.feedback < 0 else e.tokens[:-1]     # the last one may still be on the device
-            for t in known:
-                if not 0 <= int(t) < V:
-                    raise ValueError(f"token id {t} is outside the vocabulary [0, {V})")
+            if len(known):
+                ids = np.asarray(known, dtype=np.int64)
+                if int(ids.min()) < 0 or int(ids.max()) >= V:
+                    bad = int(ids[(ids < 0) | (ids >= V)][0])
+                    raise ValueError(f"token id {bad} is outside the vocabulary [0, {V})")
             if e.feedback >= self.sampled.numel():
                 raise ValueError(f"feedback index {e.feedback} is outside the {self.sampled.numel()} sampled tokens")
             e.past = self.cache.length(e.slot)
@@ -133,9 +137,21 @@ class ModelRunner:
             raise OutOfPages("the step's tokens do not fit the free pages")
         for e in entries:
             self.cache.ensure(e.slot, e.past + len(e.tokens))
-        batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled)
+        writes = []
+        for name, slot, values in state_writes:
+            t = self.cache.state[name]
+            if t.dtype != torch.int32 or len(values) != t[0].numel():
+                raise ValueError(f"state {name!r} wants {t[0].numel()} int32 values per request")
+            base = slot * t[0].numel()
+            writes.append((np.arange(base, base + len(values), dtype=np.int64), np.asarray(values, dtype=np.int64)))
+        batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled, state_writes=writes)
         region = self.buffers.last                              # where pack_step put this step
         counts = region.dev_view("counts")
+        for (name, _, _), (at, n) in zip(state_writes, batch.state_ranges):
+            o = region.off["state_index"][0]
+            v = region.off["state_value"][0]
+            ops.scatter_int32(self.cache.state[name].view(-1), region.dev[o + at:o + at + n], region.dev[v + at:v + at + n],
+                              None, n, self.buffers.status)
         for g, group in enumerate(self.cache.groups):
             n = int(region.host_view("counts")[8 + g])
             if n:

@@ -2,7 +2,6 @@
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 from typing import Dict, Optional
 
@@ -158,7 +157,6 @@ class AttentionMixer:
 
 
 _slots = {}
-_PREFILL_KERNEL = os.environ.get("LLM_PREFILL", "tcgen05")     # "mma" keeps the mma.sync kernel everywhere
 
 
 def _cta_slots(device) -> int:
@@ -190,7 +188,7 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
                                        nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
         if work.num_prefill_tiles:
             kernel = (ops.paged_attention_prefill_tcgen05
-                      if _PREFILL_KERNEL != "mma" and ops.prefill_tcgen05_supported(d, ctx.page_size)
+                      if ops.prefill_tcgen05_supported(d, ctx.page_size)
                       else ops.paged_attention_prefill)       # tcgen05/TMEM/TMA where it applies, mma.sync otherwise
             kernel(q, out, cache, work.prefill_tiles, work.num_prefill_tiles, b.entry_slot, b.entry_q_start,
                    b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

@@ -59,6 +59,9 @@ class Model:
         p = self.plan
         params = self.parameters()
         aliased = check_source(params, source, where)
+        if self.dtype == torch.bfloat16:               # one decision for all of the model's matrices
+            ops.begin_model(sum(2 * ps.shape[0] * ps.shape[1] for n, ps in params.items()
+                                if len(ps.shape) == 2 and n not in aliased), self.device)
         get = lambda n: fetch_tensor(source, n, params[n], self.dtype, self.device)
         self.embedding = get(p.embedding_name).contiguous()
         for spec, block in zip(p.blocks, self.blocks):

@@ -461,8 +461,8 @@ def test_prefill_kernel_window_edges(window):
 @pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (16, 48, 4096), (9, 1000, 1544),
                                    (5, 17, 8), (8, 6144, 4096)])
 def test_skinny_product(M, N, K, out_dtype):
-    """The weight-streaming product for decode steps against float64, at sizes that are no multiple
-    of its tiles (N of 16, K of 512, M of 8)."""
+    """The weight-streaming product for decode steps, its weights fetched box by box from their plain
+    layout, against float64, at sizes that are no multiple of its tiles (N of 64, K of 256, M of 8)."""
     torch.manual_seed(M * 1000 + N)
     x = torch.randn(M, K).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
@@ -470,6 +470,7 @@ def test_skinny_product(M, N, K, out_dtype):
     got = ops().linear_skinny(x.to(DEV), w.to(DEV), DT[out_dtype])
     assert got.dtype == DT[out_dtype] and got.shape == (M, N)
     close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
+    assert ops().stream_status(DEV).tolist() == [0, 0]
     lib = torch.mm(x.to(DEV), w.to(DEV).t(), out_dtype=torch.float32)
     close(got, lib, 2e-5 if out_dtype == "float32" else 6e-3)      # and against the library product
 
@@ -519,28 +520,6 @@ def test_output_head_at_the_real_vocabulary(M):
     assert torch.equal(tiled, plain)
     assert ops().argmax_rows(tiled).tolist() == torch.argmax(lib, dim=1).tolist()
     assert int(ops().argmax_rows(tiled)[0]) == 151935
-    assert ops().stream_status(DEV).tolist() == [0, 0]
-
-
-@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,N,K", [(17, 16, 512), (33, 100, 520), (64, 331, 80), (20, 48, 4096), (128, 1000, 1544),
-                                   (65, 17, 8), (64, 6144, 4096), (32, 4096, 12288), (100, 300, 64)])
-def test_stream_tcgen05_product(T, N, K, out_dtype):
-    """The tcgen05 weight-streaming product for 17..128 rows against float64, at sizes that are no
-    multiple of its tiles (N of 128, K of 64, T of 32/64/128), in both ways of cutting the work
-    (whole k-splits per tile; one even run of items per CTA) and with the partial sums left to
-    the caller."""
-    torch.manual_seed(T * 1000 + N)
-    x = torch.randn(T, K).to(torch.bfloat16)
-    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
-    ref = x.double() @ w.double().T
-    wd = w.to(DEV)
-    ops().prepare_streaming(wd)
-    got = ops().linear_stream(x.to(DEV), wd, DT[out_dtype])
-    assert got.dtype == DT[out_dtype] and got.shape == (T, N)
-    close(got, ref, 2e-5 if out_dtype == "float32" else 6e-3)
-    parts = ops().linear_stream(x.to(DEV), wd, DT[out_dtype], partials_ok=True)
-    close(ops().as_tensor(parts), ref, 2e-5 if out_dtype == "float32" else 6e-3)
     assert ops().stream_status(DEV).tolist() == [0, 0]
 
 
