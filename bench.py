@@ -402,7 +402,10 @@ class Bench:
             out = engine.generate(prompts, max_new_tokens=64)
             torch.cuda.synchronize()
             return sum(len(o) for o in out), time.perf_counter() - t0, runner.steps_run - steps0
-        job()                                               # warm-up: kernels built, graphs captured
+        # Warm-up, twice: a decode step of a batch size is captured as a graph the second time that size is
+        # seen, and the sizes of the tail (requests finishing one by one) occur once a job.
+        job()
+        job()
         made, secs, nsteps = job()
         d32 = self.decode_device_timed(runner, 32, 32, 8, context=384)
         points["qwen3_0p6b_mixed"] = {

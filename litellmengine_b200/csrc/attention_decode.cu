@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = nq / nkv, h0 = kvh * G;
     const int t = rows ? rows[r] : r;
+    if (t < 0) return;                                              // a padding entry of the row list: no work
     const int pos = positions[t];
     const int32_t* table = block_table + static_cast<size_t>(entry_slot[token_entry[t]]) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -274,6 +275,7 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
     pdl_begin();
     const int r = blockIdx.x, h = blockIdx.y;
     const int t = rows ? rows[r] : r;
+    if (t < 0) return;                                              // a padding entry of the row list: no work
     const size_t hrow = static_cast<size_t>(r) * nq + h;
     float M = -CUDART_INF_F;
     for (int s = 0; s < num_splits; ++s)

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = nq / nkv, h0 = kvh * G;
     const int t = rows ? rows[r] : r;
+    if (t < 0) return;                                              // a padding entry of the row list: no work
     const int pos = positions[t];
     const int32_t* table = block_table + static_cast<size_t>(entry_slot[token_entry[t]]) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;

@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int tile = blockIdx.y, h = blockIdx.x;      // heads vary fastest: the tile list's expensive tiles start first
     const int kvh = h / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    if (e < 0) return;                                            // a padding entry of the tile list: no work
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
     const int past = kv_len - q_len;
     const int row_base = entry_q_start[e] + q0;                       // batch row of the tile's first query

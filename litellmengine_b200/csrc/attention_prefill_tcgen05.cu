@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(64 + 128 * HEADS, 1) paged_prefill_attention_t
     const int h0 = blockIdx.x * HEADS;                            // first query head of this CTA
     const int kvh = h0 / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    if (e < 0) return;                                            // a padding entry of the tile list: no work
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
     const int past = kv_len - q_len;
     const int row_base = entry_q_start[e] + q0;
@@ -467,6 +468,7 @@ __global__ void __launch_bounds__(T5O_THREADS, 1) paged_prefill_attention_tcgen0
     const int h0 = blockIdx.x * 2;                                // first of this CTA's two query heads
     const int kvh = h0 / (nq / nkv);
     const int e = tiles[2 * tile], q0 = tiles[2 * tile + 1];
+    if (e < 0) return;                                            // a padding entry of the tile list: no work
     const int q_len = entry_q_len[e], kv_len = entry_kv_len[e];
     const int past = kv_len - q_len;
     const int row_base = entry_q_start[e] + q0;

@@ -110,8 +110,28 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_bound_stream: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _bound_stream if _bound_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class bound_stream:
+    """Inside this scope every launch goes to the stream that was current at its entry, looked up
+    once (asking for the current stream costs as much as three launches).  For code that does not
+    switch streams while it runs: a model's forward pass."""
+
+    def __enter__(self):
+        global _bound_stream
+        self._prev = _bound_stream
+        _bound_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _bound_stream
+        _bound_stream = self._prev
+        return False
 
 
 def _i32(t: Optional[torch.Tensor], what: str) -> None:

@@ -137,6 +137,11 @@ class StepBatch:
     feedback: Optional[torch.Tensor] = None   # int32 device buffer that negative token ids point into
     layout: str = "large"                     # which of StepBuffers' two layouts holds this step's arrays
     preludes: Dict[str, object] = field(default_factory=dict)   # the parts' `StepPrelude` views by name
+    # True while the step is captured as a graph that must serve ANY step of as many tokens: kernels
+    # whose work depends on how the tokens are divided among requests launch over their preludes'
+    # padded lists, and the wanted rows are `want_rows` padded to `want_cap` entries
+    any_division: bool = False
+    want_cap: int = 0
     state_ranges: List[tuple] = field(default_factory=list)     # (offset, count) of each state write in the buffer
     # what a part computes on the device in the first layer that needs it and shares with the layers
     # after it (emptied before a step is captured as a graph, so that the graph holds the kernel)
@@ -185,6 +190,9 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
                 raise ValueError(f"want={j} is outside the entry's {n} tokens")
             wr[w], ws[w] = int(q_start[i]) + j, e.slot
             w += 1
+    want_cap = min(buffers.max_entries, region.token_cap)
+    if w < want_cap:
+        wr[w:want_cap] = 0                                        # padding for a graph that reads `want_cap` rows
     hv("entry_slot")[:B] = slot
     hv("entry_q_start")[:B] = q_start
     hv("entry_q_len")[:B] = q_len
@@ -217,7 +225,7 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
         status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=int(q_len.max()),
         max_kv_len=int((past + q_len).max()), entries=entries, feedback=feedback,
-        layout="small" if region is buffers.small else "large")
+        layout="small" if region is buffers.small else "large", want_cap=want_cap)
     batch.state_ranges = ranges
     for p, got in filled:
         batch.preludes[p.name] = p.views({k: dv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}, got)

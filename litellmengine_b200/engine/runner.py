@@ -34,6 +34,11 @@ class ModelRunner:
     has `step`.
     """
 
+    # Graphs of "any step of T tokens" are kept for steps short enough that launching their kernels one
+    # by one costs as much as running them, and for a bounded number of different T.
+    MIXED_GRAPH_MAX_TOKENS = 1024
+    MIXED_GRAPH_MAX_COUNT = 16
+
     def __init__(self, model: Model, page_size: int = 16, max_total_tokens: int = 4096,
                  max_requests: int = 64, max_tokens_per_step: int = 8192,
                  max_request_tokens: Optional[int] = None, use_graphs: bool = True):
@@ -70,6 +75,8 @@ class ModelRunner:
             getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
             for b in model.blocks)
         self._graphs = {}
+        self._mixed_graphs = True               # graphs for steps that are not all single decoded tokens
+        self._mixed_count = 0
         self._graph_seen = {}
         self._graph_pool = None
         self._graph_weights = ops.streaming_generation()
@@ -166,33 +173,50 @@ class ModelRunner:
         self.steps_run += 1
 
     def forward(self, batch: StepBatch) -> torch.Tensor:
-        """The device half of a step.  A step of B single decoded tokens that wants all B logits
-        replays a captured CUDA graph of the same kernels; everything else launches them one by
-        one.  A graph's logits tensor is reused by the next replay of that batch size: read it
-        (sample, copy) before stepping again."""
-        B = batch.num_tokens
-        if self.use_graphs and batch.max_q_len == 1 and batch.num_want == B:
+        """The device half of a step.  Steps are replayed as captured CUDA graphs of the same kernels
+        where one graph can serve them: a step of B single decoded tokens that wants all B logits
+        (one graph per B), and any other step of T tokens that wants at most one row per entry slot
+        (one graph per T: its attention kernels run over padded work lists, so it does not matter how
+        the T tokens are divided among requests).  A graph is captured the second time its key is
+        seen; everything else launches the kernels one by one.  A graph's logits tensor is reused by
+        the next replay of that graph: read it (sample, copy) before stepping again."""
+        if self.use_graphs:
+            B = batch.num_tokens
             if self._graph_weights != ops.streaming_generation():   # the tiled weight copies a graph points at are gone
                 self._graphs.clear()
+                self._mixed_count = 0
                 self._graph_weights = ops.streaming_generation()
-            key = (B, batch.layout)                  # a graph holds the device addresses of one layout
-            g = self._graphs.get(key)
-            if g is None:
-                seen = self._graph_seen.get(key, 0)
-                self._graph_seen[key] = seen + 1
-                if seen >= 1:
-                    g = self._capture(batch)
-            if g is not None:
-                g[0].replay()
-                self.graph_replays += 1
-                ops.launch_count += g[2]          # the kernels the graph holds ran again
-                return g[1]
+            if batch.max_q_len == 1 and batch.num_want == B:
+                key = (B, "decode", batch.layout)                 # a graph holds the device addresses of one layout
+            elif self._mixed_graphs and batch.num_want <= batch.want_cap and B <= self.MIXED_GRAPH_MAX_TOKENS:
+                # "none": a prompt portion that wants nothing has no output head in its graph
+                key = (B, "any" if batch.num_want else "none", batch.layout)
+                if key not in self._graphs and self._mixed_count >= self.MIXED_GRAPH_MAX_COUNT:
+                    key = None
+            else:
+                key = None
+            if key is not None:
+                g = self._graphs.get(key)
+                if g is None:
+                    seen = self._graph_seen.get(key, 0)
+                    self._graph_seen[key] = seen + 1
+                    if seen >= 1:
+                        g = self._capture(batch, key)
+                if g is not None:
+                    g[0].replay()
+                    self.graph_replays += 1
+                    ops.launch_count += g[2]          # the kernels the graph holds ran again
+                    return g[1] if key[1] == "decode" else g[1][:batch.num_want]
         return self.model.forward(batch, self.cache)
 
-    def _capture(self, batch: StepBatch):
-        B = batch.num_tokens
-        real_max_kv = batch.max_kv_len
+    def _capture(self, batch: StepBatch, key):
+        real = (batch.max_kv_len, batch.num_want, batch.want_rows, batch.any_division)
         batch.max_kv_len = 1 << 30              # kernel choices inside a graph must not depend on lengths
+        if key[1] != "decode":                  # nor on how the tokens are divided, nor on how many rows are wanted
+            batch.any_division = True
+            if key[1] == "any":
+                batch.num_want = batch.want_cap
+                batch.want_rows = self.buffers.last.dev_view("want_rows", batch.want_cap)
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
@@ -209,9 +233,10 @@ class ModelRunner:
             logits = self.model.forward(batch, self.cache)
         kernels = ops.launch_count - before     # counted while capturing, not run
         ops.launch_count = before
-        batch.max_kv_len = real_max_kv
-        self._graphs[(B, batch.layout)] = (graph, logits, kernels)
-        return self._graphs[(B, batch.layout)]
+        batch.max_kv_len, batch.num_want, batch.want_rows, batch.any_division = real
+        self._graphs[key] = (graph, logits, kernels)
+        self._mixed_count += key[1] != "decode"
+        return self._graphs[key]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens as one batch; returns float32 [wanted, vocab] in the order of

@@ -19,7 +19,11 @@ from .registry import lookup, register_mixer
 class AttentionWork(StepPrelude):
     """How the attention kernels cut a step: rows of entries that bring one token go to the
     split-key decode kernel, longer portions are cut into tiles of `ops.PREFILL_TILE_ROWS` query
-    rows (entry, first row inside it) for the tensor-core prompt kernel, longest walk first."""
+    rows (entry, first row inside it) for the tensor-core prompt kernel, longest walk first.
+    Both lists are padded with -1 up to what a step of as many tokens could need at most, so that
+    a launch over the whole padded list does the same work (a kernel's block that meets -1 returns
+    at once): that is how a captured graph of a step of T tokens serves every later step of T
+    tokens, however they are divided among requests."""
     name = "attention_work"
 
     @dataclass
@@ -28,16 +32,27 @@ class AttentionWork(StepPrelude):
         prefill_tiles: torch.Tensor      # int32 [num_prefill_tiles, 2]
         num_decode: int
         num_prefill_tiles: int
+        padded_rows: torch.Tensor        # the same lists over their padding: [rows_cap], [tiles_cap, 2]
+        padded_tiles: torch.Tensor
 
     def sections(self, max_tokens: int, max_entries: int):
+        self.max_entries = max_entries
         return {"decode_rows": max_tokens,
                 "prefill_tiles": 2 * (max_tokens // ops.PREFILL_TILE_ROWS + max_entries + 1)}
+
+    def caps(self, num_tokens: int):
+        """The most rows and tiles a step of `num_tokens` tokens can have."""
+        return (min(num_tokens, self.max_entries),
+                num_tokens // ops.PREFILL_TILE_ROWS + min(num_tokens // 2, self.max_entries) + 1)
 
     def fill(self, facts, out):
         R = ops.PREFILL_TILE_ROWS
         single = facts.q_len == 1
         n_dec = int(single.sum())
+        rows_cap, tiles_cap = self.caps(facts.num_tokens)
+        tiles_cap = min(tiles_cap, len(out["prefill_tiles"]) // 2)
         out["decode_rows"][:n_dec] = facts.q_start[single]
+        out["decode_rows"][n_dec:rows_cap] = -1
         n_tiles = 0
         if n_dec < len(facts.q_len):
             tiles = [(i, q0) for i in np.nonzero(~single)[0] for q0 in range(0, int(facts.q_len[i]), R)]
@@ -45,12 +60,14 @@ class AttentionWork(StepPrelude):
             tiles.sort(key=lambda t: -(int(facts.past[t[0]]) + t[1]))
             n_tiles = len(tiles)
             out["prefill_tiles"][:2 * n_tiles] = np.asarray(tiles, dtype=np.int64).reshape(-1)
-        return n_dec, n_tiles
+        out["prefill_tiles"][2 * n_tiles:2 * tiles_cap] = -1
+        return n_dec, n_tiles, rows_cap, tiles_cap
 
     def views(self, dev, filled):
-        n_dec, n_tiles = filled
+        n_dec, n_tiles, rows_cap, tiles_cap = filled
         return AttentionWork.Views(dev["decode_rows"][:n_dec], dev["prefill_tiles"][:2 * n_tiles].view(n_tiles, 2),
-                                   n_dec, n_tiles)
+                                   n_dec, n_tiles, dev["decode_rows"][:rows_cap],
+                                   dev["prefill_tiles"][:2 * tiles_cap].view(tiles_cap, 2))
 
 
 @register_mixer("attention")
@@ -179,19 +196,25 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
     if (work is not None and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
             and ops.fast_attention_supported(d, nq // nkv)):
         out = torch.empty_like(q)
-        if work.num_decode:
+        # A step that is being captured as a graph of "any step of this many tokens" launches both
+        # kernels over the padded lists; otherwise over what this step has.
+        padded = getattr(b, "any_division", False)
+        n_dec = work.padded_rows.shape[0] if padded else work.num_decode
+        n_tiles = work.padded_tiles.shape[0] if padded else work.num_prefill_tiles
+        if n_dec:
             # Key splits: as many as keep the whole grid resident at once (two CTAs per SM), since
             # a second, partial wave costs more than it balances; at least 256 keys per split.
-            splits = max(1, min(16, _cta_slots(q.device) // (work.num_decode * nkv), b.max_kv_len // 256))
-            ops.paged_attention_decode(q, out, cache, None if work.num_decode == b.num_tokens else work.decode_rows,
-                                       work.num_decode, b.positions, b.token_entry, b.entry_slot, ctx.block_table,
-                                       nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
-        if work.num_prefill_tiles:
+            splits = max(1, min(16, _cta_slots(q.device) // (n_dec * nkv), b.max_kv_len // 256))
+            rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
+            ops.paged_attention_decode(q, out, cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
+                                       ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)
+        if n_tiles:
             kernel = (ops.paged_attention_prefill_tcgen05
                       if ops.prefill_tcgen05_supported(d, ctx.page_size)
                       else ops.paged_attention_prefill)       # tcgen05/TMEM/TMA where it applies, mma.sync otherwise
-            kernel(q, out, cache, work.prefill_tiles, work.num_prefill_tiles, b.entry_slot, b.entry_q_start,
-                   b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)
+            kernel(q, out, cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
+                   b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, nq, nkv, d, ctx.page_size, window,
+                   scale, ctx.status)
         return out
     return ops.paged_attention_generic(q, cache, b.positions, b.token_entry, b.entry_slot,
                                        ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, ctx.status)

@@ -112,17 +112,18 @@ class Model:
     def forward(self, batch, cache) -> torch.Tensor:
         """batch: StepBatch already on the device; cache: CacheManager.  Returns float32
         [batch.num_want, vocab] (an empty tensor when nothing is wanted)."""
-        h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
-        delta = None
-        for s, st in enumerate(self.plan.order):
-            block = self.blocks[st.block]
-            h, delta = block.forward(h, delta, self.stage_context(s, batch, cache))
-        if batch.num_want == 0:
-            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
-        if not getattr(self.final_norm, "accepts_partials", False):
-            delta = ops.as_tensor(delta)
-        hn = self.final_norm.forward(h, self.dtype, delta=delta, rows=batch.want_rows)
-        return ops.linear(hn, self.output, out_dtype=torch.float32)
+        with ops.bound_stream():                       # one stream for the whole pass, looked up once
+            h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
+            delta = None
+            for s, st in enumerate(self.plan.order):
+                block = self.blocks[st.block]
+                h, delta = block.forward(h, delta, self.stage_context(s, batch, cache))
+            if batch.num_want == 0:
+                return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+            if not getattr(self.final_norm, "accepts_partials", False):
+                delta = ops.as_tensor(delta)
+            hn = self.final_norm.forward(h, self.dtype, delta=delta, rows=batch.want_rows)
+            return ops.linear(hn, self.output, out_dtype=torch.float32)
 
     def stage_context(self, s: int, batch, cache) -> StageContext:
         st = self.plan.order[s]

@@ -229,3 +229,44 @@ def test_prompt_portions_through_the_paired_product(policy, monkeypatch):
     if policy == "all":
         assert any("gemm_pair_tcgen05" in name for name in ops.loaded_libraries())
 
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_one_size_divided_differently_replay_one_graph(dtype):
+    """A step that is not all single decoded tokens is captured, the second time its number of tokens is
+    seen, as a graph for ANY step of that many tokens: the attention kernels run over work lists padded
+    with entries that mean "nothing".  Steps of 24 tokens divided among one to four requests in seven
+    different ways (a whole portion; portions beside decoded tokens; decoded tokens that want nothing),
+    each wanting at most one row per request: same logits as the plain code, and as with graphs off."""
+    from litellmengine_b200.engine import StepEntry
+    cfg, page, w, _ = setup("E", dtype)
+    reqs = rh.requests_for(cfg, [200, 170, 150, 90], 77)
+    ref = rh.plain_rows(cfg, w, reqs, dtype)
+    names = list(reqs)
+    cuts = [[24], [20, 4], [1, 23], [12, 1, 11], [1, 1, 22], [6, 6, 6, 6], [1, 1, 1, 21], [24], [2, 22], [13, 11]]
+    results = {}
+    for graphs in (True, False):
+        runner = rh.make_runner(cfg, w, dtype, page, max_total_tokens=1024, max_requests=4, max_tokens_per_step=64)
+        runner.use_graphs = runner.use_graphs and graphs
+        slots = {r: runner.admit() for r in names}
+        at = {r: 0 for r in names}
+        got = {}
+        for step, cut in enumerate(cuts):
+            order = names[step % 4:] + names[:step % 4]               # who gets which share changes too
+            entries, wanted = [], []
+            for r, n in zip(order, cut):
+                want = [n - 1] if (step + n) % 3 else []                # some entries want nothing
+                entries.append(StepEntry(slots[r], reqs[r][at[r]:at[r] + n], want))
+                if want:
+                    wanted.append((r, at[r] + n - 1))
+                at[r] += n
+            logits = runner.step(entries).float().cpu().numpy()
+            assert logits.shape[0] == len(wanted)
+            for (r, pos), row in zip(wanted, logits):
+                got[(r, pos)] = row
+        runner.check_status()
+        kinds = {k[1] for k in runner._graphs}
+        assert (("any" in kinds) and runner.graph_replays >= 6) if graphs else runner.graph_replays == 0
+        rh.assert_rows_match(got, ref, rh.tol_for(dtype), f"24-token steps, graphs {graphs}")
+        results[graphs] = got
+    assert results[True].keys() == results[False].keys()
