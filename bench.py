@@ -159,6 +159,20 @@ def reference_arm(args) -> int:
     except Exception as e:                      # ReferenceUnavailable, a missing compiler, a time-out
         print(json.dumps({"impl": "reference", "unavailable": " ".join(str(e).split())[:400]}))
         return 0
+    points = {}
+    if not args.no_points and "0p6b" in args.points.split(","):
+        # the workload the reference publishes a figure for (readme.md:66: 32 requests, 64 new tokens each,
+        # paged batch decode), with the prompts of the 0.6B benchmark configuration: the whole job timed,
+        # prefill and engine construction included, as its own benchmark does
+        try:
+            j = ra.run(QWEN3_0P6B, batch=32, context=512 + 64, steps=0, warmup=1, page_size=PAGE, seed=3,
+                       job={"prompt_min": 64, "prompt_max": 512, "new_tokens": 64})
+            points["qwen3_0p6b_mixed"] = {"tok_s": round(j["tokens"] / j["wall_s"], 2), "new_tokens": j["tokens"],
+                                          "seconds": round(j["wall_s"], 3), "dtype": "fp32",
+                                          "config": shape_config(QWEN3_0P6B, QWEN3_0P6B["num_hidden_layers"], 32, 576,
+                                                                 prompt_min=64, prompt_max=512, new_tokens=64)}
+        except Exception as e:
+            points["qwen3_0p6b_mixed"] = {"unavailable": " ".join(str(e).split())[:300]}
     ms = r["device_ms"] / r["steps"]
     out = {
         "impl": "reference",
@@ -173,7 +187,7 @@ def reference_arm(args) -> int:
                 "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
         "prefill": {"value": round(args.batch * r["longest_prompt"] / r["prefill_s"], 1),
                     "tokens": r["longest_prompt"], "ms": round(r["prefill_s"] * 1e3 / args.batch, 1)},
-        "clocks": ck,
+        "points": points, "clocks": ck,
     }
     print(json.dumps(out))
     return 0
@@ -363,6 +377,9 @@ class Bench:
                 points[f"decode_b{b}_frac"] = round(r["frac"], 4)
                 points[f"decode_b{b}_check"] = {"ok": c["rms"] <= allowed, "rms_err": float("%.3g" % c["rms"]),
                                                 "allowed_rms": float("%.3g" % allowed)}
+            # end to end at batch 64 too (beside `decode_b64`: the host's share of a step grows with the batch)
+            n64 = max(8, min(args.steps, 32)) + 3 + 64
+            points["e2e_b64"] = round(self.e2e_decode(runner, 64, CONTEXT - n64, n64 + 8, max(8, min(args.steps, 32)), 3), 1)
         if "generate" in want_points:
             # the workload the baseline states: 2,048-token prompts, then 256 new tokens, end to end
             for b in (1, 8, 64):

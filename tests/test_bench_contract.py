@@ -26,7 +26,7 @@ def test_more_than_one_gpu_is_one_line_and_exit_code_2():
 def test_the_reference_arm_without_a_gpu_is_one_line_with_the_reason():
     """Here the reference's engine cannot run (it needs a CUDA device, or its sources are not at
     hand): the arm still exits 0 with one JSON line."""
-    r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3", "--layers", "1")
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3", "--layers", "1", "--no-points")
     assert r.returncode == 0
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     d = json.loads(lines[-1])
@@ -41,7 +41,7 @@ def test_the_reference_arm_without_a_gpu_is_one_line_with_the_reason():
 def test_the_reference_arm_times_the_reference_engine():
     """One layer of the benchmark's shape through the unmodified reference: the line has the
     contract's keys, float32 as its dtype, and an end-to-end figure of its own."""
-    r = run("--impl", "reference", "--gpus", "1", "--steps", "3", "--warmup", "3", "--layers", "1")
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "3", "--warmup", "3", "--layers", "1", "--no-points")
     assert r.returncode == 0, r.stderr[-400:]
     d = json.loads(r.stdout.strip().splitlines()[-1])
     assert d["impl"] == "reference"
