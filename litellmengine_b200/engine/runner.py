@@ -76,6 +76,13 @@ class ModelRunner:
             for b in model.blocks)
         self._graphs = {}
         self._mixed_graphs = True               # graphs for steps that are not all single decoded tokens
+        # Parts that say `any_division_safe` read the step's per-entry arrays only through kernels that
+        # take their work from a prelude's padded lists: one graph then serves every step of T tokens.
+        # Parts that are only `graph_safe` may shape tensors by the number of entries, so their graphs
+        # are kept per (tokens, entries).
+        self._entries_free = all(
+            getattr(b.mixer, "any_division_safe", False) and getattr(b.feed_forward, "any_division_safe", False)
+            for b in model.blocks)
         self._mixed_count = 0
         self._graph_seen = {}
         self._graph_pool = None
@@ -177,7 +184,8 @@ class ModelRunner:
         where one graph can serve them: a step of B single decoded tokens that wants all B logits
         (one graph per B), and any other step of T tokens that wants at most one row per entry slot
         (one graph per T: its attention kernels run over padded work lists, so it does not matter how
-        the T tokens are divided among requests).  A graph is captured the second time its key is
+        the T tokens are divided among requests; per (T, entries) for models with a part that does
+        not say `any_division_safe`).  A graph is captured the second time its key is
         seen; everything else launches the kernels one by one.  A graph's logits tensor is reused by
         the next replay of that graph: read it (sample, copy) before stepping again."""
         if self.use_graphs:
@@ -187,10 +195,10 @@ class ModelRunner:
                 self._mixed_count = 0
                 self._graph_weights = ops.streaming_generation()
             if batch.max_q_len == 1 and batch.num_want == B:
-                key = (B, "decode", batch.layout)                 # a graph holds the device addresses of one layout
+                key = (B, "decode", batch.layout, B)              # a graph holds the device addresses of one layout
             elif self._mixed_graphs and batch.num_want <= batch.want_cap and B <= self.MIXED_GRAPH_MAX_TOKENS:
                 # "none": a prompt portion that wants nothing has no output head in its graph
-                key = (B, "any" if batch.num_want else "none", batch.layout)
+                key = (B, "any" if batch.num_want else "none", batch.layout, 0 if self._entries_free else batch.num_entries)
                 if key not in self._graphs and self._mixed_count >= self.MIXED_GRAPH_MAX_COUNT:
                     key = None
             else:
@@ -220,8 +228,14 @@ class ModelRunner:
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
+        # The warm-up below runs the step for real and the first replay runs it again.  Keys and values
+        # land in the same places with the same values both times; a mixer's fixed-size state would be
+        # advanced twice, so it is put back in between.
+        states = {k: t.clone() for k, t in self.cache.state.items() if isinstance(k, int)}
         with torch.cuda.stream(side):           # warm every kernel and library handle outside capture
             self.model.forward(batch, self.cache)
+            for k, t in states.items():
+                self.cache.state[k].copy_(t)
         cur.wait_stream(side)
         torch.cuda.synchronize()
         batch.tables.clear()                    # what the warm-up computed once for its layers: the graph must compute its own

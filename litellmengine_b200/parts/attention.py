@@ -79,6 +79,7 @@ class AttentionMixer:
     (src/ops/attention.cu:204-207)."""
 
     graph_safe = True          # forward only launches kernels on the current stream
+    any_division_safe = True   # and nothing in it is shaped by the number of entries of the step
 
     def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:

@@ -17,6 +17,7 @@ class SwiGLU:
     src/ops/silu_and_mul.cu:44-46).  Gate and up are one fused product [g | u]."""
 
     graph_safe = True          # forward only launches kernels on the current stream
+    any_division_safe = True   # and nothing in it is shaped by the number of entries of the step
 
     def __init__(self, spec: FeedForwardSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.intermediate_size <= 0:

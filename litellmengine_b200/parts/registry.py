@@ -33,8 +33,11 @@ may then be one), a feed-forward with `supports_partials = True` (it is then cal
 `partials_ok=True`), a mixer through `ctx.partials_ok`.  Parts that say nothing never see one.
 
 A mixer or feed-forward whose forward only launches kernels on the current stream (no host
-reads, no loops over host data) may set the class attribute `graph_safe = True`; decode steps
-of a model whose parts all do are replayed as CUDA graphs.
+reads, no loops over host data) may set the class attribute `graph_safe = True`; steps of a
+model whose parts all do are replayed as CUDA graphs, one per (tokens, entries) of a step.  A
+part in which nothing is shaped by the number of entries either (it reads the per-entry arrays
+only inside kernels, and takes its work lists from a prelude that pads them) may also set
+`any_division_safe = True`: one graph then serves every step of as many tokens.
 """
 from __future__ import annotations
 

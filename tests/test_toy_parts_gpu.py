@@ -1,5 +1,5 @@
 """The framework's generality, shown with toy parts that exist only in this file: a mixer with
-a state of its own (no pages), a windowed attention layer (a cache group that gives pages
+a state of its own (no pages; updated by tensor operations alone, so its steps are replayed as graphs), a windowed attention layer (a cache group that gives pages
 back), a layer that runs twice, a layer that reads another stage's cache, a feed-forward that
 routes tokens to experts, and a position encoding with a frequency table of its own.  They are
 registered, built and stepped here without a change to the framework's files, in every way of
@@ -45,20 +45,21 @@ def register_toys():
         def cache_need(self):
             return StateNeed((self.hidden + 1,), "float32")
 
+        graph_safe = True          # tensor operations on the current stream only: no host reads, no loops over entries
+
         def forward(self, x, ctx):
-            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
-            row = 0
-            for e in ctx.batch.entries:
-                n = len(e.tokens)
-                st = ctx.state[e.slot]
-                assert int(st[-1].item()) == e.past, "the slot's state does not belong to this request"
-                sums = st[:-1] + torch.cumsum(x[row:row + n].float(), dim=0)
-                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
-                out[row:row + n] = (sums / counts[:, None]) @ self.w.T
-                st[:-1] = sums[-1]
-                st[-1] = counts[-1]
-                row += n
-            return out
+            b = ctx.batch
+            T = x.shape[0]
+            ent = b.token_entry.long()
+            slot = b.entry_slot.long()[ent]                              # [T] the slot of each token's request
+            start = b.entry_q_start.long()[ent]                          # [T] first row of the token's entry
+            cs = torch.cumsum(x.double(), dim=0)                         # in double: the difference below must not cancel
+            before = torch.where((start > 0)[:, None], cs[(start - 1).clamp(min=0)], torch.zeros_like(cs))
+            sums = ctx.state[slot, :-1] + (cs - before).float()          # running sum inside the entry, on top of the slot's
+            counts = ctx.state[slot, -1] + (torch.arange(T, device=x.device) - start + 1).float()
+            last = b.entry_q_start.long() + b.entry_q_len.long() - 1     # each entry's last row carries the new state
+            ctx.state[b.entry_slot.long()] = torch.cat([sums[last], counts[last][:, None]], dim=1)
+            return (sums / counts[:, None]) @ self.w.T
 
     @register_architecture("ToyPartsForCausalLM")
     @dataclass(frozen=True)
@@ -163,8 +164,11 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype, tmp_path):
             groups = runner.cache.groups
             assert sorted((str(g.need.window), len(g.stages)) for g in groups) == [("6", 2), ("None", 1)]
             assert set(runner.cache.stage_state) == {1, 5} and runner.cache.stage_group[4] == runner.cache.stage_group[2]
+            assert runner.use_graphs                                   # every part of the toy model launches kernels only
             got = rh.run_trace(runner, steps)
             rh.assert_rows_match(got, ref, rh.tol_for(dtype), f"toy {dtype} {what}")
+            if what in ("tail", "mixed"):                              # steps of one size recur: they were replayed as graphs,
+                assert runner.graph_replays > 0                        # the mixer's state advancing once per step all the same
         # the windowed group really gave pages back while a request was still running
         runner = ModelRunner.from_config(Toy(), dtype=dtype, device=DEV, page_size=4, max_requests=2,
                                          max_tokens_per_step=128, max_total_tokens=128,
