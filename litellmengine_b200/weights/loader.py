@@ -118,11 +118,50 @@ def _name_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
+_MASK32 = (1 << 32) - 1
+_M1, _M2 = 0x7FEB352D, 0x846CA68B          # multipliers of a 32-bit integer finaliser ("lowbias32")
+
+
+def _mix32(x: torch.Tensor) -> torch.Tensor:
+    """A 32-bit avalanche hash on int64 tensors that hold values below 2^32: shifts, xors and
+    products that stay below 2^63, so the host and the GPU compute the same integers."""
+    x = x ^ (x >> 16)
+    x = (x * _M1) & _MASK32
+    x = x ^ (x >> 15)
+    x = (x * _M2) & _MASK32
+    return x ^ (x >> 16)
+
+
+def seeded_normal(shape, key: int, std: float, mean: float, device, chunk: int = 1 << 24) -> torch.Tensor:
+    """float32 tensor of `shape` whose element i is mean + std * z_i, z_i a function of (key, i) alone:
+    the sum of eight 16-bit integers hashed from (key, i), centred and scaled to unit variance (an
+    Irwin-Hall approximation of the normal distribution; |z| < 4.9).  Only integer arithmetic, one
+    integer-to-float conversion and two float32 products are involved, so every device gives the same
+    bits."""
+    n = 1
+    for d in shape:
+        n *= int(d)
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    k_lo, k_hi = key & _MASK32, (key >> 32) & _MASK32
+    scale = (12.0 / (8.0 * (65536.0 ** 2 - 1.0))) ** 0.5
+    for at in range(0, n, chunk):
+        i = torch.arange(at, min(at + chunk, n), dtype=torch.int64, device=device)
+        lo, hi = i & _MASK32, i >> 32
+        total = torch.zeros_like(i)
+        for word in range(4):                                    # four 32-bit hashes = eight 16-bit integers
+            h = _mix32(_mix32(lo ^ k_lo ^ (word * 0x9E3779B9 & _MASK32)) ^ hi ^ k_hi)
+            total += (h & 0xFFFF) + (h >> 16)
+        z = (total - 262140).to(torch.float32) * scale            # 262140 = 8 * 65535 / 2
+        out[at:at + z.numel()] = z * std + mean
+    return out.view(tuple(shape))
+
+
 class RandomSource(WeightSource):
     """Seeded random tensors for a set of `ParamSpec`s: matrices N(0, std), norm
-    weights 1 + N(0, std).  Each tensor's stream is keyed by (seed, tensor name), so
-    a tensor's values do not depend on which other tensors exist.  Values are drawn
-    in float32 on `device` and then rounded to `dtype`; CPU and GPU draws differ.
+    weights 1 + N(0, std).  Each tensor's values are a function of (seed, tensor name, element
+    index), so they do not depend on which other tensors exist, and not on `device` either: drawn
+    on the host or on the GPU, the same seed gives the same model, bit for bit (`seeded_normal`).
+    Values are drawn in float32 and then rounded to `dtype`.
     Tensors that have an `optional_alias` (a tied output head) are left out.
     """
 
@@ -139,17 +178,12 @@ class RandomSource(WeightSource):
 
     def get(self, name):
         p = self._p[name]
-        g = torch.Generator(device=self.device)
-        g.manual_seed(_name_seed(self.seed, name))
         if p.role == "index":
             raise ValueError(f"{name}: no random rule for integer tables")
         kind, std = p.init
-        t = torch.empty(p.shape, dtype=torch.float32, device=self.device)
-        t.normal_(0.0, std, generator=g)
-        if kind == "one_plus_normal":
-            t += 1.0
-        elif kind != "normal":
+        if kind not in ("normal", "one_plus_normal"):
             raise ValueError(f"{name}: unknown init {kind!r}")
+        t = seeded_normal(p.shape, _name_seed(self.seed, name), std, 1.0 if kind == "one_plus_normal" else 0.0, self.device)
         return t.to(self.dtype)
 
 

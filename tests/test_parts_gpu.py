@@ -141,3 +141,19 @@ def test_whole_block_alone(dtype):
     act = pq.to_bf16 if bf else pq.identity
     ref = pq.decoder_layer(h + pending, torch.arange(T, dtype=torch.int32), allw, 1, cfg, act=act)
     close(hg + delta.float(), ref, TOL[dtype])
+
+
+def test_random_weights_do_not_depend_on_where_they_are_drawn():
+    """The random-weights mode draws a tensor as a function of (seed, name, element): on the host and on
+    the GPU the same bits, in float32 and after rounding to bfloat16, for shapes past one chunk of the
+    generator too."""
+    from litellmengine_b200.weights import ParamSpec, RandomSource
+    from litellmengine_b200.weights.loader import seeded_normal
+    params = {"a.weight": ParamSpec((300, 129)), "n.weight": ParamSpec((77,), role="scale", init=("one_plus_normal", 0.01))}
+    for dtype in (torch.float32, torch.bfloat16):
+        host, dev = RandomSource(params, 9, dtype, "cpu"), RandomSource(params, 9, dtype, DEV)
+        for name in params:
+            assert torch.equal(host.get(name), dev.get(name).cpu()), name
+    a = seeded_normal((5000, 700), 123456789, 0.02, 0.0, "cpu", chunk=1 << 20)
+    b = seeded_normal((5000, 700), 123456789, 0.02, 0.0, DEV)
+    assert torch.equal(a, b.cpu()) and abs(float(a.std()) - 0.02) < 2e-4 and abs(float(a.mean())) < 1e-4
