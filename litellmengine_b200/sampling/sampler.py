@@ -21,6 +21,8 @@ from ..csrc import ops
 
 
 def slot_state_row(seed: int, counter: int, temperature: float) -> List[int]:
+    """The four int32 of a request's stream, written into its slot by the step that admits it
+    (counter = tokens it has sampled so far, so a recomputed request continues its own stream)."""
     seed &= 0xFFFFFFFFFFFFFFFF
     lo, hi = seed & 0xFFFFFFFF, seed >> 32
     tbits = struct.unpack("<i", struct.pack("<f", float(temperature)))[0]
@@ -31,12 +33,6 @@ def slot_state_row(seed: int, counter: int, temperature: float) -> List[int]:
 class Sampler:
     def __init__(self, sampler_state: torch.Tensor):
         self.state = sampler_state            # int32 [slots, 4] inside the cache manager's state slots
-
-    def admit(self, slot: int, seed: int, counter: int, temperature: float) -> None:
-        """Write a request's stream into its slot (counter = tokens it has sampled so far, so a
-        recomputed request continues its own stream)."""
-        row = torch.tensor(slot_state_row(seed, counter, temperature), dtype=torch.int32)
-        self.state[slot].copy_(row, non_blocking=False)
 
     def sample(self, logits: torch.Tensor, want_slot: torch.Tensor, any_sampling: bool,
                out: torch.Tensor = None) -> torch.Tensor:
