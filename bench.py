@@ -45,10 +45,11 @@ QWEN3_0P6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attentio
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
                  intermediate_size=25600)
 CONTEXT = 4096
+LONG_CONTEXT = 32768                 # the further context length of the "long" points (Qwen3-8B allows 40,960)
 PAGE = 16
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-ALL_POINTS = ("decode", "generate", "fp32", "0p6b", "32b")
+ALL_POINTS = ("decode", "generate", "long", "fp32", "0p6b", "32b")
 # The check before the line is printed: decode steps against whole prompts, same model, same positions.
 # Two bfloat16 ways of computing one position are two roundings of the same exact value; their
 # difference grows with depth like a random walk.  Measured on this shape against the float32 path
@@ -386,6 +387,45 @@ class Bench:
                 points[f"generate_p2048_n256_b{b}"] = round(self.e2e_decode(runner, b, 2048, 256 + b, 200, 8), 1)
         return out
 
+    # ---- the same shape at a context of 32,768 ----------------------------------------------------------
+    def qwen3_8b_long(self, points):
+        """One 32,768-token prompt in one step (the attention's share of the work grows with the length),
+        then decode steps at batch 8 and batch 1 that end at that context: a step reads 39 GB of keys
+        and values beside the weights, so the attention kernel is most of it."""
+        args, pk, torch = self.args, self.pk, self.torch
+        C = LONG_CONTEXT
+        try:
+            runner = self.build(QWEN3_8B, args.layers, "bfloat16", 8, C, seed=2)
+            s = runner.admit()
+            runner.step([self.Entry(s, self.tokens(C), [C - 1])])
+            runner.release(s)
+            torch.cuda.synchronize()
+            a, b = self.ev(), self.ev()
+            a.record()
+            s = runner.admit()
+            runner.step([self.Entry(s, self.tokens(C), [C - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.release(s)
+            pms = a.elapsed_time(b)
+            flops = self.prefill_flops(runner.config, args.layers, C)
+            rec = {"context": C, "prefill_tok_s": round(C / (pms * 1e-3), 1), "prefill_ms": round(pms, 1),
+                   "prefill_frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                   "prefill_peak": "sustained"}
+            for bsz in (8, 1):
+                r = self.decode_device_timed(runner, bsz, 16, 4, context=C, keep=True)
+                c = self.check_last_step(runner, r)
+                allowed = CHECK_RMS_PER_SQRT_LAYER * args.layers ** 0.5 * c["scale"]
+                rec[f"decode_b{bsz}"] = round(r["tok_s"], 1)
+                rec[f"decode_b{bsz}_ms"] = round(r["ms"], 3)
+                rec[f"decode_b{bsz}_frac"] = round(r["frac"], 4)
+                rec[f"decode_b{bsz}_check"] = {"ok": c["rms"] <= allowed, "rms_err": float("%.3g" % c["rms"]),
+                                               "allowed_rms": float("%.3g" % allowed)}
+            rec["ok"] = all(rec[f"decode_b{bsz}_check"]["ok"] for bsz in (8, 1))
+            points["context_32768"] = rec
+        except torch.cuda.OutOfMemoryError as e:
+            points["context_32768"] = {"skipped": "out of device memory: " + str(e)[:80]}
+
     # ---- the same shape in true float32 -------------------------------------------------------------
     def qwen3_8b_fp32(self, points):
         args = self.args
@@ -508,7 +548,7 @@ def main() -> int:
                           "max_error": check["max"], "largest_logit": check["scale"]}))
         return 1
     bench.free_memory()
-    for name, fn in (("fp32", bench.qwen3_8b_fp32), ("0p6b", bench.qwen3_0p6b), ("32b", bench.qwen3_32b)):
+    for name, fn in (("long", bench.qwen3_8b_long), ("fp32", bench.qwen3_8b_fp32), ("0p6b", bench.qwen3_0p6b), ("32b", bench.qwen3_32b)):
         if name in want_points:
             fn(points)
             bench.free_memory()

@@ -194,11 +194,15 @@ class ModelRunner:
                 self._graphs.clear()
                 self._mixed_count = 0
                 self._graph_weights = ops.streaming_generation()
+            # The last member of a key: what the parts' launches depend on beyond the token count (the
+            # decode attention's key splits grow with the longest cached length, in steps).
             if batch.max_q_len == 1 and batch.num_want == B:
-                key = (B, "decode", batch.layout, B)              # a graph holds the device addresses of one layout
+                # a graph holds the device addresses of one layout
+                key = (B, "decode", batch.layout, B, self.model.graph_variant(batch, False))
             elif self._mixed_graphs and batch.num_want <= batch.want_cap and B <= self.MIXED_GRAPH_MAX_TOKENS:
                 # "none": a prompt portion that wants nothing has no output head in its graph
-                key = (B, "any" if batch.num_want else "none", batch.layout, 0 if self._entries_free else batch.num_entries)
+                key = (B, "any" if batch.num_want else "none", batch.layout, 0 if self._entries_free else batch.num_entries,
+                       self.model.graph_variant(batch, True))
                 if key not in self._graphs and self._mixed_count >= self.MIXED_GRAPH_MAX_COUNT:
                     key = None
             else:
@@ -218,9 +222,11 @@ class ModelRunner:
         return self.model.forward(batch, self.cache)
 
     def _capture(self, batch: StepBatch, key):
-        real = (batch.max_kv_len, batch.num_want, batch.want_rows, batch.any_division)
-        batch.max_kv_len = 1 << 30              # kernel choices inside a graph must not depend on lengths
-        if key[1] != "decode":                  # nor on how the tokens are divided, nor on how many rows are wanted
+        # Launch choices inside a graph may depend on the step's lengths only as far as the parts'
+        # `graph_variant` says (it is part of the key), not on how the tokens are divided, nor on how
+        # many rows are wanted.
+        real = (batch.num_want, batch.want_rows, batch.any_division)
+        if key[1] != "decode":
             batch.any_division = True
             if key[1] == "any":
                 batch.num_want = batch.want_cap
@@ -247,7 +253,7 @@ class ModelRunner:
             logits = self.model.forward(batch, self.cache)
         kernels = ops.launch_count - before     # counted while capturing, not run
         ops.launch_count = before
-        batch.max_kv_len, batch.num_want, batch.want_rows, batch.any_division = real
+        batch.num_want, batch.want_rows, batch.any_division = real
         self._graphs[key] = (graph, logits, kernels)
         self._mixed_count += key[1] != "decode"
         return self._graphs[key]

@@ -93,6 +93,7 @@ class AttentionMixer:
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.d))
         self.dtype = compute_dtype
+        self.device = torch.device(device)
         self.position = lookup("position", spec.position.kind)(spec.position, self.d, device)
         self.q_norm = self.k_norm = None
         if spec.qk_norm is not None:
@@ -137,6 +138,18 @@ class AttentionMixer:
 
     def step_prelude(self):
         return AttentionWork()
+
+    @property
+    def graph_variant_group(self):
+        return ("attention", self.nkv)
+
+    def graph_variant(self, batch, padded: bool) -> int:
+        """The decode kernel's key splits: the one launch choice here that depends on lengths."""
+        work = batch.preludes.get(AttentionWork.name)
+        if work is None:
+            return 0
+        n_dec = work.padded_rows.shape[0] if padded else work.num_decode
+        return decode_key_splits(self.device, n_dec, self.nkv, batch.max_kv_len) if n_dec else 0
 
     def forward(self, x: torch.Tensor, ctx: StageContext) -> torch.Tensor:
         b = ctx.batch
@@ -184,6 +197,19 @@ def _cta_slots(device) -> int:
     return n
 
 
+# Key splits of the decode kernel by the longest cached length, in steps: a captured graph holds its
+# number of splits, so steps whose lengths give the same number share a graph.
+_SPLIT_STEPS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64)
+
+
+def decode_key_splits(device, n_dec: int, nkv: int, max_kv_len: int) -> int:
+    """As many splits as keep the whole grid resident at once (two CTAs per SM: a second, partial
+    wave costs more than it balances), about 256 keys or more to a split."""
+    by_length = max(1, -(-max_kv_len // 256))
+    step = max(s for s in _SPLIT_STEPS if s <= by_length)
+    return max(1, min(step, _cta_slots(device) // max(1, n_dec * nkv)))
+
+
 def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,
                          window: Optional[int], scale: float) -> torch.Tensor:
     """Pick the attention kernels for this batch.  Every choice reads the same pages and gives
@@ -203,9 +229,7 @@ def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, 
         n_dec = work.padded_rows.shape[0] if padded else work.num_decode
         n_tiles = work.padded_tiles.shape[0] if padded else work.num_prefill_tiles
         if n_dec:
-            # Key splits: as many as keep the whole grid resident at once (two CTAs per SM), since
-            # a second, partial wave costs more than it balances; at least 256 keys per split.
-            splits = max(1, min(16, _cta_slots(q.device) // (n_dec * nkv), b.max_kv_len // 256))
+            splits = decode_key_splits(q.device, n_dec, nkv, b.max_kv_len)
             rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
             ops.paged_attention_decode(q, out, cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
                                        ctx.block_table, nq, nkv, d, ctx.page_size, window, scale, splits, ctx.status)

@@ -90,6 +90,23 @@ class Model:
                     out.append(make())
         return out
 
+    def graph_variant(self, batch, padded: bool) -> tuple:
+        """What the parts' kernel choices for this step depend on beyond the number of tokens: a part
+        whose launches vary with the step's lengths says so through an optional
+        `graph_variant(batch, padded)` (any hashable; `padded`: the step would be captured over its
+        preludes' padded lists).  Steps with equal variants can replay one captured graph.  Parts that
+        give the same `graph_variant_group` choose alike and are asked once."""
+        out, seen = [], set()
+        for b in self.blocks:
+            for part in (b.mixer, b.feed_forward):
+                ask = getattr(part, "graph_variant", None)
+                group = getattr(part, "graph_variant_group", None)
+                if ask is None or (group is not None and group in seen):
+                    continue
+                seen.add(group)
+                out.append(ask(batch, padded))
+        return tuple(out)
+
     def weight_bytes(self) -> int:
         """Bytes of every weight tensor one decode step reads (a tied head counts twice: the
         embedding rows read are negligible, the head is read whole)."""

@@ -170,8 +170,9 @@ def test_a_status_code_in_either_word_is_raised_and_cleared():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_replayed_as_graphs_match_kernel_by_kernel_launches(dtype):
     """Steps made only of single decoded tokens are replayed as CUDA graphs from the third step of
-    a batch size on.  Same trace with graphs off: same logits up to rounding (a graph fixes the
-    number of key splits once, the plain launches choose it per step)."""
+    a batch size on.  Same trace with graphs off: same logits up to rounding (the graph of a mixed
+    step chooses its key splits for the most single tokens such a step could hold, the plain
+    launches for those it has)."""
     cfg, page, w, _ = setup("D", dtype)
     reqs = rh.requests_for(cfg, [90, 41, 140], 5)
     ref = rh.plain_rows(cfg, w, reqs, dtype)
@@ -191,6 +192,30 @@ def test_decode_steps_replayed_as_graphs_match_kernel_by_kernel_launches(dtype):
         assert (runner.graph_replays > 20) == graphs
     worst = max(float(np.abs(got[True][k] - got[False][k]).max()) for k in got[True])
     assert worst <= rh.tol_for(dtype)
+
+
+def test_graphs_follow_the_key_splits_as_a_context_grows():
+    """One request decoding from 200 to 1,300 tokens with head size 128 in bfloat16: the decode
+    kernel's key splits grow with the context (1, 2, 3, 4, 6 by 1,300 keys), a captured graph holds its
+    number of splits, so the graph's key carries it and a step whose length asks for another number
+    is captured anew.  Every decoded position against the plain code, and bit for bit against the same
+    trace launched kernel by kernel: graph or not, a step makes the same choices."""
+    cfg, page, w, _ = setup("E", "bfloat16")
+    reqs = {"r0": tm.random_tokens(cfg, 1300, 91)}
+    ref = rh.plain_rows(cfg, w, reqs, "bfloat16")
+    steps = rh.trace_tail_decode(reqs, 1100)
+    got = {}
+    for graphs in (True, False):
+        runner = rh.make_runner(cfg, w, "bfloat16", page, max_total_tokens=1344, max_requests=1, max_tokens_per_step=256)
+        runner.use_graphs = runner.use_graphs and graphs
+        got[graphs] = rh.run_trace(runner, steps)
+        rh.assert_rows_match(got[graphs], ref, rh.BF16_TOL, f"growing context, graphs={graphs}")
+        if graphs:
+            splits = sorted({k[-1][0] for k in runner._graphs if k[1] == "decode"})
+            assert splits == [1, 2, 3, 4, 6], splits
+            assert runner.graph_replays >= 1100 - 2 * len(splits)
+    decoded = [k for k in got[True] if k[1] >= 200]
+    assert len(decoded) == 1100 and all(np.array_equal(got[True][k], got[False][k]) for k in decoded)
 
 
 def test_one_layer_at_real_widths():
