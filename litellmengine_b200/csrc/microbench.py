@@ -122,9 +122,8 @@ def main():
     if args.kernel == "decode_attention":
         cache, table, q, pos, ent, slot = paged_setup(args, dev, 1)
         out = torch.empty_like(q)
-        work = args.batch * nkv
-        slots = 2 * torch.cuda.get_device_properties(dev).multi_processor_count
-        splits = args.splits or max(1, min(16, slots // work, args.context // 256))
+        from ..parts.attention import decode_key_splits
+        splits = args.splits or decode_key_splits(dev, args.batch, nkv, args.context)     # what the engine picks
         fn = lambda: ops.paged_attention_decode(q, out, cache, None, args.batch, pos, ent, slot, table, nq, nkv, d, P,
                                                 None, scale, splits, status)
         nbytes = args.batch * args.context * 2 * nkv * d * 2

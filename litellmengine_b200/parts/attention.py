@@ -203,9 +203,11 @@ _SPLIT_STEPS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64)
 
 
 def decode_key_splits(device, n_dec: int, nkv: int, max_kv_len: int) -> int:
-    """As many splits as keep the whole grid resident at once (two CTAs per SM: a second, partial
-    wave costs more than it balances), about 256 keys or more to a split."""
-    by_length = max(1, -(-max_kv_len // 256))
+    """A split costs its launch and its share of the merge, a key costs its bytes: the best number of
+    splits grows as the square root of the length (measured at 1 to 4 rows and 1,024 to 16,384 keys:
+    8, 12, 16, 16 to 24, 24 splits for one row).  Never more than keep the whole grid resident at once
+    (two CTAs per SM: a second, partial wave costs more than it balances), at least 64 keys a split."""
+    by_length = max(1, min(math.ceil(math.sqrt(max_kv_len / 16.0)), -(-max_kv_len // 64)))
     step = max(s for s in _SPLIT_STEPS if s <= by_length)
     return max(1, min(step, _cta_slots(device) // max(1, n_dec * nkv)))
 
