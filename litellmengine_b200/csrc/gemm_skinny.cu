@@ -169,9 +169,13 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
         gs_commit();
     }
     __syncthreads();                                                     // the barriers exist for everyone
-    float acc[MT / 8][4];
+    // Two sums per output, over the even and the odd k-steps: consecutive products then never wait
+    // for one another's accumulator.  They are added when a tile's k-range ends.
+    float acc[MT / 8][4], acc2[MT / 8][4];
 #pragma unroll
-    for (int j = 0; j < MT / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    for (int j = 0; j < MT / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = acc2[j][e] = 0.0f;
     int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk);
     for (int i = 0; i < count; ++i) {
         gs_wait<GS_STAGES - 2>();                                        // this thread's copies of the tokens' rows
@@ -197,13 +201,13 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
             unsigned a0[4], a1[4];
             gs_ldmatrix_x4(a0, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + (lane >> 4)));
             gs_ldmatrix_x4(a1, gs_at_tiled(ws, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kp * 4 + 2 + (lane >> 4)));
+            unsigned b[MT / 8][4];                                       // tokens 8j..8j+7, two k-steps
 #pragma unroll
-            for (int j = 0; j < MT / 8; ++j) {
-                unsigned b[4];                                           // tokens 8j..8j+7, two k-steps
-                gs_ldmatrix_x4(b, gs_at<GS_BK>(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
-                gs_mma(acc[j], a0, b[0], b[1]);
-                gs_mma(acc[j], a1, b[2], b[3]);
-            }
+            for (int j = 0; j < MT / 8; ++j) gs_ldmatrix_x4(b[j], gs_at<GS_BK>(xs, j * 8 + (lane & 7), kp * 4 + (lane >> 3)));
+#pragma unroll
+            for (int j = 0; j < MT / 8; ++j) gs_mma(acc[j], a0, b[j][0], b[j][1]);
+#pragma unroll
+            for (int j = 0; j < MT / 8; ++j) gs_mma(acc2[j], a1, b[j][2], b[j][3]);
         }
         const bool tile_done = kt == nk - 1;
         if (tile_done || i == count - 1) {
@@ -215,16 +219,17 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int f = f0 + (e >> 1) * 8, tok = j * 8 + t0 + (e & 1);
+                    const float sum = acc[j][e] + acc2[j][e];
                     if (f < N && tok < M) {
                         if (slices == 1) {
-                            y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(acc[j][e]);
+                            y[static_cast<size_t>(tok) * N + f] = from_f32<TO>(sum);
                         } else {
-                            partial[(static_cast<size_t>(slice) * M + tok) * N + f] = acc[j][e];
+                            partial[(static_cast<size_t>(slice) * M + tok) * N + f] = sum;
                             if (tile_done && !per_tile)
                                 for (int z = slice + 1; z < slices; ++z) partial[(static_cast<size_t>(z) * M + tok) * N + f] = 0.0f;
                         }
                     }
-                    acc[j][e] = 0.0f;
+                    acc[j][e] = acc2[j][e] = 0.0f;
                 }
             }
         }

@@ -203,13 +203,25 @@ _SPLIT_STEPS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64)
 
 
 def decode_key_splits(device, n_dec: int, nkv: int, max_kv_len: int) -> int:
-    """A split costs its launch and its share of the merge, a key costs its bytes: the best number of
-    splits grows as the square root of the length (measured at 1 to 4 rows and 1,024 to 16,384 keys:
-    8, 12, 16, 16 to 24, 24 splits for one row).  Never more than keep the whole grid resident at once
-    (two CTAs per SM: a second, partial wave costs more than it balances), at least 64 keys a split."""
+    """Two rules, measured.  (1) A split costs its launch and its share of the merge, a key costs its
+    bytes: for a few rows the best number grows as the square root of the length (one row: 8, 12,
+    16, 24 splits at 1,024, 2,304, 4,096, 16,384 keys), at least 64 keys a split.  (2) The grid runs in
+    waves of two CTAs per SM: below that ceiling take the fewest splits that fill at least 0.85 of the
+    waves they start, else the fullest (at 4,096 keys 20 rows: 5 splits, 40 rows: 4, 48 rows: 2,
+    where one split took a quarter longer; 8, 16, 32, 64 rows stay at 4, 2, 1, 1)."""
     by_length = max(1, min(math.ceil(math.sqrt(max_kv_len / 16.0)), -(-max_kv_len // 64)))
-    step = max(s for s in _SPLIT_STEPS if s <= by_length)
-    return max(1, min(step, _cta_slots(device) // max(1, n_dec * nkv)))
+    most = max(s for s in _SPLIT_STEPS if s <= by_length)
+    key = (device, n_dec * nkv, most)
+    got = _split_choice.get(key)
+    if got is None:
+        slots, ctas = _cta_slots(device), max(1, n_dec * nkv)
+        fill = lambda s: ctas * s / (-(-ctas * s // slots) * slots)
+        enough = [s for s in range(1, most + 1) if fill(s) >= 0.85]
+        got = _split_choice[key] = enough[0] if enough else max(range(1, most + 1), key=lambda s: (fill(s), -s))
+    return got
+
+
+_split_choice: Dict[tuple, int] = {}
 
 
 def attention_over_pages(q: torch.Tensor, ctx: StageContext, nq: int, nkv: int, d: int,
