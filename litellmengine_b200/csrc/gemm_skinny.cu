@@ -23,11 +23,15 @@
 #include <unordered_map>
 
 #define GS_ROWS 64          // output features per CTA (16 per warp)
-// k-values per stage and stages, by token tile: two CTAs per SM must fit.  Up to 8 tokens: three
-// stages of 256 k-values (512 contiguous bytes of each weight row per request, which the memory
-// system serves better than 256: 6.2 against 5.9 TB/s on the output head); 16 tokens: five of 128.
-#define GS_BK_FOR(MT) ((MT) <= 8 ? 256 : 128)
-#define GS_STAGES_FOR(MT) ((MT) <= 8 ? 3 : 5)
+// k-values per stage and stages, by token tile: two CTAs per SM must fit.  Three stages of weights of
+// 256 k-values (512 contiguous bytes of each weight row per request, which the memory system serves
+// better than 256: 6.2 against 5.9 TB/s on the output head).  The tokens' rows of a stage come from L2:
+// up to 8 tokens they are fetched two stages ahead like the weights; 16 tokens have room for two
+// stages of rows only and fetch one stage ahead (five stages of 128 k-values, the layout before, paid
+// a barrier round per 16 KB of weights: 39.4 us on a 24,576 x 4,096 product where this takes 36).
+#define GS_BK_FOR(MT) 256
+#define GS_STAGES_FOR(MT) 3
+#define GS_XSTAGES_FOR(MT) ((MT) <= 8 ? 3 : 2)
 #define GS_THREADS 128
 
 __device__ __forceinline__ void gs_cp_async16(void* smem, const void* gmem, bool valid) {
@@ -63,7 +67,7 @@ __host__ __device__ __forceinline__ long long gs_cta_of(long long item, long lon
 // rows whose 16-byte chunks are XOR-swizzled by the row (chunk c of row r at position c ^ (r % 8):
 // the layout the copy engine's 128-byte swizzle writes and tcgen05 reads as a K-major operand, so
 // zero-padded at the edges.  A stage of weights is then ONE
-// contiguous piece of memory (a block of 32 KB for up to 8 tokens, half a block for 9 to 16),
+// contiguous piece of memory (a block of 32 KB),
 // fetched by one bulk copy (cp.async.bulk) of one thread instead of 2,048 sixteen-byte copies
 // of 128 threads, and DRAM sees whole pages instead of 512-byte runs 8 KB apart (measured with
 // the copy engine alone: 7.4 TB/s for contiguous pieces against 6.2 for the strided form; a whole
@@ -87,8 +91,8 @@ __device__ __forceinline__ bf16* gs_at_tiled(bf16* base, int row, int chunk) {
     return base + (chunk >> 3) * (GS_ROWS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
-// MT = 8: stages of 256 k-values (a whole 32 KB block), three of them; MT = 16: stages of 128 k-values
-// (half a block: two sub-tiles, 16 KB contiguous), five of them, so that two CTAs fit an SM.
+// A stage is a whole 32 KB block; three stages of weights, and three (up to 8 tokens) or two (16) of the
+// tokens' rows, so that two CTAs fit an SM.
 //
 // BOXES: the same stage fetched from the plain [N, K] weights instead, by the copy engine's tiled mode:
 // a stage is GS_BK / 64 boxes of [64 rows][64 k-values] that the 128-byte swizzle lays down in exactly
@@ -99,12 +103,12 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
                                                                          float* __restrict__ partial, int M, int N, int K,
                                                                          int slices, int per_tile, int32_t* __restrict__ status,
                                                                          const __grid_constant__ CUtensorMap w_map) {
-    constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT);
+    constexpr int GS_STAGES = GS_STAGES_FOR(MT), GS_BK = GS_BK_FOR(MT), GS_XSTAGES = GS_XSTAGES_FOR(MT);
     constexpr unsigned W_BYTES = GS_ROWS * GS_BK * sizeof(bf16);
     const long long halves_per_tile = static_cast<long long>((K + 255) / 256) * (256 / GS_BK);   // stages of GS_BK in a tile's row of blocks
     extern __shared__ __align__(1024) unsigned char smem_raw[];          // the swizzle's pattern repeats every 1024 bytes
     bf16* w_s = reinterpret_cast<bf16*>(smem_raw);                       // [STAGES][64][BK], as stored in w_tiled
-    bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [STAGES][MT][BK]
+    bf16* x_s = w_s + GS_STAGES * GS_ROWS * GS_BK;                       // [XSTAGES][MT][BK]
     __shared__ __align__(8) unsigned long long full[GS_STAGES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nk = (K + GS_BK - 1) / GS_BK, tiles = (N + GS_ROWS - 1) / GS_ROWS;
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
     };
     auto load_x = [&](int i) {
         const int k0 = static_cast<int>((begin + i) % nk) * GS_BK;
-        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
+        bf16* xs = x_s + (i % GS_XSTAGES) * MT * GS_BK;
 #pragma unroll
         for (int j = 0; j < MT * CPR / GS_THREADS; ++j) {
             const int c = tid + GS_THREADS * j, row = c / CPR, ch = c % CPR;
@@ -164,7 +168,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
     }
     pdl_wait();
 #pragma unroll
-    for (int s = 0; s < GS_STAGES - 1; ++s) {
+    for (int s = 0; s < GS_XSTAGES - 1; ++s) {
         if (s < count) load_x(s);
         gs_commit();
     }
@@ -178,7 +182,7 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
         for (int e = 0; e < 4; ++e) acc[j][e] = acc2[j][e] = 0.0f;
     int tile = static_cast<int>(begin / nk), kt = static_cast<int>(begin % nk);
     for (int i = 0; i < count; ++i) {
-        gs_wait<GS_STAGES - 2>();                                        // this thread's copies of the tokens' rows
+        gs_wait<GS_XSTAGES - 2>();                                       // this thread's copies of the tokens' rows
         {
             int n = 0;
             while (!gs_try_wait(&full[i % GS_STAGES], (i / GS_STAGES) & 1)) {
@@ -189,13 +193,11 @@ __global__ void __launch_bounds__(GS_THREADS) linear_skinny_tiled_kernel(const b
             }
         }
         __syncthreads();                                                 // everyone's rows are there; stage i-1 is no longer read
-        if (i + GS_STAGES - 1 < count) {
-            load_w(i + GS_STAGES - 1);
-            load_x(i + GS_STAGES - 1);
-        }
+        if (i + GS_STAGES - 1 < count) load_w(i + GS_STAGES - 1);
+        if (i + GS_XSTAGES - 1 < count) load_x(i + GS_XSTAGES - 1);
         gs_commit();
         bf16* ws = w_s + (i % GS_STAGES) * GS_ROWS * GS_BK;
-        bf16* xs = x_s + (i % GS_STAGES) * MT * GS_BK;
+        bf16* xs = x_s + (i % GS_XSTAGES) * MT * GS_BK;
 #pragma unroll
         for (int kp = 0; kp < GS_BK / 32; ++kp) {
             unsigned a0[4], a1[4];
@@ -367,7 +369,7 @@ static int launch_skinny_tiled(const bf16* x, const bf16* wt, void* y, float* sc
         if (m == nullptr) return LLM_REFUSED_ALIGN;                      // the driver refused the weights' address or strides
         map = *m;
     }
-    const size_t smem = static_cast<size_t>(GS_STAGES_FOR(MT)) * (GS_ROWS + MT) * GS_BK_FOR(MT) * sizeof(bf16);
+    const size_t smem = (static_cast<size_t>(GS_STAGES_FOR(MT)) * GS_ROWS + GS_XSTAGES_FOR(MT) * MT) * GS_BK_FOR(MT) * sizeof(bf16);
     auto kern = linear_skinny_tiled_kernel<MT, TO, BOXES>;
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
