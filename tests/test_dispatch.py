@@ -41,3 +41,21 @@ def test_partial_sums_add_up_and_round_once():
     assert torch.equal(total, (parts[0] + parts[1]) + parts[2])
     rounded = ops.as_tensor(ops.PartialSum(parts, torch.bfloat16))
     assert rounded.dtype == torch.bfloat16 and torch.equal(rounded, total.to(torch.bfloat16))
+
+
+def test_decode_key_splits_follow_the_length_and_the_wave_fill():
+    """On a device of 148 SMs (296 CTA slots).  Few rows: the square-root rule, in steps, never under
+    64 keys a split.  More rows: the fewest splits that fill 0.85 of the waves they start."""
+    from litellmengine_b200.parts import attention
+    dev = torch.device("cpu")
+    attention._slots[dev] = 296
+    attention._split_choice.clear()
+    try:
+        pick = lambda rows, kv, nkv=8: attention.decode_key_splits(dev, rows, nkv, kv)
+        assert [pick(1, kv) for kv in (1, 64, 65, 300, 1024, 2304, 4096, 8192, 32768)] == [1, 1, 2, 4, 8, 12, 16, 16, 32]
+        assert [pick(rows, 4096) for rows in (2, 4, 8, 12, 16, 20, 24, 32, 40, 48, 64, 128)] == [16, 8, 4, 3, 2, 5, 3, 1, 4, 2, 1, 1]
+        assert pick(40, 100) == 2 and pick(40, 64) == 1                 # a short context caps it
+        assert pick(1, 1300, nkv=2) == 8 and pick(1, 201, nkv=2) == 4
+    finally:
+        del attention._slots[dev]
+        attention._split_choice.clear()
