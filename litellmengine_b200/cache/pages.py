@@ -1,7 +1,8 @@
 """The cache manager: pages of keys and values, block tables, fixed-size state slots.
 
-Host bookkeeping is plain Python and works without a GPU (the tests drive it on the CPU);
-device tensors are attached when a device is given.
+The bookkeeping (pools, tables, slots) is native code (`csrc/host_core.cpp`, no device needed: the
+tests drive it on the CPU); the classes here give it its names, raise its errors and own the device
+tensors, which are attached when a device is given.
 
 Vocabulary
   slot    the index a live request holds from admission to release; it picks the request's
@@ -27,7 +28,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import ctypes
+
 import numpy as np
+
+from ..csrc import host
 
 
 class OutOfPages(RuntimeError):
@@ -38,44 +43,49 @@ class CacheError(RuntimeError):
     """A misuse of the cache manager: double free, unknown slot, shrinking a request."""
 
 
+def _check(rc: int) -> None:
+    if rc == 1:
+        raise OutOfPages(host.last_error())
+    if rc:
+        raise CacheError(host.last_error())
+
+
+def _int32(values) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.int32)
+
+
 class PagePool:
     """Free list of physical page ids, last-in first-out; a fresh pool hands out 0, 1, 2, ..."""
 
-    def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise CacheError("a page pool needs at least one page")
-        self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._used = [False] * num_pages
+    def __init__(self, num_pages: int, _borrowed=None):
+        self._lib = host.lib()
+        self._own = _borrowed is None
+        self._h = self._lib.hc_pool_new(int(num_pages)) if self._own else _borrowed
+        if not self._h:
+            raise CacheError(host.last_error())
+        self.num_pages = self._lib.hc_pool_num_pages(self._h)
+
+    def __del__(self):
+        if getattr(self, "_own", False) and self._h:
+            self._lib.hc_pool_delete(self._h)
+            self._h = None
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return self._lib.hc_pool_free_count(self._h)
 
     def take(self, n: int) -> List[int]:
-        if n < 0:
-            raise CacheError("cannot take a negative number of pages")
-        if n > len(self._free):
-            raise OutOfPages(f"not enough free pages: want {n}, have {len(self._free)} of {self.num_pages}")
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._used[p] = True
-        return out
+        out = np.empty(max(int(n), 0), dtype=np.int32)
+        _check(self._lib.hc_pool_take(self._h, int(n), out.ctypes.data))
+        return out.tolist()
 
     def give(self, pages: Sequence[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.num_pages:
-                raise CacheError(f"page id {p} is outside the pool")
-            if not self._used[p]:
-                raise CacheError(f"page {p} freed twice")
-        if len(set(pages)) != len(pages):
-            raise CacheError("the same page given back twice in one call")
-        for p in pages:
-            self._used[p] = False
-            self._free.append(p)
+        arr = _int32(list(pages))
+        _check(self._lib.hc_pool_give(self._h, arr.ctypes.data, len(arr)))
 
     def used_pages(self) -> List[int]:
-        return [i for i, u in enumerate(self._used) if u]
+        out = np.empty(self.num_pages, dtype=np.int32)
+        return out[:self._lib.hc_pool_used(self._h, out.ctypes.data)].tolist()
 
 
 @dataclass(frozen=True)
@@ -105,65 +115,37 @@ class StateNeed:
 
 
 class CacheGroup:
-    def __init__(self, need: PagedNeed, stages: List[int], page_size: int, num_pages: int,
-                 max_slots: int, max_pages_per_request: int):
+    """One group's view of the native records: its pool, its table `[slots, pages per request]`
+    (-1 where nothing is held), and per slot the lowest logical page still held and the number of
+    logical pages ever appended (numpy views of the library's memory), beside the device tensors."""
+
+    def __init__(self, need: PagedNeed, stages: List[int], page_size: int):
         self.need = need
         self.stages = list(stages)
         self.page_size = page_size
-        self.pool = PagePool(num_pages)
-        self.max_pages_per_request = max_pages_per_request
-        self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
-        self.first_held = [0] * max_slots     # lowest logical page still held
-        self.num_logical = [0] * max_slots    # logical pages ever appended
-        self.pending: List[Tuple[int, int]] = []    # (flat table index, page id) not yet on the device
+        self.pool: Optional[PagePool] = None
+        self.max_pages_per_request = 0
+        self.table: Optional[np.ndarray] = None
+        self.first_held: Optional[np.ndarray] = None
+        self.num_logical: Optional[np.ndarray] = None
         self.kv = None                        # device tensor [stages, pages, 2, kv_heads, P, d] when keys and values are equally wide
         self.keys = None                      # [stages, pages, kv_heads, P, key width] (a view of `kv` when that exists)
         self.values = None                    # [stages, pages, kv_heads, P, value width]
         self.table_dev = None                 # device int32 [max_slots, max_pages_per_request]
 
+    def _bind(self, lib, handle, index: int, max_slots: int, max_pages_per_request: int) -> None:
+        self.max_pages_per_request = max_pages_per_request
+        self.pool = PagePool(0, _borrowed=lib.hc_cache_pool(handle, index))
+        view = lambda ptr, shape: np.ctypeslib.as_array(ptr, shape=shape)
+        self.table = view(lib.hc_cache_table(handle, index), (max_slots, max_pages_per_request))
+        self.first_held = view(lib.hc_cache_first_held(handle, index), (max_slots,))
+        self.num_logical = view(lib.hc_cache_num_logical(handle, index), (max_slots,))
+
     def pages_for(self, length: int) -> int:
         return (length + self.page_size - 1) // self.page_size
 
-    def missing(self, slot: int, new_len: int) -> int:
-        return max(0, self.pages_for(new_len) - self.num_logical[slot])
-
-    def append(self, slot: int, new_len: int) -> None:
-        want = self.pages_for(new_len)
-        if want > self.max_pages_per_request:
-            raise CacheError(f"a request of {new_len} tokens needs {want} pages; the table holds "
-                             f"{self.max_pages_per_request}")
-        have = self.num_logical[slot]
-        if want <= have:
-            return
-        pages = self.pool.take(want - have)
-        for i, p in enumerate(pages):
-            self.table[slot, have + i] = p
-            self.pending.append((slot * self.max_pages_per_request + have + i, p))
-        self.num_logical[slot] = want
-
-    def trim_window(self, slot: int, length: int) -> int:
-        """Give back pages every position of which lies before the window of the next query
-        (position `length`, which sees keys > length - window).  Returns how many."""
-        w = self.need.window
-        if w is None:
-            return 0
-        first_needed = max(0, length - w + 1)
-        keep_from = min(first_needed // self.page_size, self.num_logical[slot])
-        lo = self.first_held[slot]
-        if keep_from <= lo:
-            return 0
-        self.pool.give([int(self.table[slot, i]) for i in range(lo, keep_from)])
-        self.first_held[slot] = keep_from
-        return keep_from - lo
-
-    def release(self, slot: int) -> None:
-        lo, hi = self.first_held[slot], self.num_logical[slot]
-        self.pool.give([int(self.table[slot, i]) for i in range(lo, hi)])
-        self.first_held[slot] = 0
-        self.num_logical[slot] = 0
-
     def held_pages(self, slot: int) -> List[int]:
-        return [int(self.table[slot, i]) for i in range(self.first_held[slot], self.num_logical[slot])]
+        return [int(p) for p in self.table[slot, self.first_held[slot]:self.num_logical[slot]]]
 
 
 class CacheManager:
@@ -202,8 +184,7 @@ class CacheManager:
                 if gi is None:
                     gi = len(self.groups)
                     by_need[need] = gi
-                    self.groups.append(CacheGroup(need, [], page_size, self.num_pages, max_slots,
-                                                  max_pages_per_request))
+                    self.groups.append(CacheGroup(need, [], page_size))
                 g = self.groups[gi]
                 self.stage_group[s] = (gi, len(g.stages))
                 g.stages.append(s)
@@ -216,9 +197,14 @@ class CacheManager:
                     raise CacheError(f"stage {s} borrows the cache of stage {src}, which has none")
                 self.stage_group[s] = self.stage_group[src]
 
-        self._free_slots = list(range(max_slots - 1, -1, -1))
-        self._live = [False] * max_slots
-        self._length = [0] * max_slots
+        self._lib = host.lib()
+        windows = _int32([-1 if g.need.window is None else g.need.window for g in self.groups])
+        self._h = self._lib.hc_cache_new(len(self.groups), windows.ctypes.data, page_size, self.num_pages, max_slots,
+                                         max_pages_per_request, self.max_request_tokens)
+        if not self._h:
+            raise CacheError(host.last_error())
+        for i, g in enumerate(self.groups):
+            g._bind(self._lib, self._h, i, max_slots, max_pages_per_request)
         self.state: Dict[object, object] = {}     # stage index or name -> device tensor [max_slots, *shape]
         self._extra_state = dict(extra_state or {})
         if device is not None:
@@ -266,123 +252,83 @@ class CacheManager:
                    for g in self.groups)
 
     # ---- slots -----------------------------------------------------------------------------
+    def __del__(self):
+        if getattr(self, "_h", None):
+            for g in self.groups:                          # their views point into what is about to go
+                g.table = g.first_held = g.num_logical = g.pool = None
+            self._lib.hc_cache_delete(self._h)
+            self._h = None
+
     @property
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.hc_cache_free_slots(self._h)
 
     def admit(self) -> int:
         """Take a slot for a new request; its state tensors are zeroed."""
-        if not self._free_slots:
-            raise OutOfPages("no free request slot")
-        slot = self._free_slots.pop()
-        self._live[slot] = True
-        self._length[slot] = 0
+        slot = ctypes.c_int()
+        _check(self._lib.hc_cache_admit(self._h, ctypes.byref(slot)))
         for t in self.state.values():
-            t[slot].zero_()
-        return slot
-
-    def _check_live(self, slot: int) -> None:
-        if not (0 <= slot < self.max_slots) or not self._live[slot]:
-            raise CacheError(f"slot {slot} is not held by a request")
+            t[slot.value].zero_()
+        return slot.value
 
     def length(self, slot: int) -> int:
-        self._check_live(slot)
-        return self._length[slot]
+        out = ctypes.c_longlong()
+        _check(self._lib.hc_cache_length(self._h, int(slot), ctypes.byref(out)))
+        return out.value
 
     def release(self, slot: int) -> None:
         """The request is over (finished or preempted): every page and the slot go back."""
-        self._check_live(slot)
-        for g in self.groups:
-            g.release(slot)
-        self._live[slot] = False
-        self._length[slot] = 0
-        self._free_slots.append(slot)
+        _check(self._lib.hc_cache_release(self._h, int(slot)))
 
     # ---- pages -----------------------------------------------------------------------------
     def pages_missing(self, slot: int, new_len: int) -> List[int]:
-        self._check_live(slot)
-        return [g.missing(slot, new_len) for g in self.groups]
+        out = np.empty(len(self.groups), dtype=np.int32)
+        _check(self._lib.hc_cache_pages_missing(self._h, int(slot), int(new_len), out.ctypes.data))
+        return out.tolist()
 
     def can_hold(self, wants: Sequence[Tuple[Optional[int], int]]) -> bool:
         """Would `ensure` succeed for all of (slot or None for a request not yet admitted,
         new length) together?"""
-        need = [0] * len(self.groups)
-        new_slots = 0
-        for slot, new_len in wants:
-            if new_len > self.max_request_tokens:
-                return False
-            if slot is None:
-                new_slots += 1
-                for i, g in enumerate(self.groups):
-                    need[i] += g.pages_for(new_len)
-            else:
-                for i, m in enumerate(self.pages_missing(slot, new_len)):
-                    need[i] += m
-        return new_slots <= self.free_slots and all(n <= g.pool.free_count for n, g in zip(need, self.groups))
+        slots = _int32([-1 if s is None else s for s, _ in wants])
+        lens = np.ascontiguousarray([n for _, n in wants], dtype=np.int64)
+        yes = ctypes.c_int()
+        _check(self._lib.hc_cache_can_hold(self._h, len(slots), slots.ctypes.data, lens.ctypes.data, ctypes.byref(yes)))
+        return bool(yes.value)
 
     def reserve(self, need: Sequence[int], slot: Optional[int], new_len: int) -> Optional[List[int]]:
         """`need` (pages per group already promised in this step) plus what (slot or None, new
         length) wants, or None if that does not fit the free pages.  `can_hold` one request at a
         time, for callers that build a step up."""
-        if new_len > self.max_request_tokens:
-            return None
-        if slot is None:
-            total = [n + g.pages_for(new_len) for n, g in zip(need, self.groups)]
-        else:
-            total = [n + m for n, m in zip(need, self.pages_missing(slot, new_len))]
-        return total if all(t <= g.pool.free_count for t, g in zip(total, self.groups)) else None
+        have = _int32(need)
+        total = np.empty(len(self.groups), dtype=np.int32)
+        fits = ctypes.c_int()
+        _check(self._lib.hc_cache_reserve(self._h, have.ctypes.data, -1 if slot is None else int(slot), int(new_len),
+                                          total.ctypes.data, ctypes.byref(fits)))
+        return total.tolist() if fits.value else None
 
     def ensure(self, slot: int, new_len: int) -> None:
         """Make room for positions [0, new_len) of the request, in every group, or take nothing."""
-        self._check_live(slot)
-        if new_len < self._length[slot]:
-            raise CacheError("a request's cache never shrinks")
-        if new_len > self.max_request_tokens:
-            raise OutOfPages(f"a request of {new_len} tokens exceeds the limit of {self.max_request_tokens}")
-        for g, m in zip(self.groups, self.pages_missing(slot, new_len)):
-            if m > g.pool.free_count:
-                raise OutOfPages(f"not enough free pages: want {m}, have {g.pool.free_count} of {g.pool.num_pages}")
-        for g in self.groups:
-            g.append(slot, new_len)
+        _check(self._lib.hc_cache_ensure(self._h, int(slot), int(new_len)))
 
     def commit(self, slot: int, new_len: int) -> int:
         """The step that filled positions up to new_len has been issued: record the length and
         give back pages that a window has passed.  Returns the number of pages given back."""
-        self._check_live(slot)
-        if new_len < self._length[slot]:
-            raise CacheError("a request's cache never shrinks")
-        self._length[slot] = new_len
-        return sum(g.trim_window(slot, new_len) for g in self.groups)
+        given = ctypes.c_int()
+        _check(self._lib.hc_cache_commit(self._h, int(slot), int(new_len), ctypes.byref(given)))
+        return given.value
 
     def drain_updates(self) -> List[Tuple[np.ndarray, np.ndarray]]:
         """Per group: (flat table indices, page ids) changed since the last call."""
         out = []
-        for g in self.groups:
-            if g.pending:
-                arr = np.asarray(g.pending, dtype=np.int32)
-                out.append((arr[:, 0].copy(), arr[:, 1].copy()))
-                g.pending.clear()
-            else:
-                out.append((np.empty(0, np.int32), np.empty(0, np.int32)))
+        for i in range(len(self.groups)):
+            n = self._lib.hc_cache_pending(self._h, i)
+            idx, val = np.empty(n, np.int32), np.empty(n, np.int32)
+            if n:
+                self._lib.hc_cache_drain(self._h, i, idx.ctypes.data, val.ctypes.data)
+            out.append((idx, val))
         return out
 
     # ---- checks ----------------------------------------------------------------------------
     def check_invariants(self) -> None:
         """No page lost, none held twice, none both free and held."""
-        for gi, g in enumerate(self.groups):
-            held: List[int] = []
-            for slot in range(self.max_slots):
-                if self._live[slot]:
-                    held += g.held_pages(slot)
-                elif g.num_logical[slot] or g.first_held[slot]:
-                    raise CacheError(f"group {gi}: released slot {slot} still has pages")
-            if len(set(held)) != len(held):
-                raise CacheError(f"group {gi}: a page is held twice")
-            used = set(g.pool.used_pages())
-            if used != set(held):
-                raise CacheError(f"group {gi}: pool says {sorted(used)} are out, requests hold {sorted(held)}")
-            if g.pool.free_count + len(held) != g.pool.num_pages:
-                raise CacheError(f"group {gi}: {g.pool.free_count} free + {len(held)} held != {g.pool.num_pages}")
-        live = sum(self._live)
-        if live + len(self._free_slots) != self.max_slots or len(set(self._free_slots)) != len(self._free_slots):
-            raise CacheError("slot accounting is off")
+        _check(self._lib.hc_cache_check(self._h))

@@ -36,14 +36,21 @@ FAMILIES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu"],
     "gemm_skinny": ["gemm_skinny.cu"],
     "gemm_pair_tcgen05": ["gemm_pair_tcgen05.cu"],
+    "host_core": ["host_core.cpp"],            # the host side's bookkeeping: plain C++, no device code
 }
+HOST_FAMILIES = {"host_core"}
 HEADERS = ["common.cuh", "attention_decode_noalloc.h", "attention_decode_tma.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC",
 ]
+HOST_FLAGS = ["-O2", "-std=c++17", "--shared", "-Xcompiler", "-fPIC"]
 EXTRA_FLAGS: Dict[str, List[str]] = {}
+
+
+def _flags(family: str) -> List[str]:
+    return (HOST_FLAGS if family in HOST_FAMILIES else NVCC_FLAGS) + EXTRA_FLAGS.get(family, [])
 
 _lock = threading.Lock()
 _family_locks: Dict[str, threading.Lock] = {}
@@ -94,11 +101,11 @@ def build_dir() -> str:
 
 def _digest(family: str) -> str:
     h = hashlib.sha256()
-    for fn in HEADERS + FAMILIES[family]:
+    for fn in ([] if family in HOST_FAMILIES else HEADERS) + FAMILIES[family]:
         with open(os.path.join(CSRC, fn), "rb") as f:
             h.update(fn.encode())
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS.get(family, [])).encode())
+    h.update(" ".join(_flags(family)).encode())
     return h.hexdigest()[:16]
 
 
@@ -124,10 +131,11 @@ def ensure_built(family: str, verbose: bool = True) -> str:
         nvcc = _nvcc()
         srcs = [os.path.join(CSRC, fn) for fn in FAMILIES[family]]
         tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-        cmd = [nvcc] + NVCC_FLAGS + EXTRA_FLAGS.get(family, []) + ["-I", CSRC, "-o", tmp] + srcs
+        cmd = [nvcc] + _flags(family) + ["-I", CSRC, "-o", tmp] + srcs
+        what = family if family in HOST_FAMILIES else f"{family} for sm_100a"
         t0 = time.time()
         if verbose:
-            print(f"[litellmengine_b200] compiling {family} for sm_100a ...", file=sys.stderr, flush=True)
+            print(f"[litellmengine_b200] compiling {what} ...", file=sys.stderr, flush=True)
         proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                                 cwd=build_dir())
         done = threading.Event()
