@@ -1,8 +1,9 @@
 // The host side's bookkeeping, native: page pools, block tables and request slots of the cache
-// manager.  Plain C++ behind a C interface (called through ctypes like the kernels); it touches no
-// device and runs on a machine without one.  The Python classes of `cache/pages.py` own the device
-// tensors and present these records under their documented names; the rules are the ones stated
-// there and are pinned by the CPU tests.
+// manager, and the scheduler's records and decisions.  Plain C++ behind a C interface (called through
+// ctypes like the kernels); it touches no device and runs on a machine without one.  The Python
+// classes of `cache/pages.py` and `engine/scheduler.py` own the device tensors and the token lists
+// and present these records under their documented names; the rules are the ones stated there and
+// are pinned by the CPU tests.
 //
 // What is kept from the reference's block table manager (src/engine/block_table_manager.cpp:17-275):
 // a last-in first-out free list that hands out 0, 1, 2, ... first (213-253), all-or-nothing `ensure`
@@ -15,6 +16,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <deque>
 #include <string>
 #include <vector>
 
@@ -136,8 +138,76 @@ struct Cache {
     }
 };
 
+// ---- the scheduler's records --------------------------------------------------------------------------
+// A request as the scheduler knows it: lengths and states, no token (the token lists stay with the
+// caller).  `pending` counts a token that a launched step has sampled on the device and the host has
+// not read yet: part of the request's length, not of its known tokens.
+enum { ST_WAITING = 0, ST_RUNNING = 1, ST_FINISHED = 2 };
+enum { FIN_NONE = 0, FIN_EOS = 1, FIN_LENGTH = 2, FIN_RELEASED = 3 };
+
+struct Req {
+    int32_t status = ST_WAITING, slot = -1, pending = 0, feedback_index = -1, preemptions = 0, finish = FIN_NONE, eos = -1;
+    long long input_len = 0, prompt_len = 0, max_new = 0, generated = 0, cached_len = 0;
+    long long extend_len() const { return input_len + pending - cached_len; }
+    long long remain_len() const { return max_new - generated - pending; }   // tokens still to be sampled by steps not yet launched
+};
+
+struct Portion {
+    int32_t id;
+    long long num_tokens;
+    int32_t samples, admitted;
+};
+
+struct Sched {
+    Cache* cache;
+    long long max_tokens, chunk, num_preemptions = 0;
+    std::vector<Req> reqs;                                // by request id
+    std::deque<int32_t> waiting;                          // first come first served; a preempted request goes to the front
+    std::vector<int32_t> running;                         // in admission order
+
+    // `need` plus what (slot or -1, new length) wants, into `need`; false if that exceeds the free pages
+    // (or the request's limit), and `need` is then left as it was.
+    bool reserve(std::vector<int32_t>& need, int slot, long long new_len, bool keep_anyway = false) const {
+        if (new_len > cache->max_request_tokens && !keep_anyway) return false;
+        std::vector<int32_t> total(need.size());
+        bool ok = true;
+        for (size_t g = 0; g < need.size(); ++g) {
+            const Group& gr = cache->groups[g];
+            total[g] = need[g] + (slot < 0 ? gr.pages_for(new_len) : gr.missing(slot, new_len));
+            ok = ok && total[g] <= gr.pool.free_count();
+        }
+        if (ok || keep_anyway) need = total;
+        return ok;
+    }
+    int release_slot(Req& r) {
+        for (Group& g : cache->groups)
+            if (int rc = g.release(r.slot)) return rc;
+        cache->live[r.slot] = 0;
+        cache->length[r.slot] = 0;
+        cache->free_slots.push_back(r.slot);
+        r.slot = -1;
+        return HC_OK;
+    }
+    // Pages ran out for an older request: the most recently admitted running request gives back its
+    // pages and its slot, keeps its tokens and goes to the front of the waiting queue.
+    int preempt_latest(int32_t* victim) {
+        *victim = running.back();
+        running.pop_back();
+        Req& r = reqs[*victim];
+        if (int rc = release_slot(r)) return rc;
+        r.cached_len = 0;
+        r.status = ST_WAITING;
+        ++r.preemptions;
+        ++num_preemptions;
+        waiting.push_front(*victim);
+        return HC_OK;
+    }
+    bool has_work() const { return !waiting.empty() || !running.empty(); }
+};
+
 Pool* pool_of(void* p) { return static_cast<Pool*>(p); }
 Cache* cache_of(void* p) { return static_cast<Cache*>(p); }
+Sched* sched_of(void* p) { return static_cast<Sched*>(p); }
 
 }  // namespace
 
@@ -343,6 +413,220 @@ int hc_cache_check(void* cp) {
     std::sort(sorted.begin(), sorted.end());
     if (live + static_cast<int>(sorted.size()) != c->max_slots || std::adjacent_find(sorted.begin(), sorted.end()) != sorted.end())
         return fail(HC_MISUSE, "slot accounting is off");
+    return HC_OK;
+}
+
+// ---- the scheduler ----------------------------------------------------------------------------------------
+// Rules, every step: (1) running requests that decode go first, oldest admission first; (2) running
+// requests still reading their prompt get a portion of at most `chunk` tokens within what is left of
+// `max_tokens`; (3) waiting requests are admitted first come first served while a slot is free, budget
+// is left and the pages of their first portion are free, stopping at the first that does not fit.
+// When pages run out for a running request the most recently admitted one is preempted, again and
+// again until the older one fits; no admission in a step that preempted.
+void* hc_sched_new(void* cache, long long max_tokens, long long chunk) {
+    if (max_tokens <= 0 || chunk <= 0) {
+        fail(HC_MISUSE, "max_tokens_per_step and chunk must be positive");
+        return nullptr;
+    }
+    Sched* s = new Sched();
+    s->cache = cache_of(cache);
+    s->max_tokens = max_tokens;
+    s->chunk = std::min(chunk, max_tokens);
+    return s;
+}
+void hc_sched_delete(void* s) { delete sched_of(s); }
+
+int hc_sched_add(void* sp, long long prompt_len, long long max_new, int eos, int* id) {
+    Sched* s = sched_of(sp);
+    if (prompt_len <= 0) return fail(HC_MISUSE, "a request needs at least one prompt token");
+    if (max_new < 0) return fail(HC_MISUSE, "max_new_tokens must be >= 0");
+    const long long longest = prompt_len + std::max(max_new - 1, 0LL);   // the last sampled token is never run
+    if (longest > s->cache->max_request_tokens)
+        return fail(HC_OUT_OF_PAGES, "request needs " + str(longest) + " cached tokens; the cache takes at most " +
+                                         str(s->cache->max_request_tokens) + " per request");
+    Req r;
+    r.input_len = r.prompt_len = prompt_len;
+    r.max_new = max_new;
+    r.eos = eos;
+    *id = static_cast<int>(s->reqs.size());
+    if (max_new == 0) {
+        r.status = ST_FINISHED;
+        r.finish = FIN_LENGTH;
+    } else {
+        s->waiting.push_back(*id);
+    }
+    s->reqs.push_back(r);
+    return HC_OK;
+}
+
+int hc_sched_has_work(void* s) { return sched_of(s)->has_work() ? 1 : 0; }
+long long hc_sched_num_preemptions(void* s) { return sched_of(s)->num_preemptions; }
+int hc_sched_queue(void* sp, int which, int32_t* out, int cap) {     // which: 0 waiting, 1 running; returns the length
+    Sched* s = sched_of(sp);
+    int n = 0;
+    if (which == 0) {
+        for (int32_t id : s->waiting) { if (n < cap) out[n] = id; ++n; }
+    } else {
+        for (int32_t id : s->running) { if (n < cap) out[n] = id; ++n; }
+    }
+    return n;
+}
+
+// field: 0 status, 1 slot, 2 pending, 3 feedback_index, 4 preemptions, 5 finish reason, 6 cached_len,
+// 7 input_len, 8 generated
+long long hc_sched_get(void* sp, int id, int field) {
+    const Req& r = sched_of(sp)->reqs[id];
+    switch (field) {
+        case 0: return r.status;
+        case 1: return r.slot;
+        case 2: return r.pending;
+        case 3: return r.feedback_index;
+        case 4: return r.preemptions;
+        case 5: return r.finish;
+        case 6: return r.cached_len;
+        case 7: return r.input_len;
+        default: return r.generated;
+    }
+}
+
+// The next step: up to `cap` portions (request id, tokens, whether a token is sampled at its end, whether
+// the request was admitted just now: its slot's state is the caller's to clear).
+int hc_sched_schedule(void* sp, int32_t* ids, long long* num_tokens, int32_t* samples, int32_t* admitted, int cap, int* count) {
+    Sched* s = sched_of(sp);
+    Cache* c = s->cache;
+    long long budget = s->max_tokens;
+    std::vector<Portion> plan;
+    std::vector<int32_t> need(c->groups.size(), 0);       // pages per group already promised in this step
+    bool preempted = false;
+    std::vector<int32_t> queue(s->running);               // decoders first, each kind oldest first
+    std::stable_sort(queue.begin(), queue.end(), [&](int32_t a, int32_t b) {
+        return (s->reqs[a].extend_len() > 1) < (s->reqs[b].extend_len() > 1);
+    });
+    for (size_t i = 0; i < queue.size(); ++i) {
+        Req& r = s->reqs[queue[i]];
+        if (r.status != ST_RUNNING || r.remain_len() <= 0) continue;    // preempted below, or only awaiting its last token
+        if (budget <= 0) break;
+        const long long n = std::min({r.extend_len(), s->chunk, budget});
+        bool fits;
+        while (!(fits = s->reserve(need, r.slot, r.cached_len + n))) {
+            int32_t victim;
+            if (int rc = s->preempt_latest(&victim)) return rc;
+            preempted = true;
+            plan.erase(std::remove_if(plan.begin(), plan.end(), [&](const Portion& p) { return p.id == victim; }), plan.end());
+            budget = s->max_tokens;
+            std::fill(need.begin(), need.end(), 0);
+            for (const Portion& p : plan) {               // the pool changed: count the promises again
+                budget -= p.num_tokens;
+                const Req& q = s->reqs[p.id];
+                s->reserve(need, q.slot, q.cached_len + p.num_tokens, true);
+            }
+            if (victim == queue[i]) break;
+        }
+        if (!fits || r.status != ST_RUNNING) continue;
+        plan.push_back({queue[i], n, n == r.extend_len() ? 1 : 0, 0});
+        budget -= n;
+    }
+    // no admission in a step that had to preempt: the victim would come straight back
+    while (!preempted && !s->waiting.empty() && budget > 0 && !c->free_slots.empty()) {
+        const int32_t id = s->waiting.front();
+        Req& r = s->reqs[id];
+        if (r.remain_len() <= 0) break;                   // preempted with its last token on its way
+        const long long n = std::min({r.extend_len(), s->chunk, budget});
+        if (!s->reserve(need, -1, n)) break;
+        s->waiting.pop_front();
+        int slot;
+        if (int rc = hc_cache_admit(c, &slot)) return rc;
+        r.slot = slot;
+        r.status = ST_RUNNING;
+        s->running.push_back(id);
+        plan.push_back({id, n, n == r.extend_len() ? 1 : 0, 1});
+        budget -= n;
+    }
+    if (plan.empty() && s->has_work()) {
+        bool any_pending = false;
+        for (int32_t id : s->running) any_pending = any_pending || s->reqs[id].pending;
+        for (int32_t id : s->waiting) any_pending = any_pending || s->reqs[id].pending;
+        if (!any_pending) return fail(HC_OUT_OF_PAGES, "nothing can be scheduled: the cache is too small for the oldest request");
+    }
+    if (static_cast<int>(plan.size()) > cap) return fail(HC_MISUSE, "a plan of " + str(plan.size()) + " portions where " + str(cap) + " fit");
+    for (size_t k = 0; k < plan.size(); ++k) {
+        ids[k] = plan[k].id;
+        num_tokens[k] = plan[k].num_tokens;
+        samples[k] = plan[k].samples;
+        admitted[k] = plan[k].admitted;
+    }
+    *count = static_cast<int>(plan.size());
+    return HC_OK;
+}
+
+// The step of the plan has been launched: its tokens count as cached, and each portion that samples
+// leaves a pending token (`feedback_index`: its place among the step's sampled tokens, in plan order).
+void hc_sched_advance(void* sp, const int32_t* ids, const long long* num_tokens, const int32_t* samples, int n) {
+    Sched* s = sched_of(sp);
+    int k = 0;
+    for (int i = 0; i < n; ++i) {
+        Req& r = s->reqs[ids[i]];
+        r.cached_len += num_tokens[i];
+        if (samples[i]) {
+            ++r.pending;                                  // two for a moment: the step before is read after this
+            r.feedback_index = k++;
+        }
+    }
+}
+
+// The host has read the tokens of the step of the plan (one per sampling portion, in plan order): count
+// them, finish requests (a token equal to the request's end-of-sequence id, when that is >= 0, finishes it
+// and is kept; so does reaching max_new), free finished requests' pages and slots.  `kept[i]` says
+// whether token i counts: a token sampled for a request that had already finished is dropped.
+int hc_sched_deliver(void* sp, const int32_t* ids, const int32_t* samples, int n, const int32_t* tokens, int n_tokens, int32_t* kept) {
+    Sched* s = sched_of(sp);
+    int k = 0;
+    for (int i = 0; i < n; ++i) {
+        if (!samples[i]) continue;
+        if (k >= n_tokens) return fail(HC_MISUSE, "fewer tokens than portions that sample");
+        Req& r = s->reqs[ids[i]];
+        const int32_t token = tokens[k];
+        kept[k++] = 0;
+        --r.pending;
+        if (r.status == ST_FINISHED) continue;
+        kept[k - 1] = 1;
+        ++r.input_len;
+        ++r.generated;
+        if (r.eos >= 0 && token == r.eos) {
+            r.finish = FIN_EOS;
+        } else if (r.generated >= r.max_new) {
+            r.finish = FIN_LENGTH;
+        } else {
+            continue;
+        }
+        const int32_t before = r.status;
+        r.status = ST_FINISHED;
+        if (before == ST_RUNNING) {
+            s->running.erase(std::find(s->running.begin(), s->running.end(), ids[i]));
+            if (int rc = s->release_slot(r)) return rc;
+        } else {                                          // preempted while its last token was on its way
+            auto it = std::find(s->waiting.begin(), s->waiting.end(), ids[i]);
+            if (it != s->waiting.end()) s->waiting.erase(it);
+        }
+    }
+    return HC_OK;
+}
+
+// Forget an unfinished request: out of the queues, its pages and slot freed (a token of it that a
+// launched step is still sampling is dropped when it arrives).
+int hc_sched_release(void* sp, int id) {
+    Sched* s = sched_of(sp);
+    Req& r = s->reqs[id];
+    if (r.status == ST_FINISHED) return HC_OK;
+    if (r.status == ST_RUNNING) {
+        s->running.erase(std::find(s->running.begin(), s->running.end(), id));
+        if (int rc = s->release_slot(r)) return rc;
+    } else {
+        auto it = std::find(s->waiting.begin(), s->waiting.end(), id);
+        if (it != s->waiting.end()) s->waiting.erase(it);
+    }
+    r.status = ST_FINISHED;
+    r.finish = FIN_RELEASED;
     return HC_OK;
 }
 

@@ -21,7 +21,7 @@ import torch
 from ..sampling import Sampler
 from ..sampling.sampler import slot_state_row
 from .batch import StepEntry
-from .request import GenerationRequest, RequestStatus
+from .request import GenerationRequest
 from .runner import ModelRunner
 from .scheduler import ScheduledPortion, Scheduler
 
@@ -79,12 +79,7 @@ class PagedGenerateEngine:
         it that a launched step is still sampling is dropped when it arrives)."""
         req = self.request(request_id)
         if not req.finished:
-            if req in self.scheduler.running:
-                self.scheduler.running.remove(req)
-                self.runner.cache.release(req.slot)
-            elif req in self.scheduler.waiting:
-                self.scheduler.waiting.remove(req)
-            req.status, req.finish_reason = RequestStatus.FINISHED, "released"
+            self.scheduler.release(req)
         del self.scheduler.requests[request_id]
 
     # ---- stepping --------------------------------------------------------------------------

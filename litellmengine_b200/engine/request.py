@@ -9,11 +9,13 @@ so does reaching `max_new_tokens`; `max_new_tokens == 0` is finished at once.  A
 away, its tokens kept), and a request may be prefilled in portions.  `pending` counts a
 token that a launched step has sampled on the device and the host has not read yet: it is
 part of the request's length (the next step may already run it) but not of `input_ids`.
+
+The token lists and the request's facts live here; its lengths and states are the native
+scheduler's records (`csrc/host_core.cpp`), read through it.
 """
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
 from typing import List, Optional
 
 
@@ -23,23 +25,36 @@ class RequestStatus(enum.Enum):
     FINISHED = "finished"
 
 
-@dataclass(eq=False)            # a request is itself: lists of requests are searched by identity
+_STATUS = (RequestStatus.WAITING, RequestStatus.RUNNING, RequestStatus.FINISHED)
+_FINISH = (None, "eos", "length", "released")
+# field numbers of the native record
+_F_STATUS, _F_SLOT, _F_PENDING, _F_FEEDBACK, _F_PREEMPTIONS, _F_FINISH, _F_CACHED = range(7)
+
+
 class GenerationRequest:
-    request_id: int
-    input_ids: List[int]
-    prompt_len: int
-    max_new_tokens: int
-    eos_token_id: int = -1
-    temperature: float = 0.0
-    seed: int = 0
-    generated_ids: List[int] = field(default_factory=list)
-    cached_len: int = 0
-    slot: int = -1
-    status: RequestStatus = RequestStatus.WAITING
-    preemptions: int = 0
-    finish_reason: Optional[str] = None
-    pending: int = 0             # sampled tokens of this request that are still on the device (1 when a step is planned)
-    feedback_index: int = -1     # where among the last launched step's sampled tokens its token is
+    """A request is itself: lists of requests are searched by identity."""
+
+    def __init__(self, records, request_id: int, prompt: List[int], max_new_tokens: int, eos_token_id: int = -1,
+                 temperature: float = 0.0, seed: int = 0):
+        self._get = records                  # (request id, field) -> the native record's value
+        self.request_id = request_id
+        self.input_ids = prompt
+        self.prompt_len = len(prompt)
+        self.max_new_tokens = max_new_tokens
+        self.eos_token_id = eos_token_id
+        self.temperature = temperature
+        self.seed = seed
+        self.generated_ids: List[int] = []
+
+    status = property(lambda self: _STATUS[self._get(self.request_id, _F_STATUS)])
+    slot = property(lambda self: self._get(self.request_id, _F_SLOT))
+    cached_len = property(lambda self: self._get(self.request_id, _F_CACHED))
+    preemptions = property(lambda self: self._get(self.request_id, _F_PREEMPTIONS))
+    finish_reason = property(lambda self: _FINISH[self._get(self.request_id, _F_FINISH)])
+    # sampled tokens of this request that are still on the device (1 when a step is planned)
+    pending = property(lambda self: self._get(self.request_id, _F_PENDING))
+    # where among the last launched step's sampled tokens its token is
+    feedback_index = property(lambda self: self._get(self.request_id, _F_FEEDBACK))
 
     @property
     def device_len(self) -> int:
@@ -59,13 +74,6 @@ class GenerationRequest:
     def finished(self) -> bool:
         return self.status is RequestStatus.FINISHED
 
-    def append_token(self, token: int) -> None:
-        """src/engine/request_manager.cpp:122-159"""
-        if self.status is RequestStatus.FINISHED:
-            raise RuntimeError("append_token on a finished request")
-        self.input_ids.append(int(token))
-        self.generated_ids.append(int(token))
-        if self.eos_token_id >= 0 and token == self.eos_token_id:
-            self.status, self.finish_reason = RequestStatus.FINISHED, "eos"
-        elif len(self.generated_ids) >= self.max_new_tokens:
-            self.status, self.finish_reason = RequestStatus.FINISHED, "length"
+    def __repr__(self) -> str:
+        return (f"GenerationRequest({self.request_id}, {self.status.value}, prompt {self.prompt_len}, "
+                f"generated {len(self.generated_ids)}/{self.max_new_tokens}, cached {self.cached_len})")

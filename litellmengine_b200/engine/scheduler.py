@@ -1,9 +1,11 @@
 """The scheduler: which requests run in the next step, and with how many tokens.
 
 Pure host logic over the cache manager's bookkeeping, so its decisions are tested on the
-CPU.  The reference has no scheduler: it prefills each prompt whole, one request at a time,
-then decodes all unfinished requests together, and sizes the pool so that pages never run
-out (src/engine/paged_generate_engine.cpp:343-365, src/benchmark/generation_benchmark.cpp:
+CPU; the records and the decisions themselves are native code (`csrc/host_core.cpp`), this
+class gives them their names and keeps the token lists.  The reference has no scheduler: it
+prefills each prompt whole, one request at a time, then decodes all unfinished requests
+together, and sizes the pool so that pages never run out
+(src/engine/paged_generate_engine.cpp:343-365, src/benchmark/generation_benchmark.cpp:
 152-159,291-315); when they do run out it throws (src/engine/block_table_manager.cpp:82-84).
 
 Rules, in this order, every step:
@@ -27,12 +29,41 @@ to have ended with its end-of-sequence token has run one token too many, which `
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass
-from typing import Deque, Dict, List, Optional
+from typing import Dict, List, Optional
 
-from ..cache import CacheManager, OutOfPages
-from .request import GenerationRequest, RequestStatus
+import numpy as np
+
+from ..cache import CacheManager
+from ..cache.pages import _check
+from ..csrc import host
+from .request import GenerationRequest
+
+_SIGNATURES = {
+    "hc_sched_new": ([ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong], ctypes.c_void_p),
+    "hc_sched_delete": ([ctypes.c_void_p], None),
+    "hc_sched_add": ([ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int, ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "hc_sched_has_work": ([ctypes.c_void_p], ctypes.c_int),
+    "hc_sched_num_preemptions": ([ctypes.c_void_p], ctypes.c_longlong),
+    "hc_sched_queue": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int], ctypes.c_int),
+    "hc_sched_get": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_longlong),
+    "hc_sched_schedule": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                           ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "hc_sched_advance": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int], None),
+    "hc_sched_deliver": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                          ctypes.c_void_p], ctypes.c_int),
+    "hc_sched_release": ([ctypes.c_void_p, ctypes.c_int], ctypes.c_int),
+}
+
+
+def _library():
+    lib = host.lib()
+    if lib.hc_sched_new.argtypes is None:
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            f = getattr(lib, name)
+            f.argtypes, f.restype = argtypes, restype
+    return lib
 
 
 @dataclass
@@ -51,11 +82,44 @@ class Scheduler:
         self.chunk = min(chunk or max_tokens_per_step, max_tokens_per_step)
         if self.chunk <= 0:
             raise ValueError("chunk must be positive")
-        self.waiting: Deque[GenerationRequest] = deque()
-        self.running: List[GenerationRequest] = []       # in admission order
+        self._lib = _library()
+        self._h = self._lib.hc_sched_new(cache._h, max_tokens_per_step, self.chunk)
+        if not self._h:
+            raise ValueError(host.last_error())
         self.requests: Dict[int, GenerationRequest] = {}
-        self._next_id = 0
-        self.num_preemptions = 0
+        n = cache.max_slots
+        self._ids = np.empty(n, np.int32)                  # the plan the native scheduler writes
+        self._tokens = np.empty(n, np.int64)
+        self._samples = np.empty(n, np.int32)
+        self._admitted = np.empty(n, np.int32)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.hc_sched_delete(self._h)
+            self._h = None
+
+    def _record(self, request_id: int, field: int) -> int:
+        return self._lib.hc_sched_get(self._h, request_id, field)
+
+    def _queue(self, which: int) -> List[GenerationRequest]:
+        n = self._lib.hc_sched_queue(self._h, which, None, 0)
+        ids = np.empty(n, np.int32)
+        self._lib.hc_sched_queue(self._h, which, ids.ctypes.data, n)
+        return [self.requests[i] for i in ids.tolist() if i in self.requests]
+
+    @property
+    def waiting(self) -> List[GenerationRequest]:
+        """First come first served; a preempted request stands at the front.  A copy."""
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[GenerationRequest]:
+        """In admission order.  A copy."""
+        return self._queue(1)
+
+    @property
+    def num_preemptions(self) -> int:
+        return self._lib.hc_sched_num_preemptions(self._h)
 
     # ---- requests --------------------------------------------------------------------------
     def add(self, prompt_ids, max_new_tokens: int, eos_token_id: int = -1, temperature: float = 0.0,
@@ -67,129 +131,67 @@ class Scheduler:
             raise ValueError("max_new_tokens must be >= 0")
         if temperature < 0:
             raise ValueError("--temperature must be >= 0")
-        # the last sampled token is never run, so the cache holds at most prompt + new - 1
-        longest = len(prompt) + max(max_new_tokens - 1, 0)
-        if longest > self.cache.max_request_tokens:
-            raise OutOfPages(f"request needs {longest} cached tokens; the cache takes at most "
-                             f"{self.cache.max_request_tokens} per request")
-        req = GenerationRequest(self._next_id, prompt, len(prompt), max_new_tokens, eos_token_id,
+        rid = ctypes.c_int()
+        _check(self._lib.hc_sched_add(self._h, len(prompt), int(max_new_tokens), int(eos_token_id), ctypes.byref(rid)))
+        req = GenerationRequest(self._record, rid.value, prompt, int(max_new_tokens), int(eos_token_id),
                                 float(temperature), int(seed))
-        self._next_id += 1
         self.requests[req.request_id] = req
-        if max_new_tokens == 0:
-            req.status, req.finish_reason = RequestStatus.FINISHED, "length"
-        else:
-            self.waiting.append(req)
         return req
 
+    def release(self, req: GenerationRequest) -> None:
+        """Forget an unfinished request: out of the queues, its pages and slot freed (a token of it
+        that a launched step is still sampling is dropped when it arrives)."""
+        _check(self._lib.hc_sched_release(self._h, req.request_id))
+
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.hc_sched_has_work(self._h))
 
     # ---- one step --------------------------------------------------------------------------
-    def _preempt_latest(self) -> GenerationRequest:
-        victim = self.running.pop()
-        self.cache.release(victim.slot)
-        victim.slot, victim.cached_len = -1, 0
-        victim.status = RequestStatus.WAITING
-        victim.preemptions += 1
-        self.num_preemptions += 1
-        self.waiting.appendleft(victim)
-        return victim
-
     def schedule(self) -> List[ScheduledPortion]:
-        budget = self.max_tokens_per_step
-        plan: List[ScheduledPortion] = []
-        need = [0] * len(self.cache.groups)               # pages per group already promised in this step
-
-        preempted = False
-        i = 0
-        order = sorted(range(len(self.running)), key=lambda k: (self.running[k].extend_len > 1, k))
-        queue = [self.running[k] for k in order]          # decoders first, each kind oldest first
-        while i < len(queue):
-            req = queue[i]
-            if req.status is not RequestStatus.RUNNING or req.remain_len <= 0:   # preempted below, or only awaiting its last token
-                i += 1
-                continue
-            if budget <= 0:
-                break
-            n = min(req.extend_len, self.chunk, budget)
-            while True:
-                got = self.cache.reserve(need, req.slot, req.cached_len + n)
-                if got is not None:
-                    break
-                victim = self._preempt_latest()
-                preempted = True
-                plan = [p for p in plan if p.request is not victim]
-                budget = self.max_tokens_per_step - sum(p.num_tokens for p in plan)
-                need = [0] * len(self.cache.groups)
-                for p in plan:                            # the pool changed: count the promises again
-                    need = self.cache.reserve(need, p.request.slot, p.request.cached_len + p.num_tokens)
-                if victim is req:
-                    break
-            if req.status is not RequestStatus.RUNNING:
-                i += 1
-                continue
-            need = got
-            plan.append(ScheduledPortion(req, n, n == req.extend_len))
-            budget -= n
-            i += 1
-
-        # no admission in a step that had to preempt: the victim would come straight back
-        while not preempted and self.waiting and budget > 0 and self.cache.free_slots > 0:
-            req = self.waiting[0]
-            if req.remain_len <= 0:                       # preempted with its last token on its way
-                break
-            n = min(req.extend_len, self.chunk, budget)
-            got = self.cache.reserve(need, None, n)
-            if got is None:
-                break
-            need = got
-            self.waiting.popleft()
-            req.slot = self.cache.admit()
-            req.status = RequestStatus.RUNNING
-            self.running.append(req)
-            plan.append(ScheduledPortion(req, n, n == req.extend_len))
-            budget -= n
-        if not plan and self.has_work() and not any(r.pending for r in list(self.running) + list(self.waiting)):
-            raise OutOfPages("nothing can be scheduled: the cache is too small for the oldest request")
+        count = ctypes.c_int()
+        _check(self._lib.hc_sched_schedule(self._h, self._ids.ctypes.data, self._tokens.ctypes.data, self._samples.ctypes.data,
+                                           self._admitted.ctypes.data, len(self._ids), ctypes.byref(count)))
+        n = count.value
+        plan = []
+        for rid, tokens, samples, admitted in zip(self._ids[:n].tolist(), self._tokens[:n].tolist(),
+                                                  self._samples[:n].tolist(), self._admitted[:n].tolist()):
+            req = self.requests[rid]
+            if admitted:                                  # a slot taken just now: its state tensors start from zero
+                for t in self.cache.state.values():
+                    t[req.slot].zero_()
+            plan.append(ScheduledPortion(req, tokens, bool(samples)))
         return plan
+
+    def _plan_arrays(self, plan: List[ScheduledPortion]):
+        ids = np.fromiter((p.request.request_id for p in plan), np.int32, len(plan))
+        tokens = np.fromiter((p.num_tokens for p in plan), np.int64, len(plan))
+        samples = np.fromiter((p.samples for p in plan), np.int32, len(plan))
+        return ids, tokens, samples
 
     def advance(self, plan: List[ScheduledPortion]) -> None:
         """The step of `plan` has been launched: its tokens count as cached, and each portion
         that samples leaves a pending token (`feedback_index` = its place among the step's
         sampled tokens, in plan order)."""
-        k = 0
-        for p in plan:
-            req = p.request
-            req.cached_len += p.num_tokens
-            if p.samples:
-                req.pending += 1                          # two for a moment: the step before is read after this
-                req.feedback_index = k
-                k += 1
+        ids, tokens, samples = self._plan_arrays(plan)
+        self._lib.hc_sched_advance(self._h, ids.ctypes.data, tokens.ctypes.data, samples.ctypes.data, len(plan))
 
     def deliver(self, plan: List[ScheduledPortion], sampled: List[int]) -> List[tuple]:
         """The host has read the tokens of the step of `plan` (one per portion with `samples`, in
         plan order): append them, free finished requests' pages and slots.  Returns
         [(request, token)] of the tokens that count; a token sampled for a request that had
         already finished (end of sequence found one step late, or released) is dropped."""
-        it = iter(sampled)
+        ids, _, samples = self._plan_arrays(plan)
+        toks = np.ascontiguousarray(sampled, dtype=np.int32)
+        kept = np.zeros(len(toks), np.int32)
+        _check(self._lib.hc_sched_deliver(self._h, ids.ctypes.data, samples.ctypes.data, len(plan), toks.ctypes.data, len(toks),
+                                          kept.ctypes.data))
         out = []
-        for p in plan:
-            if not p.samples:
-                continue
-            req, token = p.request, next(it)
-            req.pending -= 1
-            if req.finished:
-                continue
-            req.append_token(token)
-            out.append((req, token))
-            if req.finished:
-                if req in self.running:
-                    self.running.remove(req)
-                    self.cache.release(req.slot)
-                    req.slot = -1
-                elif req in self.waiting:                 # preempted while its last token was on its way
-                    self.waiting.remove(req)
+        owners = [p.request for p in plan if p.samples]
+        for req, token, keep in zip(owners, toks.tolist(), kept.tolist()):
+            if keep:
+                req.input_ids.append(token)
+                req.generated_ids.append(token)
+                out.append((req, token))
         return out
 
     def update(self, plan: List[ScheduledPortion], sampled: List[int]) -> List[GenerationRequest]:
