@@ -1,4 +1,5 @@
-"""ctypes access to the native host code (`host_core.cpp`): the records of the cache manager.
+"""ctypes access to the native host code (`host_core.cpp`): the records of the cache manager and the
+packing of a step (the scheduler declares its own functions).
 
 Needs no GPU.  The library is compiled in-tree on first use like the kernels' (by nvcc as plain
 C++); a failed call raises what the Python classes document: `OutOfPages` for "nothing was taken",
@@ -41,6 +42,8 @@ _SIGNATURES = {
     "hc_cache_pending": ([c_void_p, c_int], c_int),
     "hc_cache_drain": ([c_void_p, c_int, c_void_p, c_void_p], None),
     "hc_cache_check": ([c_void_p], c_int),
+    "hc_pack_step": ([c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_void_p], c_int),
 }
 
 

@@ -1,5 +1,5 @@
 // The host side's bookkeeping, native: page pools, block tables and request slots of the cache
-// manager, and the scheduler's records and decisions.  Plain C++ behind a C interface (called through
+// manager, the scheduler's records and decisions, and the packing of a step's arrays.  Plain C++ behind a C interface (called through
 // ctypes like the kernels); it touches no device and runs on a machine without one.  The Python
 // classes of `cache/pages.py` and `engine/scheduler.py` own the device tensors and the token lists
 // and present these records under their documented names; the rules are the ones stated there and
@@ -627,6 +627,62 @@ int hc_sched_release(void* sp, int id) {
     }
     r.status = ST_FINISHED;
     r.finish = FIN_RELEASED;
+    return HC_OK;
+}
+
+// ---- packing a step -----------------------------------------------------------------------------------------
+// The arrays every kernel of a step reads, written into the step's pinned buffer (`base`, int32) at the
+// offsets the buffer's layout gives: per token its id, its absolute position and its entry; per entry its
+// slot, first row, number of rows and cached length after the step; the rows whose logits are wanted
+// (padded with row 0 up to `want_cap`, for a graph that reads that many) and their slots; counts
+// {tokens, entries, wanted}.  A token id that is still on the device is written as -1 - (its index among
+// the previous step's sampled tokens).  offsets: token_ids, positions, token_entry, entry_slot,
+// entry_q_start, entry_q_len, entry_kv_len, want_rows, want_slot, counts.
+// facts (out): tokens, wanted rows, longest portion, longest cached length.
+int hc_pack_step(int32_t* base, const long long* offsets, int num_entries, const int32_t* slot, const long long* past,
+                 const long long* q_len, const int32_t* feedback, const long long* tokens, const long long* want,
+                 const int32_t* want_count, int want_cap, long long* facts) {
+    int32_t* token_ids = base + offsets[0];
+    int32_t* positions = base + offsets[1];
+    int32_t* token_entry = base + offsets[2];
+    int32_t* entry_slot = base + offsets[3];
+    int32_t* entry_q_start = base + offsets[4];
+    int32_t* entry_q_len = base + offsets[5];
+    int32_t* entry_kv_len = base + offsets[6];
+    int32_t* want_rows = base + offsets[7];
+    int32_t* want_slot = base + offsets[8];
+    int32_t* counts = base + offsets[9];
+    long long t = 0, w = 0, wi = 0, max_q = 0, max_kv = 0;
+    for (int e = 0; e < num_entries; ++e) {
+        const long long n = q_len[e];
+        entry_slot[e] = slot[e];
+        entry_q_start[e] = static_cast<int32_t>(t);
+        entry_q_len[e] = static_cast<int32_t>(n);
+        entry_kv_len[e] = static_cast<int32_t>(past[e] + n);
+        max_q = std::max(max_q, n);
+        max_kv = std::max(max_kv, past[e] + n);
+        for (long long i = 0; i < n; ++i) {
+            token_ids[t + i] = static_cast<int32_t>(tokens[t + i]);
+            positions[t + i] = static_cast<int32_t>(past[e] + i);
+            token_entry[t + i] = e;
+        }
+        if (feedback[e] >= 0) token_ids[t + n - 1] = -1 - feedback[e];
+        for (int k = 0; k < want_count[e]; ++k) {
+            const long long j = want[wi++];
+            if (j < 0 || j >= n) return fail(HC_MISUSE, "want=" + str(j) + " is outside the entry's " + str(n) + " tokens");
+            want_rows[w] = static_cast<int32_t>(t + j);
+            want_slot[w++] = slot[e];
+        }
+        t += n;
+    }
+    for (long long k = w; k < want_cap; ++k) want_rows[k] = 0;
+    counts[0] = static_cast<int32_t>(t);
+    counts[1] = num_entries;
+    counts[2] = static_cast<int32_t>(w);
+    facts[0] = t;
+    facts[1] = w;
+    facts[2] = max_q;
+    facts[3] = max_kv;
     return HC_OK;
 }
 

@@ -20,7 +20,12 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..csrc import host
 from ..parts.context import StepFacts, StepPrelude
+
+# the sections the native packing writes, in the order it takes their offsets
+_PACKED = ("token_ids", "positions", "token_entry", "entry_slot", "entry_q_start", "entry_q_len", "entry_kv_len",
+           "want_rows", "want_slot", "counts")
 
 
 @dataclass
@@ -56,6 +61,7 @@ class _Region:
             self.off[name] = (off, n)
             off += n
         self.size = off
+        self.packed_offsets = np.asarray([self.off[name][0] for name in _PACKED], dtype=np.int64)
         self.pinned = torch.zeros(off, dtype=torch.int32, pin_memory=True)
         self.host = self.pinned.numpy()
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
@@ -167,38 +173,26 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
     region.wait_reusable()
     hv = region.host_view
     past = np.fromiter((e.past for e in entries), dtype=np.int64, count=B)
-    slot = np.fromiter((e.slot for e in entries), dtype=np.int64, count=B)
-    q_start = np.cumsum(q_len) - q_len
-    tok = hv("token_ids")
+    slot = np.fromiter((e.slot for e in entries), dtype=np.int32, count=B)
+    fed = np.fromiter((e.feedback for e in entries), dtype=np.int32, count=B)
     if T == B:                                                    # single tokens only: no lists to join
-        tok[:T] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=B)
-        ent = np.arange(B)
-        hv("positions")[:T] = past
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=B)
     else:
-        tok[:T] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-        ent = np.repeat(np.arange(B), q_len)
-        hv("positions")[:T] = np.arange(T) - np.repeat(q_start - past, q_len)
-    hv("token_entry")[:T] = ent
-    w = 0
-    wr, ws = hv("want_rows"), hv("want_slot")
-    for i, e in enumerate(entries):
-        n = int(q_len[i])
-        if e.feedback >= 0:
-            tok[int(q_start[i]) + n - 1] = -1 - e.feedback
-        for j in e.want:
-            if not 0 <= j < n:
-                raise ValueError(f"want={j} is outside the entry's {n} tokens")
-            wr[w], ws[w] = int(q_start[i]) + j, e.slot
-            w += 1
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+    want_count = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=B)
+    want = np.fromiter((j for e in entries for j in e.want), dtype=np.int64, count=int(want_count.sum()))
     want_cap = min(buffers.max_entries, region.token_cap)
-    if w < want_cap:
-        wr[w:want_cap] = 0                                        # padding for a graph that reads `want_cap` rows
-    hv("entry_slot")[:B] = slot
-    hv("entry_q_start")[:B] = q_start
-    hv("entry_q_len")[:B] = q_len
-    hv("entry_kv_len")[:B] = past + q_len
+    if len(want) > region.token_cap:
+        raise ValueError(f"{len(want)} wanted rows in a step of {T} tokens")
+    facts4 = np.empty(4, dtype=np.int64)
+    # token ids, positions, entries, wanted rows (padded to `want_cap` for a graph that reads that many), counts
+    if host.lib().hc_pack_step(region.host.ctypes.data, region.packed_offsets.ctypes.data, B, slot.ctypes.data, past.ctypes.data,
+                               q_len.ctypes.data, fed.ctypes.data, tokens.ctypes.data, want.ctypes.data,
+                               want_count.ctypes.data, want_cap, facts4.ctypes.data):
+        raise ValueError(host.last_error())
+    w, max_q_len, max_kv_len = int(facts4[1]), int(facts4[2]), int(facts4[3])
+    q_start = np.cumsum(q_len) - q_len
     counts = hv("counts")
-    counts[0], counts[1], counts[2] = T, B, w
     facts = StepFacts(q_start=q_start, q_len=q_len, past=past, slot=slot, num_tokens=T)
     filled = [(p, p.fill(facts, {k: hv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}))
               for p in buffers.preludes]
@@ -223,8 +217,8 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         token_ids=dv("token_ids", T), positions=dv("positions", T), token_entry=dv("token_entry", T),
         entry_slot=dv("entry_slot", B), entry_q_start=dv("entry_q_start", B), entry_q_len=dv("entry_q_len", B),
         entry_kv_len=dv("entry_kv_len", B), want_rows=dv("want_rows", w), want_slot=dv("want_slot", w),
-        status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=int(q_len.max()),
-        max_kv_len=int((past + q_len).max()), entries=entries, feedback=feedback,
+        status=buffers.status, num_tokens=T, num_entries=B, num_want=w, max_q_len=max_q_len,
+        max_kv_len=max_kv_len, entries=entries, feedback=feedback,
         layout="small" if region is buffers.small else "large", want_cap=want_cap)
     batch.state_ranges = ranges
     for p, got in filled:
