@@ -317,6 +317,22 @@ class CacheManager:
         _check(self._lib.hc_cache_commit(self._h, int(slot), int(new_len), ctypes.byref(given)))
         return given.value
 
+    # ---- a step's requests at once (what the step function calls) ---------------------------
+    def lengths(self, slots: np.ndarray) -> np.ndarray:
+        """int64 lengths of the requests in `slots` (int32)."""
+        out = np.empty(len(slots), dtype=np.int64)
+        _check(self._lib.hc_cache_lengths(self._h, len(slots), slots.ctypes.data, out.ctypes.data))
+        return out
+
+    def ensure_all(self, slots: np.ndarray, new_lens: np.ndarray) -> None:
+        """`ensure` for every (slot, new length) of a step together, or take nothing."""
+        _check(self._lib.hc_cache_ensure_all(self._h, len(slots), slots.ctypes.data, new_lens.ctypes.data))
+
+    def commit_all(self, slots: np.ndarray, new_lens: np.ndarray) -> int:
+        given = ctypes.c_int()
+        _check(self._lib.hc_cache_commit_all(self._h, len(slots), slots.ctypes.data, new_lens.ctypes.data, ctypes.byref(given)))
+        return given.value
+
     def drain_updates(self) -> List[Tuple[np.ndarray, np.ndarray]]:
         """Per group: (flat table indices, page ids) changed since the last call."""
         out = []

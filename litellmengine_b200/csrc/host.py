@@ -42,6 +42,9 @@ _SIGNATURES = {
     "hc_cache_pending": ([c_void_p, c_int], c_int),
     "hc_cache_drain": ([c_void_p, c_int, c_void_p, c_void_p], None),
     "hc_cache_check": ([c_void_p], c_int),
+    "hc_cache_lengths": ([c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "hc_cache_ensure_all": ([c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "hc_cache_commit_all": ([c_void_p, c_int, c_void_p, c_void_p, POINTER(c_int)], c_int),
     "hc_pack_step": ([c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_void_p], c_int),
 }

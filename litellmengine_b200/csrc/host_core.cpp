@@ -416,6 +416,50 @@ int hc_cache_check(void* cp) {
     return HC_OK;
 }
 
+// ---- a step's entries at once ------------------------------------------------------------------------------
+int hc_cache_lengths(void* cp, int n, const int32_t* slots, long long* out) {
+    Cache* c = cache_of(cp);
+    for (int i = 0; i < n; ++i) {
+        if (int rc = c->check_live(slots[i])) return rc;
+        out[i] = c->length[slots[i]];
+    }
+    return HC_OK;
+}
+
+// Room for positions [0, lens[i]) of every listed request, or nothing is taken.
+int hc_cache_ensure_all(void* cp, int n, const int32_t* slots, const long long* lens) {
+    Cache* c = cache_of(cp);
+    std::vector<long long> need(c->groups.size(), 0);
+    for (int i = 0; i < n; ++i) {
+        if (int rc = c->check_live(slots[i])) return rc;
+        if (lens[i] < c->length[slots[i]]) return fail(HC_MISUSE, "a request's cache never shrinks");
+        if (lens[i] > c->max_request_tokens)
+            return fail(HC_OUT_OF_PAGES, "a request of " + str(lens[i]) + " tokens exceeds the limit of " + str(c->max_request_tokens));
+        for (size_t g = 0; g < c->groups.size(); ++g) {
+            const Group& gr = c->groups[g];
+            if (gr.pages_for(lens[i]) > gr.max_pages)
+                return fail(HC_MISUSE, "a request of " + str(lens[i]) + " tokens needs " + str(gr.pages_for(lens[i])) + " pages; the table holds " + str(gr.max_pages));
+            need[g] += gr.missing(slots[i], lens[i]);
+        }
+    }
+    for (size_t g = 0; g < c->groups.size(); ++g)
+        if (need[g] > c->groups[g].pool.free_count()) return fail(HC_OUT_OF_PAGES, "the step's tokens do not fit the free pages");
+    for (int i = 0; i < n; ++i)
+        for (Group& g : c->groups)
+            if (int rc = g.append(slots[i], lens[i])) return rc;
+    return HC_OK;
+}
+
+int hc_cache_commit_all(void* cp, int n, const int32_t* slots, const long long* lens, int* given) {
+    *given = 0;
+    for (int i = 0; i < n; ++i) {
+        int one = 0;
+        if (int rc = hc_cache_commit(cp, slots[i], lens[i], &one)) return rc;
+        *given += one;
+    }
+    return HC_OK;
+}
+
 // ---- the scheduler ----------------------------------------------------------------------------------------
 // Rules, every step: (1) running requests that decode go first, oldest admission first; (2) running
 // requests still reading their prompt get a portion of at most `chunk` tokens within what is left of
@@ -491,7 +535,10 @@ long long hc_sched_get(void* sp, int id, int field) {
 
 // The next step: up to `cap` portions (request id, tokens, whether a token is sampled at its end, whether
 // the request was admitted just now: its slot's state is the caller's to clear).
-int hc_sched_schedule(void* sp, int32_t* ids, long long* num_tokens, int32_t* samples, int32_t* admitted, int cap, int* count) {
+// `facts`: per portion {slot, tokens already cached, tokens known to the host, feedback index}, what the
+// caller needs to build the step's entry without asking for each.
+int hc_sched_schedule(void* sp, int32_t* ids, long long* num_tokens, int32_t* samples, int32_t* admitted, long long* facts, int cap,
+                      int* count) {
     Sched* s = sched_of(sp);
     Cache* c = s->cache;
     long long budget = s->max_tokens;
@@ -554,6 +601,11 @@ int hc_sched_schedule(void* sp, int32_t* ids, long long* num_tokens, int32_t* sa
         num_tokens[k] = plan[k].num_tokens;
         samples[k] = plan[k].samples;
         admitted[k] = plan[k].admitted;
+        const Req& r = s->reqs[plan[k].id];
+        facts[4 * k] = r.slot;
+        facts[4 * k + 1] = r.cached_len;
+        facts[4 * k + 2] = r.input_len;
+        facts[4 * k + 3] = r.feedback_index;
     }
     *count = static_cast<int>(plan.size());
     return HC_OK;

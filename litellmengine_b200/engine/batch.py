@@ -152,17 +152,50 @@ class StepBatch:
     # what a part computes on the device in the first layer that needs it and shares with the layers
     # after it (emptied before a step is captured as a graph, so that the graph holds the kernel)
     tables: Dict[object, object] = field(default_factory=dict)
+    entry_slots: Optional[np.ndarray] = None                    # host copies for the cache manager: int32 [B] slots,
+    entry_new_len: Optional[np.ndarray] = None                  # int64 [B] each request's length after this step
+
+
+@dataclass
+class EntryArrays:
+    """A step's entries as arrays, made once: what the checks, the cache manager and the packing read."""
+    q_len: np.ndarray                # int64 [B] tokens each entry brings
+    slot: np.ndarray                 # int32 [B]
+    fed: np.ndarray                  # int32 [B] `StepEntry.feedback`
+    tokens: np.ndarray               # int64 [T] all entries' tokens, joined
+    want: np.ndarray                 # int64 all entries' wanted places, joined
+    want_count: np.ndarray           # int32 [B]
+    past: Optional[np.ndarray] = None    # int64 [B], when the cache manager has been asked
+
+    @staticmethod
+    def of(entries: Sequence[StepEntry]) -> "EntryArrays":
+        B = len(entries)
+        q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        if int(q_len.sum()) == B:                                 # single tokens only: no lists to join
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=B)
+        elif B:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        else:
+            tokens = np.empty(0, np.int64)
+        want_count = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=B)
+        return EntryArrays(
+            q_len=q_len, slot=np.fromiter((e.slot for e in entries), dtype=np.int32, count=B),
+            fed=np.fromiter((e.feedback for e in entries), dtype=np.int32, count=B), tokens=tokens,
+            want=np.fromiter((j for e in entries for j in e.want), dtype=np.int64, count=int(want_count.sum())),
+            want_count=want_count)
 
 
 def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
-              feedback: Optional[torch.Tensor] = None, state_writes=()) -> StepBatch:
+              feedback: Optional[torch.Tensor] = None, state_writes=(), arrays: Optional[EntryArrays] = None) -> StepBatch:
     """Fill the pinned buffer from `entries` (whose `past` is set) and the cache manager's
     pending table `updates`, let every prelude fill its share, start the copy, and return the
     device views.  `state_writes`: [(flat indices, int32 values)] to be written into per-request
     state tensors by the step function after the copy (they ride in the same buffer; at most
     8 values per entry in all); their places in the buffer come back in `batch.state_ranges`."""
     B = len(entries)
-    q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+    a = arrays if arrays is not None else EntryArrays.of(entries)
+    q_len, slot, fed, tokens, want, want_count = a.q_len, a.slot, a.fed, a.tokens, a.want, a.want_count
+    past = a.past if a.past is not None else np.fromiter((e.past for e in entries), dtype=np.int64, count=B)
     T = int(q_len.sum())
     if T > buffers.max_tokens or B > buffers.max_entries:
         raise ValueError(f"a step of {T} tokens in {B} entries exceeds the limits "
@@ -172,15 +205,6 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
     buffers.last = region
     region.wait_reusable()
     hv = region.host_view
-    past = np.fromiter((e.past for e in entries), dtype=np.int64, count=B)
-    slot = np.fromiter((e.slot for e in entries), dtype=np.int32, count=B)
-    fed = np.fromiter((e.feedback for e in entries), dtype=np.int32, count=B)
-    if T == B:                                                    # single tokens only: no lists to join
-        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=B)
-    else:
-        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-    want_count = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=B)
-    want = np.fromiter((j for e in entries for j in e.want), dtype=np.int64, count=int(want_count.sum()))
     want_cap = min(buffers.max_entries, region.token_cap)
     if len(want) > region.token_cap:
         raise ValueError(f"{len(want)} wanted rows in a step of {T} tokens")
@@ -221,6 +245,7 @@ def pack_step(buffers: StepBuffers, entries: List[StepEntry], updates,
         max_kv_len=max_kv_len, entries=entries, feedback=feedback,
         layout="small" if region is buffers.small else "large", want_cap=want_cap)
     batch.state_ranges = ranges
+    batch.entry_slots, batch.entry_new_len = slot, past + q_len
     for p, got in filled:
         batch.preludes[p.name] = p.views({k: dv(f"{p.name}:{k}") for k in region.prelude_keys[p.name]}, got)
     return batch

@@ -88,17 +88,17 @@ class PagedGenerateEngine:
         sampling into `runner.sampled`, and the start of the copy of the sampled tokens."""
         entries, samplers, admitted = [], [], []
         for p in plan:
-            req = p.request
-            if req.cached_len == 0:           # first portion since admission: bind its random stream (in this step's upload)
-                admitted.append(("sampler", req.slot, slot_state_row(req.seed, len(req.generated_ids) + req.pending,
-                                                                     req.temperature)))
-            end = req.cached_len + p.num_tokens
-            toks = req.input_ids[req.cached_len:end]
+            req, known = p.request, len(p.request.input_ids)
+            if p.cached_len == 0:             # first portion since admission: bind its random stream (in this step's upload)
+                admitted.append(("sampler", p.slot, slot_state_row(req.seed, len(req.generated_ids) + req.pending,
+                                                                   req.temperature)))
+            end = p.cached_len + p.num_tokens
+            toks = req.input_ids[p.cached_len:end]
             feedback = -1
-            if end > len(req.input_ids):      # the portion ends with the token that is still on the device
+            if end > known:                   # the portion ends with the token that is still on the device
                 toks = toks + [0]
-                feedback = req.feedback_index
-            entries.append(StepEntry(req.slot, toks, [p.num_tokens - 1] if p.samples else [], feedback=feedback))
+                feedback = p.feedback_index
+            entries.append(StepEntry(p.slot, toks, [p.num_tokens - 1] if p.samples else [], feedback=feedback))
             if p.samples:
                 samplers.append(req)
         batch = self.runner.prepare(entries, state_writes=admitted)

@@ -14,7 +14,7 @@ from ..config import load_config
 from ..csrc import ops
 from ..parts.model import Model
 from ..weights import RandomSource, SafetensorsSource, WeightSource
-from .batch import StepBatch, StepBuffers, StepEntry, pack_step
+from .batch import EntryArrays, StepBatch, StepBuffers, StepEntry, pack_step
 
 STATUS_TEXT = {1: "a token id outside the vocabulary reached the embedding kernel",
                2: "a block-table update pointed outside the table",
@@ -128,29 +128,31 @@ class ModelRunner:
         entries = list(entries)
         if not entries:
             raise ValueError("a step needs at least one entry")
-        V, seen = self.plan.vocab_size, set()
-        for e in entries:
-            if e.slot in seen:
-                raise ValueError(f"slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            if len(e.tokens) == 0:
-                raise ValueError("an entry needs at least one token")
-            known = e.tokens if e.feedback < 0 else e.tokens[:-1]     # the last one may still be on the device
-            if len(known):
-                ids = np.asarray(known, dtype=np.int64)
-                if int(ids.min()) < 0 or int(ids.max()) >= V:
-                    bad = int(ids[(ids < 0) | (ids >= V)][0])
-                    raise ValueError(f"token id {bad} is outside the vocabulary [0, {V})")
-            if e.feedback >= self.sampled.numel():
-                raise ValueError(f"feedback index {e.feedback} is outside the {self.sampled.numel()} sampled tokens")
-            e.past = self.cache.length(e.slot)
-            if e.past + len(e.tokens) > self.plan.max_position:
-                raise ValueError(f"position {e.past + len(e.tokens) - 1} exceeds max_position_embeddings "
-                                 f"{self.plan.max_position}")
-        if not self.cache.can_hold([(e.slot, e.past + len(e.tokens)) for e in entries]):
-            raise OutOfPages("the step's tokens do not fit the free pages")
-        for e in entries:
-            self.cache.ensure(e.slot, e.past + len(e.tokens))
+        a = EntryArrays.of(entries)
+        V, B = self.plan.vocab_size, len(entries)
+        if len(np.unique(a.slot)) != B:
+            twice = next(s for i, s in enumerate(a.slot.tolist()) if s in a.slot[:i])
+            raise ValueError(f"slot {twice} appears twice in one step")
+        if int(a.q_len.min()) == 0:
+            raise ValueError("an entry needs at least one token")
+        if int(a.fed.max()) >= self.sampled.numel():
+            raise ValueError(f"feedback index {int(a.fed.max())} is outside the {self.sampled.numel()} sampled tokens")
+        known = a.tokens
+        if int(a.fed.max()) >= 0:                                 # an entry's last token may still be on the device
+            known = np.delete(known, (np.cumsum(a.q_len) - 1)[a.fed >= 0])
+        if len(known) and (int(known.min()) < 0 or int(known.max()) >= V):
+            bad = int(known[(known < 0) | (known >= V)][0])
+            raise ValueError(f"token id {bad} is outside the vocabulary [0, {V})")
+        a.past = self.cache.lengths(a.slot)
+        new_len = a.past + a.q_len
+        if int(new_len.max()) > self.plan.max_position:
+            raise ValueError(f"position {int(new_len.max()) - 1} exceeds max_position_embeddings {self.plan.max_position}")
+        for e, p in zip(entries, a.past.tolist()):
+            e.past = p
+        try:
+            self.cache.ensure_all(a.slot, new_len)                # for all of them, or nothing is taken
+        except OutOfPages as err:
+            raise OutOfPages(f"the step's tokens do not fit the free pages ({err})") from None
         writes = []
         for name, slot, values in state_writes:
             t = self.cache.state[name]
@@ -158,7 +160,8 @@ class ModelRunner:
                 raise ValueError(f"state {name!r} wants {t[0].numel()} int32 values per request")
             base = slot * t[0].numel()
             writes.append((np.arange(base, base + len(values), dtype=np.int64), np.asarray(values, dtype=np.int64)))
-        batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled, state_writes=writes)
+        batch = pack_step(self.buffers, entries, self.cache.drain_updates(), feedback=self.sampled, state_writes=writes,
+                          arrays=a)
         region = self.buffers.last                              # where pack_step put this step
         counts = region.dev_view("counts")
         for (name, _, _), (at, n) in zip(state_writes, batch.state_ranges):
@@ -175,8 +178,7 @@ class ModelRunner:
         return batch
 
     def finish(self, batch: StepBatch) -> None:
-        for e in batch.entries:
-            self.cache.commit(e.slot, e.past + len(e.tokens))
+        self.cache.commit_all(batch.entry_slots, batch.entry_new_len)
         self.steps_run += 1
 
     def forward(self, batch: StepBatch) -> torch.Tensor:

@@ -48,8 +48,8 @@ _SIGNATURES = {
     "hc_sched_num_preemptions": ([ctypes.c_void_p], ctypes.c_longlong),
     "hc_sched_queue": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int], ctypes.c_int),
     "hc_sched_get": ([ctypes.c_void_p, ctypes.c_int, ctypes.c_int], ctypes.c_longlong),
-    "hc_sched_schedule": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
-                           ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
+    "hc_sched_schedule": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                           ctypes.c_int, ctypes.POINTER(ctypes.c_int)], ctypes.c_int),
     "hc_sched_advance": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int], None),
     "hc_sched_deliver": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                           ctypes.c_void_p], ctypes.c_int),
@@ -71,6 +71,10 @@ class ScheduledPortion:
     request: GenerationRequest
     num_tokens: int
     samples: bool          # the portion ends at the request's last token, so a token is sampled
+    # the request's records when the plan was made (what the step's entry is built from)
+    slot: int = -1
+    cached_len: int = 0
+    feedback_index: int = -1
 
 
 class Scheduler:
@@ -92,6 +96,7 @@ class Scheduler:
         self._tokens = np.empty(n, np.int64)
         self._samples = np.empty(n, np.int32)
         self._admitted = np.empty(n, np.int32)
+        self._facts = np.empty((n, 4), np.int64)
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -150,16 +155,16 @@ class Scheduler:
     def schedule(self) -> List[ScheduledPortion]:
         count = ctypes.c_int()
         _check(self._lib.hc_sched_schedule(self._h, self._ids.ctypes.data, self._tokens.ctypes.data, self._samples.ctypes.data,
-                                           self._admitted.ctypes.data, len(self._ids), ctypes.byref(count)))
+                                           self._admitted.ctypes.data, self._facts.ctypes.data, len(self._ids), ctypes.byref(count)))
         n = count.value
         plan = []
-        for rid, tokens, samples, admitted in zip(self._ids[:n].tolist(), self._tokens[:n].tolist(),
-                                                  self._samples[:n].tolist(), self._admitted[:n].tolist()):
-            req = self.requests[rid]
+        for rid, tokens, samples, admitted, (slot, cached, _, fed) in zip(
+                self._ids[:n].tolist(), self._tokens[:n].tolist(), self._samples[:n].tolist(), self._admitted[:n].tolist(),
+                self._facts[:n].tolist()):
             if admitted:                                  # a slot taken just now: its state tensors start from zero
                 for t in self.cache.state.values():
-                    t[req.slot].zero_()
-            plan.append(ScheduledPortion(req, tokens, bool(samples)))
+                    t[slot].zero_()
+            plan.append(ScheduledPortion(self.requests[rid], tokens, bool(samples), slot, cached, fed))
         return plan
 
     def _plan_arrays(self, plan: List[ScheduledPortion]):
