@@ -1,9 +1,9 @@
 // The host side's bookkeeping, native: page pools, block tables and request slots of the cache
-// manager, the scheduler's records and decisions, and the packing of a step's arrays.  Plain C++ behind a C interface (called through
-// ctypes like the kernels); it touches no device and runs on a machine without one.  The Python
-// classes of `cache/pages.py` and `engine/scheduler.py` own the device tensors and the token lists
-// and present these records under their documented names; the rules are the ones stated there and
-// are pinned by the CPU tests.
+// manager, the scheduler's records and decisions, and the packing of a step's arrays.  Plain C++
+// behind a C interface (called through ctypes like the kernels); it touches no device and runs on a
+// machine without one.  The Python classes of `cache/pages.py`, `engine/scheduler.py` and
+// `engine/batch.py` own the device tensors and the token lists and present these records under their
+// documented names; the rules are the ones stated there and are pinned by the CPU tests.
 //
 // What is kept from the reference's block table manager (src/engine/block_table_manager.cpp:17-275):
 // a last-in first-out free list that hands out 0, 1, 2, ... first (213-253), all-or-nothing `ensure`
