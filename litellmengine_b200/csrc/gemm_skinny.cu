@@ -23,14 +23,15 @@
 #include <unordered_map>
 
 #define GS_ROWS 64          // output features per CTA (16 per warp)
-// k-values per stage and stages, by token tile: two CTAs per SM must fit.  Three stages of weights of
+// k-values per stage and stages, by token tile: two CTAs per SM must fit.  Three stages of weights (two
+// for the 32-token tile, which only small, latency-bound products take) of
 // 256 k-values (512 contiguous bytes of each weight row per request, which the memory system serves
 // better than 256: 6.2 against 5.9 TB/s on the output head).  The tokens' rows of a stage come from L2:
 // up to 8 tokens they are fetched two stages ahead like the weights; 16 tokens have room for two
 // stages of rows only and fetch one stage ahead (five stages of 128 k-values, the layout before, paid
 // a barrier round per 16 KB of weights: 39.4 us on a 24,576 x 4,096 product where this takes 36).
 #define GS_BK_FOR(MT) 256
-#define GS_STAGES_FOR(MT) 3
+#define GS_STAGES_FOR(MT) ((MT) <= 16 ? 3 : 2)
 #define GS_XSTAGES_FOR(MT) ((MT) <= 8 ? 3 : 2)
 #define GS_THREADS 128
 
@@ -252,7 +253,7 @@ __global__ void linear_skinny_sum_kernel(const float* __restrict__ partial, TO* 
 }
 
 extern "C" int llm_linear_skinny_supported(int M, int N, int K) {
-    return M >= 1 && M <= 16 && N >= 1 && K >= 8 && (K % 8) == 0;
+    return M >= 1 && M <= 32 && N >= 1 && K >= 8 && (K % 8) == 0;
 }
 
 static int g_skinny_slots = 0;     // CTAs the current device holds at once (two per SM), found at the first call
@@ -298,6 +299,20 @@ static void skinny_plan(int N, int K, int bk, int* ctas, int* slices, int* per_t
     *ctas = static_cast<int>(g);
     *slices = s;
     *per_tile = 0;
+}
+
+// Whether a product is small in the sense above: fewer items than would give every CTA slot four.  Such
+// products take this kernel up to 32 tokens: measured alone its 32-token tile is no faster than the
+// library's kernels (6.9 against 5.4 us on 4,096 x 1,024), but inside a step it starts fetching weights
+// while the kernel before it drains and hands its k-splits to the kernel after it (a decode step of the
+// 0.6B shape at batch 32: 1.27 ms against 1.48).  On large products the 32-token tile loses (45.6 against
+// 35.7 us on 24,576 x 4,096) and the library stays.
+extern "C" int llm_linear_skinny_small(int N, int K) {
+    if (!skinny_device()) return 0;
+    int ctas, slices, per_tile;
+    skinny_plan(N, K, GS_BK_FOR(8), &ctas, &slices, &per_tile);
+    const long long tiles = (N + GS_ROWS - 1) / GS_ROWS, nk = (K + GS_BK_FOR(8) - 1) / GS_BK_FOR(8);
+    return per_tile == 0 && tiles * nk < 4LL * g_skinny_slots ? 1 : 0;   // the plan took the two-items rule
 }
 
 // Floats of scratch a call needs for its partial sums.
@@ -401,8 +416,11 @@ extern "C" int llm_linear_skinny_boxes(const void* x, const void* w, void* y, in
     if (M <= 8)
         return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
                                        : launch_skinny_tiled<8, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
-    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
-                                   : launch_skinny_tiled<16, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    if (M <= 16)
+        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                       : launch_skinny_tiled<16, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<32, float, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                   : launch_skinny_tiled<32, bf16, true>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 
 extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void* y, int out_dtype, float* scratch,
@@ -417,7 +435,10 @@ extern "C" int llm_linear_skinny_tiled(const void* x, const void* w_tiled, void*
     if (M <= 8)
         return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<8, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
                                        : launch_skinny_tiled<8, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
-    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
-                                   : launch_skinny_tiled<16, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    if (M <= 16)
+        return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<16, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                       : launch_skinny_tiled<16, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
+    return out_dtype == LLM_DT_F32 ? launch_skinny_tiled<32, float, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s)
+                                   : launch_skinny_tiled<32, bf16, false>(xp, wp, y, scratch, scratch_floats, M, N, K, keep_partials, status, s);
 }
 

@@ -530,6 +530,18 @@ def skinny_scratch(device, floats: int) -> Optional[torch.Tensor]:
 
 
 SKINNY_MAX_ROWS = 16     # rows up to which `linear` takes the engine's own streaming kernel
+SKINNY_SMALL_MAX_ROWS = 32    # and for small (latency-bound) products, see `skinny_small`
+_skinny_small: Dict[tuple, bool] = {}
+
+
+def skinny_small(n: int, k: int) -> bool:
+    """Whether an [n, k] product has fewer items than would give every CTA slot of the streaming kernel
+    four: then latency bounds it, not bytes, and the kernel takes it up to 32 rows."""
+    got = _skinny_small.get((n, k))
+    if got is None:
+        got = _skinny_small[(n, k)] = bool(_fn("gemm_skinny", "llm_linear_skinny_small", [c_int, c_int])(n, k))
+    return got
+
 
 
 # ---- weights stored tile by tile for the streaming product ----------------------------------
@@ -614,7 +626,7 @@ def streaming_generation() -> int:
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                   out: Optional[torch.Tensor] = None, partials_ok: bool = False):
-    """x [M <= 16, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16
+    """x [M <= 32, K] @ weight[N, K]^T with the engine's own weight-streaming kernel (bfloat16
     operands, float32 accumulation, float32 or bfloat16 result).  With `partials_ok` a product
     that is cut into k-splits comes back as a `PartialSum` instead of being added up."""
     _dev(x, weight, out)
@@ -747,7 +759,8 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.d
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            partials_ok: bool = False):
-    """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps) go through the engine's
+    """x [T, K] @ weight[N, K]^T.  Up to 16 bfloat16 rows (decode steps; up to 32 for the small products
+    of small models) go through the engine's
     own weight-streaming kernel: alone it is level with the library for N = 4096..24576 and
     faster for K = 12288 (32 us against 36) and N = 151936 (203 against 218), and in a step it
     starts fetching weights while the kernel before it drains (a whole decode step of the
@@ -757,8 +770,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     src/layers/linear.cu:169-215).  bfloat16 operands accumulate in float32; a float32 weight
     keeps its product in true float32 (no TF32), whatever x is."""
     _dev(x, weight)
-    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
-            and x.shape[1] % 8 == 0 and weight.data_ptr() % 16 == 0):
+    rows = x.shape[0]
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and weight.data_ptr() % 16 == 0
+            and rows >= 1 and (rows <= SKINNY_MAX_ROWS
+                               or (rows <= SKINNY_SMALL_MAX_ROWS and skinny_small(weight.shape[0], weight.shape[1])))):
         return linear_skinny(x, weight, out_dtype or x.dtype, partials_ok=partials_ok)
     if x.shape[0] >= PAIR_MIN_ROWS and (out_dtype or x.dtype) in (torch.float32, torch.bfloat16) and _pair_takes(
             x, weight, weight.shape[0], "plain"):

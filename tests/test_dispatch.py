@@ -2,6 +2,8 @@
 engine's own kernels, and when a position part offers a table for the step."""
 import types
 
+import pytest
+
 import torch
 
 from litellmengine_b200.config.specs import PositionSpec
@@ -59,3 +61,17 @@ def test_decode_key_splits_follow_the_length_and_the_wave_fill():
     finally:
         del attention._slots[dev]
         attention._split_choice.clear()
+
+
+@pytest.mark.gpu
+def test_small_products_take_the_streaming_kernel_up_to_32_rows():
+    """On the GPU (the rule reads the device's SM count): the products of a 0.6B-sized layer are small,
+    those of an 8B-sized layer and an output head are not; `linear` follows."""
+    assert all(ops.skinny_small(n, k) for n, k in ((4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)))
+    assert not any(ops.skinny_small(n, k) for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 1024)))
+    before = ops.launch_count
+    x = torch.randn(24, 1024, device="cuda:0").bfloat16()
+    w = (torch.randn(4096, 1024, device="cuda:0") * 0.05).bfloat16()
+    y = ops.linear(x, w, out_dtype=torch.float32)
+    assert ops.launch_count > before                              # the engine's own kernel ran, not the library's
+    assert float((y - x.float() @ w.float().t()).abs().max()) < 1e-4

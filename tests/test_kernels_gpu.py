@@ -459,10 +459,12 @@ def test_prefill_kernel_window_edges(window):
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (16, 48, 4096), (9, 1000, 1544),
-                                   (5, 17, 8), (8, 6144, 4096)])
+                                   (5, 17, 8), (8, 6144, 4096), (17, 331, 80), (24, 1000, 1544), (32, 4096, 1024),
+                                   (29, 1024, 3072)])
 def test_skinny_product(M, N, K, out_dtype):
     """The weight-streaming product for decode steps, its weights fetched box by box from their plain
-    layout, against float64, at sizes that are no multiple of its tiles (N of 64, K of 256, M of 8)."""
+    layout, against float64, at sizes that are no multiple of its tiles (N of 64, K of 256, M of 8, 16
+    or 32: the 32-token tile is what small products take for 17 to 32 rows)."""
     torch.manual_seed(M * 1000 + N)
     x = torch.randn(M, K).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
@@ -479,7 +481,7 @@ def test_skinny_product(M, N, K, out_dtype):
 @pytest.mark.parametrize("M,N,K", [(1, 16, 512), (8, 100, 520), (3, 331, 80), (7, 48, 4096), (8, 1000, 1544),
                                    (5, 17, 8), (8, 6144, 4096), (2, 4096, 12288),
                                    (9, 100, 520), (16, 331, 80), (13, 1000, 1544), (16, 6144, 4096), (11, 4096, 12288),
-                                   (12, 70, 384), (16, 64, 128)])
+                                   (12, 70, 384), (16, 64, 128), (17, 100, 520), (32, 1000, 1544), (25, 6144, 1024)])
 def test_skinny_product_over_tiled_weights(M, N, K, out_dtype):
     """The same product reading a copy of the weights stored tile by tile (one bulk copy per
     stage): same sums as over the plain layout, at sizes with ragged edge tiles."""
