@@ -208,9 +208,12 @@ def decode_key_splits(device, n_dec: int, nkv: int, max_kv_len: int) -> int:
     16, 24 splits at 1,024, 2,304, 4,096, 16,384 keys), at least 64 keys a split.  (2) The grid runs in
     waves of two CTAs per SM: below that ceiling take the fewest splits that fill at least 0.85 of the
     waves they start, else the fullest (at 4,096 keys 20 rows: 5 splits, 40 rows: 4, 48 rows: 2,
-    where one split took a quarter longer; 8, 16, 32, 64 rows stay at 4, 2, 1, 1)."""
+    where one split took a quarter longer; 8, 16, 32, 64 rows stay at 4, 2, 1, 1; at 384 keys 48 rows
+    stay at one split: 1.71 ms a step on the 0.6B shape against 1.79 with two)."""
     by_length = max(1, min(math.ceil(math.sqrt(max_kv_len / 16.0)), -(-max_kv_len // 64)))
     most = max(s for s in _SPLIT_STEPS if s <= by_length)
+    if n_dec * nkv > _cta_slots(device):             # more CTAs than slots already: a split only evens out the waves,
+        most = max(1, min(most, max_kv_len // 512))  # which pays for its merge kernel from about 512 keys a split
     key = (device, n_dec * nkv, most)
     got = _split_choice.get(key)
     if got is None:

@@ -56,7 +56,8 @@ def test_decode_key_splits_follow_the_length_and_the_wave_fill():
         pick = lambda rows, kv, nkv=8: attention.decode_key_splits(dev, rows, nkv, kv)
         assert [pick(1, kv) for kv in (1, 64, 65, 300, 1024, 2304, 4096, 8192, 32768)] == [1, 1, 2, 4, 8, 12, 16, 16, 32]
         assert [pick(rows, 4096) for rows in (2, 4, 8, 12, 16, 20, 24, 32, 40, 48, 64, 128)] == [16, 8, 4, 3, 2, 5, 3, 1, 4, 2, 1, 1]
-        assert pick(40, 100) == 2 and pick(40, 64) == 1                 # a short context caps it
+        assert pick(40, 100) == 1 and pick(40, 1000) == 1 and pick(40, 2048) == 4   # evening out the waves pays from 512 keys a split
+        assert pick(4, 100) == 2 and pick(4, 64) == 1                   # fewer CTAs than slots: a short context caps the splits
         assert pick(1, 1300, nkv=2) == 8 and pick(1, 201, nkv=2) == 4
     finally:
         del attention._slots[dev]
